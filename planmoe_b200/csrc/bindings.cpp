@@ -1,0 +1,406 @@
+// Python bindings of the planmoe_b200 native extension (module planmoe_b200._C).
+//
+// Thin adapters from torch::Tensor to the raw-pointer launchers of planmoe.h; every CUDA op
+// runs on the current torch stream.  The list of exported functions covers what the
+// reference binds in PlanMoE/custom/custom_kernel.cpp:292-321 (CPU sparse ops, JIT invoke,
+// collective bootstrap, codec/comm pipeline), re-expressed for this design: the NCCL bootstrap
+// becomes the symmetric-heap runtime, the FIFO compress/comm/decompress triple becomes explicit
+// handles on the Python side.
+
+#include <torch/extension.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAStream.h>
+#include <c10/cuda/CUDAGuard.h>
+
+#include "planmoe.h"
+#include "runtime/symm_heap.h"
+#include "runtime/jit.h"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+namespace py = pybind11;
+using torch::Tensor;
+using namespace planmoe;
+
+namespace {
+
+cudaStream_t cur_stream() { return c10::cuda::getCurrentCUDAStream().stream(); }
+
+void check_cuda(cudaError_t e, const char* what) {
+  TORCH_CHECK(e == cudaSuccess, what, ": ", cudaGetErrorString(e));
+}
+
+#define DISPATCH_FLOAT(t, NAME, ...)                                                     \
+  [&] {                                                                                  \
+    switch ((t).scalar_type()) {                                                         \
+      case at::kFloat: { using scalar_t = float; return __VA_ARGS__(); }                 \
+      case at::kBFloat16: { using scalar_t = __nv_bfloat16; return __VA_ARGS__(); }      \
+      case at::kHalf: { using scalar_t = __half; return __VA_ARGS__(); }                 \
+      default: TORCH_CHECK(false, NAME, ": unsupported dtype ", (t).scalar_type());      \
+    }                                                                                    \
+  }()
+
+const float* opt_f32(const c10::optional<Tensor>& t) {
+  if (!t.has_value() || !t->defined()) return nullptr;
+  TORCH_CHECK(t->scalar_type() == at::kFloat && t->is_contiguous(), "gates must be contiguous fp32");
+  return t->data_ptr<float>();
+}
+
+// ---- CPU sparse ops -------------------------------------------------------------------------
+template <class T>
+const T* opt_ptr(const c10::optional<Tensor>& t) {
+  return (t.has_value() && t->defined()) ? t->data_ptr<T>() : nullptr;
+}
+
+Tensor cpu_scatter_op(const Tensor& x, const Tensor& idx, const Tensor& loc, const c10::optional<Tensor>& gates,
+                      int64_t E, int64_t C) {
+  TORCH_CHECK(!x.is_cuda() && x.dim() == 2 && x.is_contiguous());
+  const int K = idx.size(0), S = idx.size(1), M = x.size(1);
+  Tensor out = torch::empty({E * C, M}, x.options());
+  if (x.scalar_type() == at::kFloat)
+    cpu_scatter<float>(x.data_ptr<float>(), idx.data_ptr<int>(), loc.data_ptr<int>(), opt_ptr<float>(gates),
+                       out.data_ptr<float>(), K, S, M, E, C);
+  else
+    cpu_scatter<double>(x.data_ptr<double>(), idx.data_ptr<int>(), loc.data_ptr<int>(), opt_ptr<double>(gates),
+                        out.data_ptr<double>(), K, S, M, E, C);
+  return out;
+}
+Tensor cpu_gather_op(const Tensor& disp, const Tensor& idx, const Tensor& loc, const c10::optional<Tensor>& gates,
+                     int64_t C) {
+  TORCH_CHECK(!disp.is_cuda() && disp.dim() == 2 && disp.is_contiguous());
+  const int K = idx.size(0), S = idx.size(1), M = disp.size(1);
+  Tensor out = torch::empty({S, M}, disp.options());
+  if (disp.scalar_type() == at::kFloat)
+    cpu_gather<float>(disp.data_ptr<float>(), idx.data_ptr<int>(), loc.data_ptr<int>(), opt_ptr<float>(gates),
+                      out.data_ptr<float>(), K, S, M, C);
+  else
+    cpu_gather<double>(disp.data_ptr<double>(), idx.data_ptr<int>(), loc.data_ptr<int>(), opt_ptr<double>(gates),
+                       out.data_ptr<double>(), K, S, M, C);
+  return out;
+}
+Tensor cpu_gate_grad_op(const Tensor& disp, const Tensor& dy, const Tensor& idx, const Tensor& loc, int64_t C) {
+  TORCH_CHECK(!disp.is_cuda() && disp.is_contiguous() && dy.is_contiguous());
+  const int K = idx.size(0), S = idx.size(1), M = disp.size(1);
+  Tensor out = torch::empty({K, S}, disp.options());
+  if (disp.scalar_type() == at::kFloat)
+    cpu_gate_grad<float>(disp.data_ptr<float>(), dy.data_ptr<float>(), idx.data_ptr<int>(), loc.data_ptr<int>(),
+                         out.data_ptr<float>(), K, S, M, C);
+  else
+    cpu_gate_grad<double>(disp.data_ptr<double>(), dy.data_ptr<double>(), idx.data_ptr<int>(), loc.data_ptr<int>(),
+                          out.data_ptr<double>(), K, S, M, C);
+  return out;
+}
+
+// ---- CUDA dispatch ops ----------------------------------------------------------------------
+Tensor build_slot_map_op(const Tensor& idx, const Tensor& loc, int64_t E, int64_t C) {
+  TORCH_CHECK(idx.is_cuda() && idx.scalar_type() == at::kInt && idx.is_contiguous() && loc.is_contiguous());
+  c10::cuda::CUDAGuard guard(idx.device());
+  Tensor smap = torch::empty({E * C}, idx.options());
+  launch_build_slot_map(idx.data_ptr<int>(), loc.data_ptr<int>(), smap.data_ptr<int>(), idx.size(0), idx.size(1), E, C,
+                        cur_stream());
+  return smap;
+}
+
+Tensor dispatch_scatter_op(const Tensor& x, const Tensor& slot_map, const c10::optional<Tensor>& gates, int64_t K,
+                           int64_t n_slots) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.is_contiguous(), "x must be contiguous [S, M] on CUDA");
+  const int S = x.size(0), M = x.size(1);
+  TORCH_CHECK((M * x.element_size()) % 16 == 0, "row bytes must be a multiple of 16");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor out = torch::empty({n_slots, M}, x.options());
+  DISPATCH_FLOAT(x, "dispatch_scatter", [&] {
+    launch_scatter_rows<scalar_t>(reinterpret_cast<const scalar_t*>(x.data_ptr()), slot_map.data_ptr<int>(),
+                                  opt_f32(gates), reinterpret_cast<scalar_t*>(out.data_ptr()), K, S, M, 1, n_slots,
+                                  nullptr, false, cur_stream());
+  });
+  return out;
+}
+
+Tensor dispatch_gather_op(const Tensor& disp, const Tensor& idx, const Tensor& loc, const c10::optional<Tensor>& gates,
+                          int64_t C) {
+  TORCH_CHECK(disp.is_cuda() && disp.dim() == 2 && disp.is_contiguous());
+  const int K = idx.size(0), S = idx.size(1), M = disp.size(1);
+  TORCH_CHECK(K <= 8, "top-k above 8 is not supported by the gather kernel");
+  TORCH_CHECK((M * disp.element_size()) % 16 == 0, "row bytes must be a multiple of 16");
+  c10::cuda::CUDAGuard guard(disp.device());
+  Tensor out = torch::empty({S, M}, disp.options());
+  DISPATCH_FLOAT(disp, "dispatch_gather", [&] {
+    launch_gather_rows<scalar_t>(disp.data_ptr(), nullptr, idx.data_ptr<int>(), loc.data_ptr<int>(), opt_f32(gates),
+                                 reinterpret_cast<scalar_t*>(out.data_ptr()), K, S, M, C, nullptr, cur_stream());
+  });
+  return out;
+}
+
+Tensor dispatch_gate_grad_op(const Tensor& disp, const Tensor& dy, const Tensor& idx, const Tensor& loc, int64_t C) {
+  TORCH_CHECK(disp.is_cuda() && disp.is_contiguous() && dy.is_contiguous() && disp.scalar_type() == dy.scalar_type());
+  const int K = idx.size(0), S = idx.size(1), M = disp.size(1);
+  c10::cuda::CUDAGuard guard(disp.device());
+  Tensor out = torch::empty({K, S}, disp.options().dtype(at::kFloat));
+  DISPATCH_FLOAT(disp, "dispatch_gate_grad", [&] {
+    launch_gate_grad<scalar_t>(reinterpret_cast<const scalar_t*>(disp.data_ptr()),
+                               reinterpret_cast<const scalar_t*>(dy.data_ptr()), idx.data_ptr<int>(),
+                               loc.data_ptr<int>(), out.data_ptr<float>(), K, S, M, C, cur_stream());
+  });
+  return out;
+}
+
+// ---- fused gate -------------------------------------------------------------------------------
+// returns (idx[K,S] i32, loc[K,S] i32, gates[K,S] f32, slot_map[E*C] i32, top1_count[E] i32, l_aux[1] f32)
+std::vector<Tensor> gate_forward_op(const Tensor& logits, int64_t K, int64_t C, bool normalize) {
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.is_contiguous());
+  const int S = logits.size(0), E = logits.size(1);
+  TORCH_CHECK(E <= 64 && K <= 4 && K <= E, "fused gate supports up to 64 experts and top-4");
+  c10::cuda::CUDAGuard guard(logits.device());
+  auto iopt = logits.options().dtype(at::kInt);
+  auto fopt = logits.options().dtype(at::kFloat);
+  Tensor idx = torch::empty({K, S}, iopt), loc = torch::empty({K, S}, iopt);
+  Tensor gates = torch::empty({K, S}, fopt), raw = torch::empty({K, S}, fopt);
+  Tensor smap = torch::empty({(int64_t)E * C}, iopt);
+  Tensor top1 = torch::empty({E}, iopt), laux = torch::empty({1}, fopt);
+  const int nblk = gate_workspace_blocks(S);
+  Tensor ws_rank = torch::empty({K, S}, iopt);
+  Tensor ws_cnt = torch::empty({nblk, K, E}, iopt);
+  Tensor ws_score = torch::empty({nblk, E}, fopt);
+  const float eps = logits.scalar_type() == at::kFloat ? 1.1920929e-07f
+                    : (logits.scalar_type() == at::kHalf ? 9.765625e-04f : 7.8125e-03f);
+  DISPATCH_FLOAT(logits, "gate_forward", [&] {
+    launch_gate_forward<scalar_t>(reinterpret_cast<const scalar_t*>(logits.data_ptr()), S, E, K, C, normalize, eps,
+                                  idx.data_ptr<int>(), loc.data_ptr<int>(), gates.data_ptr<float>(),
+                                  raw.data_ptr<float>(), smap.data_ptr<int>(), top1.data_ptr<int>(),
+                                  laux.data_ptr<float>(), ws_rank.data_ptr<int>(), ws_cnt.data_ptr<int>(),
+                                  ws_score.data_ptr<float>(), cur_stream());
+  });
+  return {idx, loc, gates, smap, top1, laux};
+}
+
+Tensor gate_backward_op(const Tensor& logits, const Tensor& idx, const c10::optional<Tensor>& dgates,
+                        const c10::optional<Tensor>& dl_aux, const Tensor& top1, bool normalize) {
+  const int S = logits.size(0), E = logits.size(1), K = idx.size(0);
+  c10::cuda::CUDAGuard guard(logits.device());
+  Tensor out = torch::empty_like(logits);
+  const float eps = logits.scalar_type() == at::kFloat ? 1.1920929e-07f
+                    : (logits.scalar_type() == at::kHalf ? 9.765625e-04f : 7.8125e-03f);
+  DISPATCH_FLOAT(logits, "gate_backward", [&] {
+    launch_gate_backward<scalar_t>(reinterpret_cast<const scalar_t*>(logits.data_ptr()), S, E, K, normalize, eps,
+                                   idx.data_ptr<int>(), opt_f32(dgates), opt_f32(dl_aux), top1.data_ptr<int>(),
+                                   reinterpret_cast<scalar_t*>(out.data_ptr()), cur_stream());
+  });
+  return out;
+}
+
+Tensor cumsum_sub_one_op(const Tensor& x) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.scalar_type() == at::kInt && x.is_contiguous());
+  c10::cuda::CUDAGuard guard(x.device());
+  const int S = x.size(0), E = x.size(1);
+  Tensor out = torch::empty_like(x);
+  Tensor ws = torch::empty({cumsum_tiles(S), E}, x.options());
+  launch_cumsum_sub_one(x.data_ptr<int>(), out.data_ptr<int>(), ws.data_ptr<int>(), S, E, cur_stream());
+  return out;
+}
+
+// ---- int8 codec ---------------------------------------------------------------------------------
+std::vector<Tensor> int8_encode_op(const Tensor& rows) {
+  TORCH_CHECK(rows.is_cuda() && rows.dim() == 2 && rows.is_contiguous());
+  c10::cuda::CUDAGuard guard(rows.device());
+  const int R = rows.size(0), M = rows.size(1);
+  Tensor q = torch::empty({R, M}, rows.options().dtype(at::kByte));
+  Tensor scale = torch::empty({R}, rows.options().dtype(at::kFloat)), bias = torch::empty_like(scale);
+  DISPATCH_FLOAT(rows, "int8_encode", [&] {
+    launch_int8_encode<scalar_t>(reinterpret_cast<const scalar_t*>(rows.data_ptr()), q.data_ptr<uint8_t>(),
+                                 scale.data_ptr<float>(), bias.data_ptr<float>(), R, M, cur_stream());
+  });
+  return {q, scale, bias};
+}
+Tensor int8_decode_op(const Tensor& q, const Tensor& scale, const Tensor& bias, at::ScalarType dtype) {
+  TORCH_CHECK(q.is_cuda() && q.dim() == 2 && q.is_contiguous() && q.scalar_type() == at::kByte);
+  c10::cuda::CUDAGuard guard(q.device());
+  const int R = q.size(0), M = q.size(1);
+  Tensor out = torch::empty({R, M}, q.options().dtype(dtype));
+  DISPATCH_FLOAT(out, "int8_decode", [&] {
+    launch_int8_decode<scalar_t>(q.data_ptr<uint8_t>(), scale.data_ptr<float>(), bias.data_ptr<float>(),
+                                 reinterpret_cast<scalar_t*>(out.data_ptr()), R, M, cur_stream());
+  });
+  return out;
+}
+
+// ---- grouped GEMM ---------------------------------------------------------------------------
+// Generic entry: operands are 3-D bf16 tensors [groups, rows, cols] with contiguous last dim
+// (4-D [chunks, groups, rows, cols] when `chunks` > 1); `*_mn` says the MN dim is the contiguous one.
+struct GemmOpts {
+  int64_t epilogue = 0, activation = 0;
+  c10::optional<Tensor> bias, aux, out;
+  // flag gate
+  int64_t gate_flags_ptr = 0, gate_rows = 0, gate_want = 0;
+  // push
+  int64_t heap_bases_ptr = 0, push_data_off = 0, push_flag_off = 0, push_rows = 0, push_C = 0, push_c0 = 0,
+          push_chunk = 0, W = 1, my_rank = 0;
+  int64_t budget_ms = 0, status_ptr = 0, max_ctas = 0;
+};
+
+GemmOperand operand_of(const Tensor& t, bool mn_major) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16, "GEMM operands must be CUDA bf16");
+  TORCH_CHECK(t.dim() == 3 || t.dim() == 4, "GEMM operand must be [groups, rows, cols] or [chunks, groups, rows, cols]");
+  TORCH_CHECK(t.stride(-1) == 1, "GEMM operand needs a contiguous last dim");
+  GemmOperand o{};
+  o.ptr = t.data_ptr();
+  o.mn_major = mn_major ? 1 : 0;
+  const int d = t.dim();
+  o.rows = t.size(d - 2); o.cols = t.size(d - 1);
+  o.row_stride = t.stride(d - 2);
+  o.group_stride = t.size(d - 3) > 1 ? t.stride(d - 3) : 0;
+  o.chunks = d == 4 ? t.size(0) : 1;
+  o.chunk_stride = (d == 4 && t.size(0) > 1) ? t.stride(0) : 0;
+  return o;
+}
+
+Tensor grouped_gemm_op(const Tensor& A, bool a_mn, const Tensor& B, bool b_mn, const GemmOpts& o) {
+  c10::cuda::CUDAGuard guard(A.device());
+  GemmArgs g{};
+  g.A = operand_of(A, a_mn);
+  g.B = operand_of(B, b_mn);
+  const int groups = A.size(A.dim() - 3);
+  TORCH_CHECK(B.size(B.dim() - 3) == groups, "group count mismatch");
+  g.groups = groups;
+  g.M = a_mn ? g.A.cols : g.A.rows;
+  g.K = a_mn ? g.A.rows : g.A.cols;
+  g.N = b_mn ? g.B.cols : g.B.rows;
+  const int64_t kb = b_mn ? g.B.rows : g.B.cols;
+  TORCH_CHECK(kb == g.K, "contraction extents differ: ", g.K, " vs ", kb);
+  g.epilogue = o.epilogue; g.activation = o.activation;
+
+  Tensor out;
+  if (o.epilogue != kEpiPush) {
+    if (o.out.has_value() && o.out->defined()) {
+      out = *o.out;
+      TORCH_CHECK(out.scalar_type() == at::kBFloat16 && out.stride(-1) == 1 && out.dim() == 3);
+    } else {
+      out = torch::empty({groups, g.M, g.N}, A.options());
+    }
+    g.D = out.data_ptr(); g.d_row_stride = out.stride(1); g.d_group_stride = out.stride(0);
+  }
+  if (o.aux.has_value() && o.aux->defined()) {
+    const Tensor& aux = *o.aux;
+    TORCH_CHECK(aux.scalar_type() == at::kBFloat16 && aux.stride(-1) == 1 && aux.dim() == 3);
+    g.aux = aux.data_ptr(); g.aux_row_stride = aux.stride(1); g.aux_group_stride = aux.stride(0);
+  } else {
+    TORCH_CHECK(o.epilogue != kEpiDAct, "activation-backward epilogue needs aux");
+  }
+  if (o.bias.has_value() && o.bias->defined()) {
+    const Tensor& b = *o.bias;
+    TORCH_CHECK(b.scalar_type() == at::kBFloat16 && b.is_contiguous() && b.numel() == (int64_t)groups * g.N);
+    g.bias = b.data_ptr(); g.bias_group_stride = g.N;
+  }
+  g.gate_flags = reinterpret_cast<const unsigned long long*>(o.gate_flags_ptr);
+  g.gate_rows = o.gate_rows; g.gate_want = o.gate_want;
+  g.heap_bases = reinterpret_cast<const unsigned long long*>(o.heap_bases_ptr);
+  g.push_data_off = o.push_data_off; g.push_flag_off = o.push_flag_off; g.push_rows = o.push_rows;
+  g.push_C = o.push_C; g.push_c0 = o.push_c0; g.push_chunk = o.push_chunk; g.W = o.W; g.my_rank = o.my_rank;
+  g.budget_ns = (unsigned long long)o.budget_ms * 1000000ull;
+  g.status = reinterpret_cast<int*>(o.status_ptr);
+  g.max_ctas = o.max_ctas;
+  if (o.epilogue == kEpiPush) TORCH_CHECK(g.heap_bases != nullptr, "push epilogue needs heap bases");
+  check_cuda(launch_grouped_gemm(g, cur_stream()), "grouped_gemm");
+  return out;
+}
+
+Tensor colsum_op(const Tensor& x) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 3 && x.stride(2) == 1);
+  c10::cuda::CUDAGuard guard(x.device());
+  const int groups = x.size(0), N = x.size(2);
+  const int64_t rows = x.size(1);
+  TORCH_CHECK(N % 2 == 0);
+  const int64_t slabs = (rows + 255) / 256;
+  Tensor buf = torch::empty({(int64_t)groups * N * (1 + slabs)}, x.options().dtype(at::kFloat));
+  launch_colsum_bf16(x.data_ptr(), buf.data_ptr<float>(), groups, rows, N, x.stride(1), x.stride(0), cur_stream());
+  return buf.narrow(0, 0, (int64_t)groups * N).view({groups, N});
+}
+
+// ---- push / wait wrappers for the fused MoE path ------------------------------------------------
+void scatter_push_op(const Tensor& x, const Tensor& slot_map, const c10::optional<Tensor>& gates, int64_t K, int64_t E,
+                     int64_t C, int64_t heap_bases_ptr, int64_t data_off, int64_t flag_off, int64_t W, int64_t my_rank,
+                     int64_t chunks, int64_t ctas_per_msg) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.is_contiguous());
+  c10::cuda::CUDAGuard guard(x.device());
+  PushArgs pa{};
+  pa.heap_bases = reinterpret_cast<const unsigned long long*>(heap_bases_ptr);
+  pa.data_off = data_off; pa.flag_off = flag_off; pa.scale_off = 0;
+  pa.W = W; pa.my_rank = my_rank; pa.chunks = chunks; pa.ctas_per_msg = ctas_per_msg;
+  TORCH_CHECK(E % W == 0 && C % chunks == 0);
+  const int S = x.size(0), M = x.size(1);
+  DISPATCH_FLOAT(x, "scatter_push", [&] {
+    launch_scatter_rows<scalar_t>(reinterpret_cast<const scalar_t*>(x.data_ptr()), slot_map.data_ptr<int>(),
+                                  opt_f32(gates), nullptr, K, S, M, E, C, &pa, false, cur_stream());
+  });
+}
+
+Tensor gather_wait_op(int64_t disp_ptr, at::ScalarType dtype, int64_t M, const Tensor& idx, const Tensor& loc,
+                      const c10::optional<Tensor>& gates, int64_t C, int64_t flags_ptr, int64_t n_flags, int64_t want,
+                      int64_t budget_ms, int64_t status_ptr) {
+  c10::cuda::CUDAGuard guard(idx.device());
+  const int K = idx.size(0), S = idx.size(1);
+  Tensor out = torch::empty({S, M}, idx.options().dtype(dtype));
+  WaitArgs wa{};
+  wa.flags = reinterpret_cast<const unsigned long long*>(flags_ptr);
+  wa.n_flags = n_flags; wa.want = want; wa.budget_ns = (unsigned long long)budget_ms * 1000000ull;
+  wa.status = reinterpret_cast<int*>(status_ptr);
+  DISPATCH_FLOAT(out, "gather_wait", [&] {
+    launch_gather_rows<scalar_t>(reinterpret_cast<const void*>(disp_ptr), nullptr, idx.data_ptr<int>(),
+                                 loc.data_ptr<int>(), opt_f32(gates), reinterpret_cast<scalar_t*>(out.data_ptr()), K, S,
+                                 M, C, flags_ptr ? &wa : nullptr, cur_stream());
+  });
+  return out;
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.doc() = "planmoe_b200 native extension (sm_100a kernels, symmetric heap, CPU reference ops)";
+  m.def("cpu_scatter", &cpu_scatter_op);
+  m.def("cpu_gather", &cpu_gather_op);
+  m.def("cpu_gate_grad", &cpu_gate_grad_op);
+  m.def("build_slot_map", &build_slot_map_op);
+  m.def("dispatch_scatter", &dispatch_scatter_op);
+  m.def("dispatch_gather", &dispatch_gather_op);
+  m.def("dispatch_gate_grad", &dispatch_gate_grad_op);
+  m.def("gate_forward", &gate_forward_op);
+  m.def("gate_backward", &gate_backward_op);
+  m.def("cumsum_sub_one", &cumsum_sub_one_op);
+  m.def("int8_encode", &int8_encode_op);
+  m.def("int8_decode", &int8_decode_op);
+  m.def("colsum", &colsum_op);
+  m.def("scatter_push", &scatter_push_op);
+  m.def("gather_wait", &gather_wait_op);
+  m.def("gemm_push_arrivals", &gemm_push_arrivals);
+
+  py::class_<GemmOpts>(m, "GemmOpts")
+      .def(py::init<>())
+      .def_readwrite("epilogue", &GemmOpts::epilogue)
+      .def_readwrite("activation", &GemmOpts::activation)
+      .def_readwrite("bias", &GemmOpts::bias)
+      .def_readwrite("aux", &GemmOpts::aux)
+      .def_readwrite("out", &GemmOpts::out)
+      .def_readwrite("gate_flags_ptr", &GemmOpts::gate_flags_ptr)
+      .def_readwrite("gate_rows", &GemmOpts::gate_rows)
+      .def_readwrite("gate_want", &GemmOpts::gate_want)
+      .def_readwrite("heap_bases_ptr", &GemmOpts::heap_bases_ptr)
+      .def_readwrite("push_data_off", &GemmOpts::push_data_off)
+      .def_readwrite("push_flag_off", &GemmOpts::push_flag_off)
+      .def_readwrite("push_rows", &GemmOpts::push_rows)
+      .def_readwrite("push_C", &GemmOpts::push_C)
+      .def_readwrite("push_c0", &GemmOpts::push_c0)
+      .def_readwrite("push_chunk", &GemmOpts::push_chunk)
+      .def_readwrite("W", &GemmOpts::W)
+      .def_readwrite("my_rank", &GemmOpts::my_rank)
+      .def_readwrite("budget_ms", &GemmOpts::budget_ms)
+      .def_readwrite("status_ptr", &GemmOpts::status_ptr)
+      .def_readwrite("max_ctas", &GemmOpts::max_ctas);
+  m.def("grouped_gemm", &grouped_gemm_op);
+  m.def("tensor_from_ptr", [](int64_t ptr, int64_t nbytes, int64_t device) {
+    return torch::from_blob(reinterpret_cast<void*>(ptr), {nbytes},
+                            torch::TensorOptions().dtype(at::kByte).device(at::kCUDA, device));
+  });
+
+  bind_symm_heap(m);
+  bind_jit(m);
+}

@@ -1,0 +1,641 @@
+// Grouped bf16 GEMM for the expert FFNs on 5th-generation tensor cores (sm_100a).
+//
+//   D[g] (M x N) = A[g] (M x K) . B[g] (K x N)          g = 0 .. groups-1, fp32 accumulate
+//
+// Hand-written tcgen05 pipeline, one persistent CTA per SM, 192 threads in three roles:
+//   warp 0      TMA producer: cp.async.bulk.tensor (4-D maps, 128-byte swizzle) into a 4-stage
+//               shared-memory ring, completion on mbarriers.  When the A operand is a receive
+//               buffer that peer GPUs fill, the producer first acquire-waits (bounded) on the
+//               flag of every source rank whose rows the tile touches: the GEMM starts on a
+//               tile as soon as its rows have landed ("flag-gated A").
+//   warp 1      MMA issuer: one thread issues tcgen05.mma.cta_group::1.kind::f16, 128 x 256 x 16
+//               per instruction, accumulating in TMEM (2 x 256 columns, double buffered so the
+//               epilogue of tile i overlaps the main loop of tile i+1); tcgen05.commit releases
+//               ring stages and publishes the accumulator.
+//   warps 2..5  epilogue: tcgen05.ld 32x32b -> registers -> bias / activation / activation
+//               backward -> bf16 -> swizzled shared-memory staging -> full-line 16-byte stores,
+//               either to local memory or straight into the combine buffer of the rank that
+//               owns the token ("push"), followed by a release-add on that rank's flag.
+//
+// Operands may be K-major or MN-major (weights are stored input-major, and the weight-gradient
+// GEMMs contract over the token dimension), so all four FFN GEMM flavours — forward, dgrad,
+// wgrad — run on this one kernel without transposed copies.  A split-K "chunk" dimension lets a
+// weight-gradient GEMM contract over all pipeline chunks of a receive buffer in one launch.
+//
+// TMA loads here never use cluster multicast, and peer memory is only ever written with plain
+// stores and read with plain flag loads.  Every wait (mbarrier or flag) is bounded: on expiry the
+// CTA records a code in the status word, drains, frees its TMEM and returns.
+//
+// Takes the place of the reference's torch.matmul -> cuBLAS calls and separate bias / activation
+// kernels (PlanMoE/experts/ffn.py:76-78) and of the permute copies around them
+// (PlanMoE/impls/communicate.py:604-623).
+
+#include "planmoe.h"
+#include "kernels/common.cuh"
+
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include <mutex>
+
+namespace planmoe {
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int kStages = 4;
+constexpr int kAccStages = 2;
+constexpr int kThreads = 192;
+constexpr int kEpiWarps = 4;
+constexpr uint32_t kABytes = BM * BK * 2;          // 16 KiB
+constexpr uint32_t kBBytes = BN * BK * 2;          // 32 KiB
+constexpr uint32_t kStageBytes = kABytes + kBBytes;
+constexpr uint32_t kStagingPerWarp = 2 * 32 * 128; // two 32-row x 128-byte tiles
+constexpr uint32_t kSmemRing = kStages * kStageBytes;
+constexpr uint32_t kSmemStaging = kEpiWarps * kStagingPerWarp;
+constexpr uint32_t kSmemBias = BN * 4;
+constexpr uint32_t kSmemBars = 256;
+constexpr uint32_t kSmemTotal = kSmemRing + kSmemStaging + kSmemBias + kSmemBars + 1024;  // + align slack
+constexpr uint32_t kTmemCols = 512;
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ void fence_barrier_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0,
+                                            int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void epi_bar_sync() {
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, Blackwell descriptor version 1.
+//   bits [0,14) start address >> 4, [16,30) leading byte offset >> 4, [32,46) stride byte offset >> 4,
+//   [46,48) version = 1, [61,64) layout = 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// Instruction descriptor for kind::f16 with bf16 inputs and fp32 accumulation:
+//   [4,6) D format = 1 (f32), [7,10) A format = 1 (bf16), [10,13) B format = 1 (bf16),
+//   [15] A MN-major, [16] B MN-major, [17,23) N >> 3, [24,29) M >> 4.
+__host__ __device__ constexpr uint32_t make_idesc(bool a_mn, bool b_mn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
+         ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+struct KernelParams {
+  int groups, M, N, K;           // K per chunk
+  int a_chunks;                  // split-K chunks (A and B agree)
+  int epilogue, activation;
+  __nv_bfloat16* D; long long d_row_stride, d_group_stride;
+  __nv_bfloat16* aux; long long aux_row_stride, aux_group_stride;
+  const __nv_bfloat16* bias; long long bias_group_stride;
+  const unsigned long long* gate_flags; int gate_rows; unsigned long long gate_want;
+  const unsigned long long* heap_bases; unsigned long long push_data_off, push_flag_off;
+  int push_rows, push_C, push_c0, push_chunk, W, my_rank;
+  unsigned long long budget_ns; int* status;
+};
+
+struct Ctl {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t acc_full[kAccStages];
+  uint64_t acc_empty[kAccStages];
+  uint32_t tmem_base;
+  volatile int abort;
+  volatile int epi_abort[2];   // written by epilogue warps before a barrier, read after it
+};
+
+// Bounded mbarrier wait: false on timeout or when another role already aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, Ctl* ctl, unsigned long long budget_ns,
+                                          int* status, int role, int detail) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 63u) == 0u) {
+      if (ctl->abort) return false;
+      if (global_timer_ns() - t0 > budget_ns) {
+        ctl->abort = 1;
+        report_status(status, kStatusMbarTimeout, role, detail, (int)parity);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ float act_fwd(float x, int act) {
+  switch (act) {
+    case kActRelu: return fmaxf(x, 0.f);
+    case kActGelu: return 0.5f * x * (1.f + erff(x * 0.70710678118654752f));
+    case kActSilu: return x / (1.f + __expf(-x));
+    default: return x;
+  }
+}
+__device__ __forceinline__ float act_bwd(float x, int act) {
+  switch (act) {
+    case kActRelu: return x > 0.f ? 1.f : 0.f;
+    case kActGelu: {
+      const float cdf = 0.5f * (1.f + erff(x * 0.70710678118654752f));
+      const float pdf = 0.3989422804014327f * __expf(-0.5f * x * x);
+      return cdf + x * pdf;
+    }
+    case kActSilu: {
+      const float s = 1.f / (1.f + __expf(-x));
+      return s * (1.f + x * (1.f - s));
+    }
+    default: return 1.f;
+  }
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kThreads, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const KernelParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* ring = smem;
+  uint8_t* staging = smem + kSmemRing;
+  float* bias_s = reinterpret_cast<float*>(smem + kSmemRing + kSmemStaging);
+  Ctl* ctl = reinterpret_cast<Ctl*>(smem + kSmemRing + kSmemStaging + kSmemBias);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  const int mt_count = (p.M + BM - 1) / BM;
+  const int nt_count = (p.N + BN - 1) / BN;
+  const int tiles = p.groups * mt_count * nt_count;
+  const int kb_per_chunk = (p.K + BK - 1) / BK;
+  const int kb_total = kb_per_chunk * p.a_chunks;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(smem_u32(&ctl->full[s]), 1); mbar_init(smem_u32(&ctl->empty[s]), 1); }
+    for (int a = 0; a < kAccStages; ++a) { mbar_init(smem_u32(&ctl->acc_full[a]), 1); mbar_init(smem_u32(&ctl->acc_empty[a]), kEpiWarps); }
+    ctl->abort = 0;
+    ctl->epi_abort[0] = ctl->epi_abort[1] = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+        const int nt = tile % nt_count;
+        const int mt = (tile / nt_count) % mt_count;
+        const int g = tile / (nt_count * mt_count);
+        const int m0 = mt * BM, n0 = nt * BN;
+        if (p.gate_flags != nullptr) {
+          const int last_row = min(m0 + BM, p.M) - 1;
+          const int s_lo = m0 / p.gate_rows, s_hi = last_row / p.gate_rows;
+          for (int s = s_lo; s <= s_hi && ok; ++s)
+            ok = wait_flag_ge(p.gate_flags + s, p.gate_want, p.budget_ns, p.status, s);
+          if (!ok) { ctl->abort = 1; break; }
+          fence_proxy_async();   // peers' generic-proxy stores -> this thread's async-proxy loads
+        }
+        for (int kb = 0; kb < kb_total; ++kb) {
+          ok = mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1u, ctl, p.budget_ns, p.status, 0, stage);
+          if (!ok) break;
+          const uint32_t full = smem_u32(&ctl->full[stage]);
+          const uint32_t sa = smem_u32(ring + stage * kStageBytes);
+          const uint32_t sb = sa + kABytes;
+          const int chunk = kb / kb_per_chunk;
+          const int k0 = (kb - chunk * kb_per_chunk) * BK;
+          mbar_expect_tx(full, kStageBytes);
+          if constexpr (!A_MN) {
+            tma_load_4d(sa, &tmA, full, k0, m0, g, chunk);
+          } else {
+#pragma unroll
+            for (int i = 0; i < BM / 64; ++i) tma_load_4d(sa + i * (64 * BK * 2), &tmA, full, m0 + i * 64, k0, g, chunk);
+          }
+          if constexpr (!B_MN) {
+            tma_load_4d(sb, &tmB, full, k0, n0, g, chunk);
+          } else {
+#pragma unroll
+            for (int i = 0; i < BN / 64; ++i) tma_load_4d(sb + i * (64 * BK * 2), &tmB, full, n0 + i * 64, k0, g, chunk);
+          }
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) __nanosleep(200000);   // let bulk copies already in flight land before teardown
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(A_MN, B_MN);
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+        ok = mbar_wait(smem_u32(&ctl->acc_empty[acc]), acc_phase ^ 1u, ctl, p.budget_ns, p.status, 1, 100 + acc);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < kb_total; ++kb) {
+          ok = mbar_wait(smem_u32(&ctl->full[stage]), phase, ctl, p.budget_ns, p.status, 1, stage);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t sa = smem_u32(ring + stage * kStageBytes);
+          const uint32_t sb = sa + kABytes;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            uint64_t adesc, bdesc;
+            if constexpr (!A_MN) adesc = make_desc(sa + k * (UMMA_K * 2), 16, 1024);
+            else                 adesc = make_desc(sa + k * (UMMA_K * 128), 64 * BK * 2, 1024);
+            if constexpr (!B_MN) bdesc = make_desc(sb + k * (UMMA_K * 2), 16, 1024);
+            else                 bdesc = make_desc(sb + k * (UMMA_K * 128), 64 * BK * 2, 1024);
+            umma_bf16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&ctl->empty[stage]));
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit(smem_u32(&ctl->acc_full[acc]));
+        if (++acc == kAccStages) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ epilogue warps
+    const int q = warp & 3;                       // TMEM lane quarter this warp may read
+    const int ewarp = warp - 2;
+    uint8_t* st0 = staging + ewarp * kStagingPerWarp;
+    uint8_t* st1 = st0 + 32 * 128;
+    const int etid = threadIdx.x - 64;            // 0..127
+    uint32_t acc = 0, acc_phase = 0, iter = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+      const int nt = tile % nt_count;
+      const int mt = (tile / nt_count) % mt_count;
+      const int g = tile / (nt_count * mt_count);
+      const int m0 = mt * BM, n0 = nt * BN;
+
+      // All four epilogue warps take the same exit decision: a warp that timed out raises the
+      // flag of this iteration's parity before the barrier, everyone reads it after the barrier.
+      bool got = mbar_wait(smem_u32(&ctl->acc_full[acc]), acc_phase, ctl, p.budget_ns, p.status, 2, acc);
+      got = __all_sync(0xffffffffu, got);
+      if (!got && lane == 0) ctl->epi_abort[iter & 1] = 1;
+      epi_bar_sync();                              // also: previous tile's readers of bias_s are done
+      if (ctl->epi_abort[iter & 1]) { ok = false; break; }
+      ++iter;
+      for (int i = etid; i < BN; i += 128) {
+        float b = 0.f;
+        if (p.bias != nullptr && n0 + i < p.N) b = __bfloat162float(p.bias[(long long)g * p.bias_group_stride + n0 + i]);
+        bias_s[i] = b;
+      }
+      epi_bar_sync();
+      tc_fence_after();
+
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+
+#pragma unroll 1
+      for (int c64 = 0; c64 < BN / 64; ++c64) {
+        const int nb = n0 + c64 * 64;              // first global column of this 64-wide slab
+        if (nb >= p.N) break;
+        uint32_t v[64];
+        tmem_ld32(t_row + c64 * 64, v);
+        tmem_ld32(t_row + c64 * 64 + 32, v + 32);
+        tmem_ld_wait();
+
+        // optional input slab (pre-activation) for the activation backward
+        if (p.epilogue == kEpiDAct) {
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int r = it * 4 + (lane >> 3), c = lane & 7;
+            const int m = m0 + q * 32 + r;
+            uint4 val = make_uint4(0, 0, 0, 0);
+            if (m < p.M && nb + c * 8 < p.N)
+              val = *reinterpret_cast<const uint4*>(p.aux + (long long)g * p.aux_group_stride + (long long)m * p.aux_row_stride + nb + c * 8);
+            *reinterpret_cast<uint4*>(st1 + r * 128 + ((c ^ (r & 7)) << 4)) = val;
+          }
+          __syncwarp();
+        }
+
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          float f[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[c * 8 + i]) + bias_s[c64 * 64 + c * 8 + i];
+          uint4 outv, auxv;
+          if (p.epilogue == kEpiBiasAct) {
+            auxv = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+#pragma unroll
+            for (int i = 0; i < 8; ++i) f[i] = act_fwd(f[i], p.activation);
+            *reinterpret_cast<uint4*>(st1 + lane * 128 + ((c ^ (lane & 7)) << 4)) = auxv;
+          } else if (p.epilogue == kEpiDAct) {
+            const uint4 pre = *reinterpret_cast<const uint4*>(st1 + lane * 128 + ((c ^ (lane & 7)) << 4));
+            const __nv_bfloat162* ph = reinterpret_cast<const __nv_bfloat162*>(&pre);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float2 pf = __bfloat1622float2(ph[i]);
+              f[2 * i] *= act_bwd(pf.x, p.activation);
+              f[2 * i + 1] *= act_bwd(pf.y, p.activation);
+            }
+          }
+          outv = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+          *reinterpret_cast<uint4*>(st0 + lane * 128 + ((c ^ (lane & 7)) << 4)) = outv;
+        }
+        __syncwarp();
+
+        // full-line write-out: each instruction stores 4 rows x 128 bytes
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+          const int r = it * 4 + (lane >> 3), c = lane & 7;
+          const int m = m0 + q * 32 + r;
+          if (m < p.M && nb + c * 8 < p.N) {
+            const uint4 val = *reinterpret_cast<const uint4*>(st0 + r * 128 + ((c ^ (r & 7)) << 4));
+            if (p.epilogue == kEpiPush) {
+              const int s = m / p.push_rows, cc = m - s * p.push_rows;
+              __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(
+                  reinterpret_cast<uint8_t*>(p.heap_bases[s]) + p.push_data_off);
+              const long long drow = ((long long)p.my_rank * p.groups + g) * p.push_C + p.push_c0 + cc;
+              *reinterpret_cast<uint4*>(base + drow * p.N + nb + c * 8) = val;
+            } else {
+              *reinterpret_cast<uint4*>(p.D + (long long)g * p.d_group_stride + (long long)m * p.d_row_stride + nb + c * 8) = val;
+              if (p.epilogue == kEpiBiasAct && p.aux != nullptr) {
+                const uint4 a = *reinterpret_cast<const uint4*>(st1 + r * 128 + ((c ^ (r & 7)) << 4));
+                *reinterpret_cast<uint4*>(p.aux + (long long)g * p.aux_group_stride + (long long)m * p.aux_row_stride + nb + c * 8) = a;
+              }
+            }
+          }
+        }
+        __syncwarp();
+      }
+
+      // accumulator drained: hand the TMEM stage back to the MMA warp
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ctl->acc_empty[acc]));
+      if (++acc == kAccStages) { acc = 0; acc_phase ^= 1u; }
+
+      if (p.epilogue == kEpiPush) {
+        epi_bar_sync();                            // every row of the tile has been stored
+        if (etid == 0) {
+          __threadfence_system();
+          const int last_row = min(m0 + BM, p.M) - 1;
+          const int s_lo = m0 / p.push_rows, s_hi = last_row / p.push_rows;
+          for (int s = s_lo; s <= s_hi; ++s) {
+            unsigned long long* flags = reinterpret_cast<unsigned long long*>(
+                reinterpret_cast<uint8_t*>(p.heap_bases[s]) + p.push_flag_off);
+            red_release_sys_add(flags + (long long)p.push_chunk * p.W + p.my_rank, 1ull);
+          }
+        }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn get_encode_fn() {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(sym);
+  });
+  return fn;
+}
+
+// 4-D map over (cols, rows, groups, chunks) with a (64, box_rows, 1, 1) box and 128-byte swizzle.
+bool make_map(CUtensorMap* map, const GemmOperand& op, int groups, int box_rows) {
+  EncodeFn enc = get_encode_fn();
+  if (enc == nullptr) return false;
+  const cuuint64_t chunks = op.chunks > 0 ? op.chunks : 1;
+  cuuint64_t dims[4] = {(cuuint64_t)op.cols, (cuuint64_t)op.rows, (cuuint64_t)groups, chunks};
+  long long gs = op.group_stride > 0 ? op.group_stride : op.rows * op.row_stride;
+  long long cs = op.chunk_stride > 0 ? op.chunk_stride : gs * groups;
+  cuuint64_t strides[3] = {(cuuint64_t)op.row_stride * 2, (cuuint64_t)gs * 2, (cuuint64_t)cs * 2};
+  cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(op.ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+template <bool A_MN, bool B_MN>
+cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const KernelParams& kp, int ctas,
+                           cudaStream_t stream) {
+  auto kern = grouped_gemm_kernel<A_MN, B_MN>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTotal);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  kern<<<ctas, kThreads, kSmemTotal, stream>>>(ta, tb, kp);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+int gemm_push_arrivals(int groups, int M, int N, int push_rows, int s) {
+  const int nt = (N + BN - 1) / BN;
+  const int lo = s * push_rows, hi = (s + 1) * push_rows - 1;
+  if (lo >= M) return 0;
+  const int mt_lo = lo / BM, mt_hi = (hi < M ? hi : M - 1) / BM;
+  return groups * nt * (mt_hi - mt_lo + 1);
+}
+
+cudaError_t launch_grouped_gemm(const GemmArgs& a, cudaStream_t stream) {
+  if (a.groups <= 0 || a.M <= 0 || a.N <= 0 || a.K <= 0) return cudaSuccess;
+  // 16-byte rules of TMA and of the vector epilogue
+  if ((a.N % 8) || (a.A.cols % 8) || (a.B.cols % 8) || (a.A.row_stride % 8) || (a.B.row_stride % 8) ||
+      (reinterpret_cast<uintptr_t>(a.A.ptr) % 16) || (reinterpret_cast<uintptr_t>(a.B.ptr) % 16))
+    return cudaErrorInvalidValue;
+  if (a.A.chunks != a.B.chunks) return cudaErrorInvalidValue;
+
+  CUtensorMap ta, tb;
+  if (!make_map(&ta, a.A, a.groups, a.A.mn_major ? BK : BM)) return cudaErrorInvalidValue;
+  if (!make_map(&tb, a.B, a.groups, a.B.mn_major ? BK : BN)) return cudaErrorInvalidValue;
+
+  KernelParams kp{};
+  kp.groups = a.groups; kp.M = a.M; kp.N = a.N; kp.K = a.K;
+  kp.a_chunks = a.A.chunks > 0 ? a.A.chunks : 1;
+  kp.epilogue = a.epilogue; kp.activation = a.activation;
+  kp.D = reinterpret_cast<__nv_bfloat16*>(a.D); kp.d_row_stride = a.d_row_stride; kp.d_group_stride = a.d_group_stride;
+  kp.aux = reinterpret_cast<__nv_bfloat16*>(a.aux); kp.aux_row_stride = a.aux_row_stride; kp.aux_group_stride = a.aux_group_stride;
+  kp.bias = reinterpret_cast<const __nv_bfloat16*>(a.bias); kp.bias_group_stride = a.bias_group_stride;
+  kp.gate_flags = a.gate_flags; kp.gate_rows = a.gate_rows > 0 ? a.gate_rows : a.M; kp.gate_want = a.gate_want;
+  kp.heap_bases = a.heap_bases; kp.push_data_off = a.push_data_off; kp.push_flag_off = a.push_flag_off;
+  kp.push_rows = a.push_rows > 0 ? a.push_rows : a.M; kp.push_C = a.push_C; kp.push_c0 = a.push_c0;
+  kp.push_chunk = a.push_chunk; kp.W = a.W; kp.my_rank = a.my_rank;
+  kp.budget_ns = a.budget_ns ? a.budget_ns : 20000000000ull;
+  kp.status = a.status;
+
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (sm_count <= 0) sm_count = 148;
+  }
+  const int tiles = a.groups * ((a.M + BM - 1) / BM) * ((a.N + BN - 1) / BN);
+  int ctas = a.max_ctas > 0 ? a.max_ctas : sm_count;
+  if (ctas > tiles) ctas = tiles;
+
+  if (!a.A.mn_major && a.B.mn_major) return launch_variant<false, true>(ta, tb, kp, ctas, stream);
+  if (!a.A.mn_major && !a.B.mn_major) return launch_variant<false, false>(ta, tb, kp, ctas, stream);
+  if (a.A.mn_major && a.B.mn_major) return launch_variant<true, true>(ta, tb, kp, ctas, stream);
+  return launch_variant<true, false>(ta, tb, kp, ctas, stream);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Column sums (bias gradients): fp32 [groups][N] = sum over rows of bf16 [groups][rows][N].
+// Two-stage and deterministic: every CTA reduces a row slab, partials are added in slab order.
+// ---------------------------------------------------------------------------------------------
+namespace {
+constexpr int kColsumSlab = 256;
+
+__global__ void __launch_bounds__(256)
+colsum_partial_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ partial, long long rows, int N,
+                      long long row_stride, long long group_stride, int slabs) {
+  // grid: (N/ (256*2) rounded up, slabs, groups); each thread owns 2 adjacent columns
+  const int col = (blockIdx.x * 256 + threadIdx.x) * 2;
+  if (col >= N) return;
+  const int slab = blockIdx.y, g = blockIdx.z;
+  const long long r0 = (long long)slab * kColsumSlab;
+  const long long r1 = r0 + kColsumSlab < rows ? r0 + kColsumSlab : rows;
+  const __nv_bfloat16* base = x + (long long)g * group_stride + col;
+  float a0 = 0.f, a1 = 0.f;
+  for (long long r = r0; r < r1; ++r) {
+    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(base + r * row_stride));
+    a0 += f.x; a1 += f.y;
+  }
+  float* dst = partial + ((long long)g * slabs + slab) * N + col;
+  dst[0] = a0; dst[1] = a1;
+}
+
+__global__ void colsum_final_kernel(const float* __restrict__ partial, float* __restrict__ out, int N, int slabs) {
+  const int col = blockIdx.x * blockDim.x + threadIdx.x;
+  const int g = blockIdx.y;
+  if (col >= N) return;
+  float acc = 0.f;
+  for (int s = 0; s < slabs; ++s) acc += partial[((long long)g * slabs + s) * N + col];
+  out[(long long)g * N + col] = acc;
+}
+}  // namespace
+
+// `out` must have room for groups*N floats followed by groups*slabs*N floats of scratch, where
+// slabs = ceil(rows / 256); see colsum_scratch_floats().
+void launch_colsum_bf16(const void* x, float* out, int groups, long long rows, int N, long long row_stride,
+                        long long group_stride, cudaStream_t stream) {
+  const int slabs = (int)((rows + kColsumSlab - 1) / kColsumSlab);
+  float* partial = out + (long long)groups * N;
+  dim3 g1((N / 2 + 255) / 256, slabs, groups);
+  colsum_partial_kernel<<<g1, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), partial, rows, N,
+                                              row_stride, group_stride, slabs);
+  dim3 g2((N + 255) / 256, groups);
+  colsum_final_kernel<<<g2, 256, 0, stream>>>(partial, out, N, slabs);
+}
+
+}  // namespace planmoe

@@ -1,0 +1,126 @@
+// Host-side launch interface of the planmoe_b200 native kernels (sm_100a).
+// Every launcher enqueues on the given stream and allocates nothing.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace planmoe {
+
+// ---- CPU reference loops (kernels/cpu_ref.cpp) ---------------------------------------------
+template <class T>
+void cpu_scatter(const T* x, const int* idx, const int* loc, const T* gates, T* disp, int K, int S,
+                 int M, int E, int C);
+template <class T>
+void cpu_gather(const T* disp, const int* idx, const int* loc, const T* gates, T* out, int K, int S,
+                int M, int C);
+template <class T>
+void cpu_gate_grad(const T* disp, const T* dy, const int* idx, const int* loc, T* dgates, int K,
+                   int S, int M, int C);
+
+// ---- peer-push / flag-wait descriptors -------------------------------------------------------
+// A buffer in the symmetric heap is named by its byte offset; rank r's copy lives at
+// heap_bases[r] + offset (heap_bases is a device array of W peer-mapped base addresses).
+struct PushArgs {
+  const unsigned long long* heap_bases;  // device [W]
+  unsigned long long data_off;           // destination buffer
+  unsigned long long flag_off;           // u64 flags [chunks][W] on the destination rank
+  unsigned long long scale_off;          // fp32 (range, lo) per row, int8 mode only
+  int W, my_rank, chunks, ctas_per_msg;
+};
+struct WaitArgs {
+  const unsigned long long* flags;  // local device pointer, n_flags consecutive u64
+  int n_flags;
+  unsigned long long want;          // proceed when every flag >= want
+  unsigned long long budget_ns;     // give up (status word, kernel returns) after this long
+  int* status;                      // host-mapped int32[8]
+};
+
+// ---- kernels/dispatch.cu ---------------------------------------------------------------------
+void launch_build_slot_map(const int* idx, const int* loc, int* slot_map, int K, int S, int E, int C,
+                           cudaStream_t stream);
+template <class T>
+void launch_scatter_rows(const T* x, const int* slot_map, const float* gates, T* local_out, int K,
+                         int S, int M, int E, int C, const PushArgs* push, bool quant,
+                         cudaStream_t stream);
+template <class T>
+void launch_gather_rows(const void* disp, const float* scale_bias, const int* idx, const int* loc,
+                        const float* gates, T* out, int K, int S, int M, int C, const WaitArgs* wait,
+                        cudaStream_t stream);
+template <class T>
+void launch_gate_grad(const T* disp, const T* dy, const int* idx, const int* loc, float* dgates,
+                      int K, int S, int M, int C, cudaStream_t stream);
+
+// ---- kernels/gate.cu -------------------------------------------------------------------------
+int gate_workspace_blocks(int S);
+template <class T>
+void launch_gate_forward(const T* logits, int S, int E, int K, int C, bool normalize, float eps,
+                         int* idx, int* loc, float* gates, float* raw_gate, int* slot_map,
+                         int* top1_count, float* l_aux, int* ws_rank, int* ws_blk_count,
+                         float* ws_blk_score, cudaStream_t stream);
+template <class T>
+void launch_gate_backward(const T* logits, int S, int E, int K, bool normalize, float eps,
+                          const int* idx, const float* dgates, const float* dl_aux,
+                          const int* top1_count, T* dlogits, cudaStream_t stream);
+int cumsum_tiles(int S);
+void launch_cumsum_sub_one(const int* x, int* out, int* tile_sum, int S, int E, cudaStream_t stream);
+
+// ---- codec/int8.cu ---------------------------------------------------------------------------
+template <class T>
+void launch_int8_encode(const T* x, unsigned char* q, float* scale, float* bias, int R, int M,
+                        cudaStream_t stream);
+template <class T>
+void launch_int8_decode(const unsigned char* q, const float* scale, const float* bias, T* out, int R,
+                        int M, cudaStream_t stream);
+
+// ---- kernels/gemm_tcgen05.cu -----------------------------------------------------------------
+// Grouped bf16 GEMM  D[g] (Mg x N) = A[g] (Mg x K) . B[g] (K x N), fp32 accumulation in TMEM.
+enum GemmEpilogue : int {
+  kEpiStore = 0,    // D = acc (+ bias)
+  kEpiBiasAct = 1,  // aux = acc + bias ; D = act(aux)
+  kEpiDAct = 2,     // D = acc * act'(aux)
+  kEpiPush = 3,     // (acc + bias) stored into the origin ranks' combine buffers + flags
+};
+enum Activation : int { kActIdentity = 0, kActRelu = 1, kActGelu = 2, kActSilu = 3 };
+
+struct GemmOperand {
+  const void* ptr;     // bf16
+  int mn_major;        // 0: rows of the MN dim, K contiguous; 1: rows of K, MN dim contiguous
+  // Extents / strides in elements.  Row dim = MN rows (K-major) or K rows (MN-major).
+  long long rows, cols;            // cols = contiguous extent
+  long long row_stride;            // elements between rows
+  long long group_stride;          // elements between groups
+  long long chunk_stride;          // elements between split-K chunks (0 if unused)
+  int chunks;                      // split-K chunks folded into the K loop (>= 1)
+};
+
+struct GemmArgs {
+  GemmOperand A, B;
+  int groups, M, N, K;             // per-group problem; K is per chunk when chunks > 1
+  int epilogue, activation;
+  void* D; long long d_row_stride, d_group_stride;          // bf16 output
+  void* aux; long long aux_row_stride, aux_group_stride;    // bf16 pre-activation (in or out)
+  const void* bias; long long bias_group_stride;            // bf16 [groups][N] or null
+  // flag-gated A rows (A is a receive buffer filled by peers): rows [s*gate_rows, (s+1)*gate_rows)
+  // of every group become readable when gate_flags[s] >= gate_want.
+  const unsigned long long* gate_flags; int gate_rows; unsigned long long gate_want;
+  // push epilogue: row m of group g belongs to rank s = m / push_rows; it is stored at
+  // heap_bases[s] + push_data_off + ((my_rank*groups + g) * push_C + push_c0 + m % push_rows) * N
+  // and flag (push_flag_off)[push_chunk * W + my_rank] on rank s is incremented once per tile.
+  const unsigned long long* heap_bases; unsigned long long push_data_off, push_flag_off;
+  int push_rows, push_C, push_c0, push_chunk, W, my_rank;
+  unsigned long long budget_ns; int* status;
+  int max_ctas;                    // 0 = one per SM
+};
+
+// Returns cudaSuccess or the launch / tensor-map error.
+cudaError_t launch_grouped_gemm(const GemmArgs& args, cudaStream_t stream);
+// Number of flag arrivals rank s receives per push launch (host helper for the receiver).
+int gemm_push_arrivals(int groups, int M, int N, int push_rows, int s);
+
+// Column sums of a bf16 [groups][rows][N] tensor -> fp32 [groups][N] (bias gradients).
+void launch_colsum_bf16(const void* x, float* out, int groups, long long rows, int N,
+                        long long row_stride, long long group_stride, cudaStream_t stream);
+
+}  // namespace planmoe

@@ -1,0 +1,206 @@
+"""All-to-all algorithms behind the ``comm_name`` switch of the MoE layer.
+
+Python face of the ``AbstractComm`` extension point (reference:
+``PlanMoE/custom/comm/abstract.h:10-24``) and its four algorithms:
+
+  naive  flat exchange, one message per peer                      (``comm/naive.cpp:11-27``)
+  pipe   Pipe-A2A: intra-group and inter-group peers progress     (``comm/pipe.cpp:12-31``)
+         concurrently on two independent channels
+  hetu   hierarchical: gather to group leader, leaders exchange,  (``comm/hetu.cpp:15-76``)
+         leader scatters; layout transforms in between
+  dd     2DH: intra-group exchange then inter-group exchange      (``dd_comm.cpp:15-90``)
+  nccl   torch.distributed ``all_to_all_single`` (the measured baseline transport)
+
+Every algorithm takes a tensor whose dim 0 is split evenly over the W destination ranks and
+returns the tensor whose dim 0 is the concatenation over the W source ranks.  "Group" means
+``LOCAL_SIZE`` consecutive ranks (env, default: all ranks); on one NVSwitch box
+``LOCAL_SIZE=4`` gives the two logical 4-GPU groups.
+
+On CUDA worlds the moves are SM-driven peer stores of the symmetric-heap transport
+(``planmoe_b200.parallel.transport``); on CPU (Gloo) worlds the same index arithmetic runs on
+``torch.distributed`` primitives, which is what the multi-process CPU tests exercise.
+Unknown names fall back to ``naive`` like the reference factory (``custom_kernel.cpp:209-224``).
+"""
+
+import os
+
+import torch
+import torch.distributed as dist
+
+from ..impls import communicate as C
+
+
+def local_size(world):
+    ls = int(os.environ.get('LOCAL_SIZE', 0)) or world
+    ls = min(ls, world)
+    return ls if world % ls == 0 else world
+
+
+class AbstractComm:
+    name = 'abstract'
+
+    def __init__(self, group=None):
+        self.group = group
+        self.world_size = C.get_world_size(group)
+        self.world_rank = C.get_world_rank(group)
+        self.local_size = local_size(self.world_size)
+        self.local_rank = self.world_rank % self.local_size
+
+    # -- extension points ---------------------------------------------------------------
+    def pre_comm(self, t):
+        return t
+
+    def all_to_all(self, t):
+        raise NotImplementedError
+
+    # -- helpers ------------------------------------------------------------------------
+    def _use_transport(self, t):
+        return t.is_cuda and self.world_size > 1
+
+    def _transport(self):
+        from . import transport
+        return transport.get_transport(self.group)
+
+
+def _gloo_a2a(t, group):
+    out = torch.empty_like(t)
+    dist.all_to_all_single(out, t, group=group)
+    return out
+
+
+class NaiveComm(AbstractComm):
+    name = 'naive'
+
+    def all_to_all(self, t):
+        if self.world_size == 1 or C.TUTEL_SKIP_A2A:
+            return t
+        t = t.contiguous()
+        if self._use_transport(t):
+            return self._transport().all_to_all(t, algo='flat')
+        return _gloo_a2a(t, self.group)
+
+
+class NcclComm(AbstractComm):
+    """Baseline: the collective library's own all-to-all."""
+    name = 'nccl'
+
+    def all_to_all(self, t):
+        if self.world_size == 1 or C.TUTEL_SKIP_A2A:
+            return t
+        return _gloo_a2a(t.contiguous(), self.group)
+
+
+class PipeComm(AbstractComm):
+    """Pipe-A2A: peers inside my group and peers outside it are served by two independent
+    channels that run concurrently."""
+    name = 'pipe'
+
+    def all_to_all(self, t):
+        if self.world_size == 1 or C.TUTEL_SKIP_A2A:
+            return t
+        t = t.contiguous()
+        if self._use_transport(t):
+            return self._transport().all_to_all(t, algo='pipe')
+        W, L, me = self.world_size, self.local_size, self.world_rank
+        out = torch.empty_like(t)
+        src, dst = t.view(W, -1), out.view(W, -1)
+        dst[me].copy_(src[me])
+        my_group = me // L
+        for intra in (True, False):          # two independent batches of point-to-point ops
+            ops = []
+            for p in range(W):
+                if p == me or ((p // L) == my_group) != intra:
+                    continue
+                gp = dist.get_global_rank(self.group, p) if self.group is not None else p
+                ops.append(dist.P2POp(dist.isend, src[p], gp, group=self.group))
+                ops.append(dist.P2POp(dist.irecv, dst[p], gp, group=self.group))
+            if ops:
+                for w in dist.batch_isend_irecv(ops):
+                    w.wait()
+        return out
+
+
+def _subgroups(L):
+    """(intra-group pg, same-local-rank pg) for groups of L consecutive world ranks."""
+    g = C.create_groups_from_world(-L)
+    return g.model_group, g.data_group
+
+
+class DdComm(AbstractComm):
+    """2DH: phase 1 exchanges inside the group so that every rank holds what its group sends
+    to its own local index everywhere; phase 2 exchanges between groups."""
+    name = 'dd'
+
+    def all_to_all(self, t):
+        W, L = self.world_size, self.local_size
+        if W == 1 or C.TUTEL_SKIP_A2A:
+            return t
+        t = t.contiguous()
+        if L == W or L == 1:
+            return NaiveComm(self.group).all_to_all(t)
+        if self._use_transport(t):
+            return self._transport().all_to_all(t, algo='dd')
+        assert self.group is None or self.group == dist.group.WORLD, \
+            "hierarchical CPU path works on the world group"
+        N = W // L
+        intra, inter = _subgroups(L)
+        x = t.view(N, L, -1).transpose(0, 1).contiguous()        # [dl][dn][n]
+        x = _gloo_a2a(x, intra)                                  # [sl][dn][n]
+        x = x.view(L, N, -1).transpose(0, 1).contiguous()        # [dn][sl][n]
+        x = _gloo_a2a(x, inter)                                  # [sn][sl][n]
+        return x.view(t.shape)
+
+
+class HeTuComm(AbstractComm):
+    """Hierarchical leader algorithm: gather -> transform -> leaders' exchange -> transform
+    -> scatter.  Works for any dtype and rank of tensor (the reference's scratch sizing only
+    fits 2-D fp32)."""
+    name = 'hetu'
+
+    def all_to_all(self, t):
+        W, L = self.world_size, self.local_size
+        if W == 1 or C.TUTEL_SKIP_A2A:
+            return t
+        t = t.contiguous()
+        if L == W and not t.is_cuda:
+            pass  # one group: leader gathers everything, transforms, scatters
+        if self._use_transport(t):
+            return self._transport().all_to_all(t, algo='hetu')
+        assert self.group is None or self.group == dist.group.WORLD, \
+            "hierarchical CPU path works on the world group"
+        N = W // L
+        intra, inter = _subgroups(L)
+        me = self.world_rank
+        leader = (me // L) * L
+        is_leader = (me == leader)
+        flat = t.view(-1)
+        gathered = [torch.empty_like(flat) for _ in range(L)] if is_leader else None
+        dist.gather(flat, gathered, dst=leader, group=intra)
+        scatter_list = None
+        if is_leader:
+            x = torch.stack(gathered).view(L, N, L, -1)          # [sl][dn][dl][n]
+            x = x.permute(1, 2, 0, 3).contiguous()               # [dn][dl][sl][n]
+            if N > 1:
+                x = _gloo_a2a(x, inter)                          # [sn][dl][sl][n]
+            x = x.view(N, L, L, -1).permute(1, 0, 2, 3).contiguous()   # [dl][sn][sl][n]
+            scatter_list = [x[i].reshape(-1) for i in range(L)]
+        out = torch.empty_like(flat)
+        dist.scatter(out, scatter_list, src=leader, group=intra)
+        return out.view(t.shape)
+
+
+_REGISTRY = {}
+
+
+def register_comm(name, factory):
+    """Register ``factory(group) -> AbstractComm`` under ``name`` (overrides built-ins)."""
+    _REGISTRY[name] = factory
+
+
+def get_comm(name, group=None):
+    factory = _REGISTRY.get(name, NaiveComm)
+    return factory(group)
+
+
+for _cls in (NaiveComm, NcclComm, PipeComm, DdComm, HeTuComm):
+    register_comm(_cls.name, _cls)
