@@ -1,0 +1,308 @@
+#!/usr/bin/env python3
+"""Headline benchmark: MoE layer forward + backward (+ SGD step) tokens/s.
+
+Config (the reference's ``pre_test`` CLI-default shape, ``PlanMoE/examples/pre_test.py:50-60``):
+per rank 16 x 512 tokens, model_dim 2048, hidden 2048, 2 local experts per GPU, top-2 gate,
+capacity_factor 1.0, GELU, bf16, synthetic N(0,1) input, random-init weights, seed 0.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference|ref-torch]
+
+For N > 1 launch one process per GPU with ``python -m torch.distributed.run --nproc-per-node N``.
+Rank 0 prints ONE JSON line.  ``value`` is whole-job tokens/s from CUDA-event timing of exactly
+K steps (max over ranks), with an L2 flush (256 MiB write) between timed steps that is outside the
+event brackets.  ``e2e`` repeats the measurement through the public API including, every step,
+the pinned-host -> device copy of the step's input and a device -> host read of the loss.
+"""
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+CFG = dict(batch=16, tokens=512, model_dim=2048, hidden=2048, local_experts=2, top_k=2,
+           capacity_factor=1.0)
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=20)
+    ap.add_argument('--warmup', type=int, default=5)
+    ap.add_argument('--impl', default='ours', choices=['ours', 'reference', 'ref-torch'])
+    ap.add_argument('--degree', default='1')
+    ap.add_argument('--comm', default='naive')
+    ap.add_argument('--compress', default='no')
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+    Q = ('index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,'
+         'clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,'
+         'clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap')
+
+    def __init__(self, gpu_index):
+        self.idx = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix='.csv')
+            os.close(fd)
+            self.out = open(self.path, 'w')
+            self.proc = subprocess.Popen(
+                ['nvidia-smi', '-i', str(self.idx), '--query-gpu=' + self.Q, '--format=csv,noheader,nounits',
+                 '-lms', '200'], stdout=self.out, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        res = {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': [], 'samples': 0}
+        if self.proc is None:
+            return res
+        try:
+            self.proc.terminate()
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        try:
+            self.out.close()
+            rows = [r.strip().split(', ') for r in open(self.path) if r.strip()]
+            os.unlink(self.path)
+        except Exception:
+            return res
+        sm, reasons, mx = [], set(), None
+        names = ['hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap']
+        for r in rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1]))
+                mx = float(r[2])
+            except ValueError:
+                continue
+            for n, v in zip(names, r[5:9]):
+                if v.strip().lower().startswith('active'):
+                    reasons.add(n)
+        if sm:
+            hi = sorted(sm)[len(sm) // 2:]          # upper half = samples under load
+            res.update(sm_mhz=statistics.median(hi), sm_max_mhz=mx, reasons=sorted(reasons), samples=len(sm))
+        return res
+
+
+def reference_unavailable():
+    why = ("reference cannot be installed offline unmodified: setup.py lists sources under ./schemoe/ that do "
+           "not exist (the tree is named PlanMoE/) and links a privately patched libzfp from /home/xinglinpan/zfp")
+    note = os.path.join(ROOT, 'baseline', 'install_outcome.txt')
+    if os.path.exists(note):
+        first = open(note).read().strip().splitlines()
+        if first:
+            why = first[0]
+    print(json.dumps({'impl': 'reference', 'unavailable': why}))
+
+
+def build_ours(args, device, group_world):
+    import torch
+    from planmoe_b200 import moe
+    degree = args.degree if args.degree in ('auto',) else int(args.degree)
+    layer = moe.moe_layer(
+        gate_type={'type': 'top', 'k': CFG['top_k'], 'capacity_factor': CFG['capacity_factor'], 'fp32_gate': True},
+        model_dim=CFG['model_dim'],
+        experts={'type': 'ffn', 'count_per_node': CFG['local_experts'], 'hidden_size_per_expert': CFG['hidden'],
+                 'activation_fn': 'gelu'},
+        seeds=(1, 2 + (torch.distributed.get_rank() if group_world > 1 else 0), 3),
+        a2a_ffn_overlap_degree=degree, compress_name=args.compress, comm_name=args.comm)
+    layer = layer.to(device).to(torch.bfloat16)
+    layer.gates[0].wg.float()
+    return layer
+
+
+class RefTorchLayer:
+    """REF-TORCH: what the reference executes, restated with stock PyTorch only — ATen routing
+    (one-hot masks, cumsum), index_add scatter / gather, NCCL ``all_to_all_single``, permute copies and
+    ``torch.matmul`` experts, in the chunk order of ``PlanMoE/impls/overlap.py:59-74``."""
+
+    def __init__(self, device, world):
+        import torch
+        torch.manual_seed(2)
+        M, H, El = CFG['model_dim'], CFG['hidden'], CFG['local_experts']
+        self.world = world
+        self.wg = torch.nn.Parameter(torch.randn(El * world, M, device=device) * 0.02)
+        self.w1 = torch.nn.Parameter((torch.randn(El, M, H, device=device) * 0.02).bfloat16())
+        self.b1 = torch.nn.Parameter(torch.zeros(El, H, device=device).bfloat16())
+        self.w2 = torch.nn.Parameter((torch.randn(El, H, M, device=device) * 0.02).bfloat16())
+        self.b2 = torch.nn.Parameter(torch.zeros(El, M, device=device).bfloat16())
+
+    def parameters(self):
+        return [self.wg, self.w1, self.b1, self.w2, self.b2]
+
+    def __call__(self, x):
+        import torch
+        import torch.distributed as dist
+        import torch.nn.functional as F
+        from planmoe_b200.ops import dispatch as D
+        from planmoe_b200.impls import fast_dispatch as FD
+        W = self.world
+        scores = F.softmax(x.float() @ self.wg.t(), dim=1)
+        from planmoe_b200.jit_kernels import gating
+        gating.use_fast_cumsum = False
+        crit, l_aux = FD.extract_critical(scores, CFG['top_k'], capacity_factor=CFG['capacity_factor'], alignment=4)
+        plan = crit.slots
+        disp = D.scatter_torch(x.float(), plan, None).to(x.dtype).view(crit[0], -1, x.size(-1))
+
+        def a2a(t):
+            if W == 1:
+                return t
+            from planmoe_b200.impls.communicate import all_to_all_single
+            return all_to_all_single(t.contiguous())
+        y = a2a(disp)
+        El = y.size(0) // W
+        y = y.view(W, El, -1, y.size(-1)).transpose(0, 1).contiguous().view(El, -1, y.size(-1))
+        y = torch.matmul(F.gelu(torch.matmul(y, self.w1) + self.b1.unsqueeze(1)), self.w2) + self.b2.unsqueeze(1)
+        y = y.view(El, W, -1, y.size(-1)).transpose(0, 1).contiguous().view(W * El, -1, y.size(-1))
+        y = a2a(y)
+        out = D.gather_torch(y.float().view(-1, y.size(-1)), plan, crit.stacked_gates()).to(x.dtype)
+        out.l_aux = l_aux
+        return out
+
+
+def main():
+    args = parse()
+    if args.impl == 'reference':
+        reference_unavailable()
+        return 0
+
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    rank = int(os.environ.get('RANK', '0'))
+    local_rank = int(os.environ.get('LOCAL_RANK', '0'))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            print('bench.py: --gpus %d needs torch.distributed.run with %d processes' % (args.gpus, args.gpus),
+                  file=sys.stderr)
+            return 2
+    torch.cuda.set_device(local_rank)
+    device = torch.device('cuda', local_rank)
+    if world > 1:
+        dist.init_process_group('nccl', device_id=device)
+
+    S, M = CFG['batch'] * CFG['tokens'], CFG['model_dim']
+    if args.impl == 'ours':
+        layer = build_ours(args, device, world)
+        params = [p for p in layer.parameters()]
+        from planmoe_b200.ops import native
+        launch_count = native.lib().launch_count
+    else:
+        layer = RefTorchLayer(device, world)
+        params = layer.parameters()
+        launch_count = lambda: 0  # noqa: E731
+    opt = torch.optim.SGD(params, lr=1e-4)
+
+    torch.manual_seed(100 + rank)
+    host_x = torch.randn(S, M).to(torch.bfloat16).pin_memory()
+    x_dev = host_x.to(device, non_blocking=True)
+    host_loss = torch.zeros(1, dtype=torch.float32).pin_memory()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+
+    def step(x):
+        opt.zero_grad(set_to_none=True)
+        y = layer(x)
+        loss = y.float().pow(2).mean() + 0.01 * y.l_aux.float()
+        loss.backward()
+        opt.step()
+        return loss
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step(x_dev)
+    barrier()
+
+    # ---- device-timed region -------------------------------------------------------------
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    l0 = launch_count()
+    barrier()
+    for i in range(args.steps):
+        flush.fill_(i & 0xff)
+        starts[i].record()
+        step(x_dev)
+        ends[i].record()
+    barrier()
+    launches = launch_count() - l0
+    ms = sum(s.elapsed_time(e) for s, e in zip(starts, ends))
+
+    # ---- end-to-end region: pinned H2D of the input + D2H of the loss, every step ---------------
+    e2e_s = torch.cuda.Event(enable_timing=True)
+    e2e_e = torch.cuda.Event(enable_timing=True)
+    barrier()
+    e2e_s.record()
+    for i in range(args.steps):
+        x_in = host_x.to(device, non_blocking=True)
+        loss = step(x_in)
+        host_loss.copy_(loss.detach().reshape(1), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        _ = float(host_loss[0])
+    e2e_e.record()
+    barrier()
+    e2e_ms = e2e_s.elapsed_time(e2e_e)
+    clocks = sampler.stop() if rank == 0 else None
+
+    if args.impl == 'ours':
+        from planmoe_b200.parallel import transport
+        transport.get_transport(None).check()
+
+    t = torch.tensor([ms, e2e_ms], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = t.tolist()
+
+    if rank == 0:
+        tokens = S * world * args.steps
+        out = {
+            'metric': 'moe_layer_fwd_bwd_tokens_per_sec',
+            'value': tokens / (ms / 1e3),
+            'unit': 'tokens/s',
+            'n_gpus': world, 'steps': args.steps, 'warmup': max(args.warmup, 3),
+            'ms_per_step': ms / args.steps,
+            'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None,
+            'dtype': 'bf16', 'data': 'synthetic N(0,1) tokens, random-init weights',
+            'impl': args.impl,
+            'config': {
+                'model': 'pre_test MoE layer: model_dim 2048, hidden 2048, 2 local experts/GPU, top-2, cf 1.0, GELU',
+                'global_batch': CFG['batch'] * world, 'seq_len': CFG['tokens'],
+                'parallelism': 'ep%d' % world, 'step': 'forward + backward + SGD update',
+                'l2': 'flushed between timed steps (256 MiB write outside the event brackets)',
+                'degree': args.degree, 'comm': args.comm, 'compress': args.compress,
+            },
+            'clocks': clocks,
+            'e2e': {'value': tokens / (e2e_ms / 1e3), 'unit': 'tokens/s',
+                    'h2d_bytes_per_step': host_x.numel() * host_x.element_size(),
+                    'd2h_bytes_per_step': host_loss.numel() * host_loss.element_size()},
+            'gpu_launches': int(launches),
+        }
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == '__main__':
+    sys.exit(main())

@@ -19,6 +19,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <atomic>
+
 namespace py = pybind11;
 using torch::Tensor;
 using namespace planmoe;
@@ -26,6 +28,10 @@ using namespace planmoe;
 namespace {
 
 cudaStream_t cur_stream() { return c10::cuda::getCurrentCUDAStream().stream(); }
+
+// Kernels of this extension launched so far in this process (benchmarks report the delta).
+std::atomic<long long> g_launches{0};
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
 void check_cuda(cudaError_t e, const char* what) {
   TORCH_CHECK(e == cudaSuccess, what, ": ", cudaGetErrorString(e));
@@ -94,6 +100,7 @@ Tensor cpu_gate_grad_op(const Tensor& disp, const Tensor& dy, const Tensor& idx,
 
 // ---- CUDA dispatch ops ----------------------------------------------------------------------
 Tensor build_slot_map_op(const Tensor& idx, const Tensor& loc, int64_t E, int64_t C) {
+  count_launch(1);
   TORCH_CHECK(idx.is_cuda() && idx.scalar_type() == at::kInt && idx.is_contiguous() && loc.is_contiguous());
   c10::cuda::CUDAGuard guard(idx.device());
   Tensor smap = torch::empty({E * C}, idx.options());
@@ -104,6 +111,7 @@ Tensor build_slot_map_op(const Tensor& idx, const Tensor& loc, int64_t E, int64_
 
 Tensor dispatch_scatter_op(const Tensor& x, const Tensor& slot_map, const c10::optional<Tensor>& gates, int64_t K,
                            int64_t n_slots) {
+  count_launch(1);
   TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.is_contiguous(), "x must be contiguous [S, M] on CUDA");
   const int S = x.size(0), M = x.size(1);
   TORCH_CHECK((M * x.element_size()) % 16 == 0, "row bytes must be a multiple of 16");
@@ -119,6 +127,7 @@ Tensor dispatch_scatter_op(const Tensor& x, const Tensor& slot_map, const c10::o
 
 Tensor dispatch_gather_op(const Tensor& disp, const Tensor& idx, const Tensor& loc, const c10::optional<Tensor>& gates,
                           int64_t C) {
+  count_launch(1);
   TORCH_CHECK(disp.is_cuda() && disp.dim() == 2 && disp.is_contiguous());
   const int K = idx.size(0), S = idx.size(1), M = disp.size(1);
   TORCH_CHECK(K <= 8, "top-k above 8 is not supported by the gather kernel");
@@ -133,6 +142,7 @@ Tensor dispatch_gather_op(const Tensor& disp, const Tensor& idx, const Tensor& l
 }
 
 Tensor dispatch_gate_grad_op(const Tensor& disp, const Tensor& dy, const Tensor& idx, const Tensor& loc, int64_t C) {
+  count_launch(1);
   TORCH_CHECK(disp.is_cuda() && disp.is_contiguous() && dy.is_contiguous() && disp.scalar_type() == dy.scalar_type());
   const int K = idx.size(0), S = idx.size(1), M = disp.size(1);
   c10::cuda::CUDAGuard guard(disp.device());
@@ -148,6 +158,7 @@ Tensor dispatch_gate_grad_op(const Tensor& disp, const Tensor& dy, const Tensor&
 // ---- fused gate -------------------------------------------------------------------------------
 // returns (idx[K,S] i32, loc[K,S] i32, gates[K,S] f32, slot_map[E*C] i32, top1_count[E] i32, l_aux[1] f32)
 std::vector<Tensor> gate_forward_op(const Tensor& logits, int64_t K, int64_t C, bool normalize) {
+  count_launch(2);
   TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.is_contiguous());
   const int S = logits.size(0), E = logits.size(1);
   TORCH_CHECK(E <= 64 && K <= 4 && K <= E, "fused gate supports up to 64 experts and top-4");
@@ -176,6 +187,7 @@ std::vector<Tensor> gate_forward_op(const Tensor& logits, int64_t K, int64_t C, 
 
 Tensor gate_backward_op(const Tensor& logits, const Tensor& idx, const c10::optional<Tensor>& dgates,
                         const c10::optional<Tensor>& dl_aux, const Tensor& top1, bool normalize) {
+  count_launch(1);
   const int S = logits.size(0), E = logits.size(1), K = idx.size(0);
   c10::cuda::CUDAGuard guard(logits.device());
   Tensor out = torch::empty_like(logits);
@@ -190,6 +202,7 @@ Tensor gate_backward_op(const Tensor& logits, const Tensor& idx, const c10::opti
 }
 
 Tensor cumsum_sub_one_op(const Tensor& x) {
+  count_launch(2);
   TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.scalar_type() == at::kInt && x.is_contiguous());
   c10::cuda::CUDAGuard guard(x.device());
   const int S = x.size(0), E = x.size(1);
@@ -201,6 +214,7 @@ Tensor cumsum_sub_one_op(const Tensor& x) {
 
 // ---- int8 codec ---------------------------------------------------------------------------------
 std::vector<Tensor> int8_encode_op(const Tensor& rows) {
+  count_launch(1);
   TORCH_CHECK(rows.is_cuda() && rows.dim() == 2 && rows.is_contiguous());
   c10::cuda::CUDAGuard guard(rows.device());
   const int R = rows.size(0), M = rows.size(1);
@@ -213,6 +227,7 @@ std::vector<Tensor> int8_encode_op(const Tensor& rows) {
   return {q, scale, bias};
 }
 Tensor int8_decode_op(const Tensor& q, const Tensor& scale, const Tensor& bias, at::ScalarType dtype) {
+  count_launch(1);
   TORCH_CHECK(q.is_cuda() && q.dim() == 2 && q.is_contiguous() && q.scalar_type() == at::kByte);
   c10::cuda::CUDAGuard guard(q.device());
   const int R = q.size(0), M = q.size(1);
@@ -255,6 +270,7 @@ GemmOperand operand_of(const Tensor& t, bool mn_major) {
 }
 
 Tensor grouped_gemm_op(const Tensor& A, bool a_mn, const Tensor& B, bool b_mn, const GemmOpts& o) {
+  count_launch(1);
   c10::cuda::CUDAGuard guard(A.device());
   GemmArgs g{};
   g.A = operand_of(A, a_mn);
@@ -305,6 +321,7 @@ Tensor grouped_gemm_op(const Tensor& A, bool a_mn, const Tensor& B, bool b_mn, c
 }
 
 Tensor colsum_op(const Tensor& x) {
+  count_launch(2);
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 3 && x.stride(2) == 1);
   c10::cuda::CUDAGuard guard(x.device());
   const int groups = x.size(0), N = x.size(2);
@@ -320,6 +337,7 @@ Tensor colsum_op(const Tensor& x) {
 void scatter_push_op(const Tensor& x, const Tensor& slot_map, const c10::optional<Tensor>& gates, int64_t K, int64_t E,
                      int64_t C, int64_t heap_bases_ptr, int64_t data_off, int64_t flag_off, int64_t W, int64_t my_rank,
                      int64_t chunks, int64_t ctas_per_msg) {
+  count_launch(1);
   TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.is_contiguous());
   c10::cuda::CUDAGuard guard(x.device());
   PushArgs pa{};
@@ -337,6 +355,7 @@ void scatter_push_op(const Tensor& x, const Tensor& slot_map, const c10::optiona
 Tensor gather_wait_op(int64_t disp_ptr, at::ScalarType dtype, int64_t M, const Tensor& idx, const Tensor& loc,
                       const c10::optional<Tensor>& gates, int64_t C, int64_t flags_ptr, int64_t n_flags, int64_t want,
                       int64_t budget_ms, int64_t status_ptr) {
+  count_launch(1);
   c10::cuda::CUDAGuard guard(idx.device());
   const int K = idx.size(0), S = idx.size(1);
   Tensor out = torch::empty({S, M}, idx.options().dtype(dtype));
@@ -372,6 +391,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("scatter_push", &scatter_push_op);
   m.def("gather_wait", &gather_wait_op);
   m.def("gemm_push_arrivals", &gemm_push_arrivals);
+  m.def("launch_count", [] { return (long long)g_launches.load(); });
 
   py::class_<GemmOpts>(m, "GemmOpts")
       .def(py::init<>())

@@ -56,8 +56,9 @@ __global__ void __launch_bounds__(kRowThreads)
 scatter_rows_kernel(const T* __restrict__ x, const int* __restrict__ slot_map,
                     const float* __restrict__ gates, T* __restrict__ local_out, int K, int S,
                     int M, PushGeom g) {
-  // grid: (ctas_per_msg, chunks, W); message (r, j) = slots of rank r's experts in chunk j.
-  const int r = blockIdx.z, j = blockIdx.y;
+  // grid: (ctas_per_msg, W, chunks); message (r, j) = slots of rank r's experts in chunk j.
+  // The chunk is the slowest grid dimension so that chunk 0 leaves first for every destination.
+  const int r = blockIdx.y, j = blockIdx.z;
   const int Cc = g.C / g.chunks;
   const int rows = g.E_local * Cc;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -174,7 +175,7 @@ void launch_scatter_rows(const T* x, const int* slot_map, const float* gates, T*
     ctas = push->ctas_per_msg;
   }
   if (ctas < 1) ctas = 1;
-  dim3 grid(ctas, g.chunks, g.W);
+  dim3 grid(ctas, g.W, g.chunks);
   if (quant)
     scatter_rows_kernel<T, true><<<grid, kRowThreads, 0, stream>>>(x, slot_map, gates, local_out, K, S, M, g);
   else

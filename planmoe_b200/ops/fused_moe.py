@@ -1,0 +1,279 @@
+"""The fused expert-parallel MoE path for bf16 FFN experts on B200.
+
+Forward, per pipeline chunk j of the capacity dimension (``degree`` chunks):
+
+    fused gate kernel      softmax + top-k + slot scan + slot map + GShard loss
+    dispatch  (scatter)    slot-major gather of token rows, stored straight into the receive
+                           buffer of the rank that owns the expert, + release-add on its flag
+    expert GEMM 1          tcgen05; A tiles are read from the receive buffer as soon as the flags
+                           of the source ranks they touch have arrived; bias + activation epilogue
+    expert GEMM 2          tcgen05; the epilogue stores rows straight into the combine buffer of
+                           the rank that owns the token, + release-add on its flag
+    combine   (gather)     waits for the flags, gate-weighted sum over the k picks
+
+Backward mirrors it (combine-backward is a dispatch-like push of dY, the two dgrad GEMMs are
+flag-gated / pushing in the same way, dispatch-backward is a flag-waiting gather) and the two
+weight-gradient GEMMs contract over all chunks of the receive buffers in one launch each.
+
+No NCCL call and no library GEMM is on this path; with one rank the "peer" is the local heap and
+the same kernels run.  The receive buffers are laid out ``[chunk][E_local][W_src][C/chunks][M]``,
+i.e. they *are* the grouped-GEMM operands: the reference's permute copies, chunk splits and
+concatenations (``PlanMoE/impls/overlap.py:55-75``, ``impls/communicate.py:604-623``) have no
+counterpart here.
+
+Buffer reuse: every layer owns a ring of buffer sets; a set is held from its forward until its
+backward has run.  Two sets alternate in steady state — a peer can only write a set again after it
+has passed the last exchange of the previous step, which every rank enters after its own reads.
+Flags are never reset: each use adds a known number of arrivals, receivers wait for the
+cumulative count.
+"""
+
+import torch
+import torch.nn.functional as F
+
+from . import native
+from .gemm import ACT_CODES, EPI_BIAS_ACT, EPI_DACT, EPI_PUSH, EPI_STORE, grouped_gemm
+from ..parallel import transport as T
+
+MAX_CHUNKS = 32
+PH_DISPATCH, PH_COMBINE, PH_COMBINE_BWD, PH_DISPATCH_BWD = 0, 1, 2, 3
+
+
+class _BufferSet:
+    """Symmetric receive buffers + flags for one in-flight forward/backward of one layer."""
+
+    def __init__(self, tr, key):
+        E_l, W, C, M, O = key
+        self.tr = tr
+        el = 2
+        self.sz_x = E_l * W * C * M * el         # dispatch receive      [d][E_l][W][Cc][M]
+        self.sz_y = E_l * W * C * O * el         # combine receive       [E_g][C][O]
+        flags = 4 * MAX_CHUNKS * W * 8
+        total = 2 * self.sz_x + 2 * self.sz_y + flags
+        self.block = tr.alloc(total)
+        self.off_x = self.block.offset
+        self.off_y = self.off_x + self.sz_x
+        self.off_dy = self.off_y + self.sz_y
+        self.off_dx = self.off_dy + self.sz_y
+        self.off_flags = self.off_dx + self.sz_x
+        self.W = W
+        self.arrived = [0, 0, 0, 0]               # cumulative arrivals expected per flag, per phase
+        self.held = False
+
+    def flag_off(self, phase):
+        return self.off_flags + phase * MAX_CHUNKS * self.W * 8
+
+    def flag_ptr(self, phase, chunk=0):
+        base = self.tr.segments[self.block.segment].local_base()
+        return base + self.flag_off(phase) + chunk * self.W * 8
+
+    def view(self, off, shape):
+        return self.block.tensor(torch.bfloat16, shape, byte_offset=off - self.block.offset)
+
+
+class FusedState:
+    """Per-layer state of the fused path: transport handle and the ring of buffer sets."""
+
+    def __init__(self, layer):
+        self.tr = T.get_transport(layer.group)
+        self.sets = {}
+        self.turn = {}
+
+    def acquire(self, key):
+        ring = self.sets.setdefault(key, [])
+        turn = self.turn.get(key, 0)
+        if len(ring) < 2:
+            ring.append(_BufferSet(self.tr, key))
+            bs = ring[-1]
+        else:
+            bs = ring[turn % len(ring)]
+            if bs.held:
+                free = [b for b in ring if not b.held]
+                if free:
+                    bs = free[0]
+                else:
+                    ring.append(_BufferSet(self.tr, key))
+                    bs = ring[-1]
+        self.turn[key] = turn + 1
+        bs.held = True
+        return bs
+
+
+def _send_ctas(rows_per_msg, n_msgs):
+    """CTAs per (chunk, destination) message: about four waves of 148 SMs in total."""
+    return max(1, min((rows_per_msg + 7) // 8, max(1, 592 // max(n_msgs, 1))))
+
+
+class _Lease:
+    """Returns a buffer set to its ring when the autograd node that holds it goes away, whether
+    or not backward ever ran."""
+
+    def __init__(self, bs):
+        self.bs = bs
+
+    def __del__(self):
+        self.bs.held = False
+
+
+class _FusedGate(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, top_k, capacity, normalize):
+        lib = native.lib()
+        logits = logits.contiguous()
+        idx, loc, gates, slot_map, top1, l_aux = lib.gate_forward(logits, top_k, capacity, normalize)
+        ctx.save_for_backward(logits, idx, top1)
+        ctx.normalize = normalize
+        ctx.mark_non_differentiable(idx, loc, slot_map)
+        return gates, l_aux.view(()), idx, loc, slot_map
+
+    @staticmethod
+    def backward(ctx, dgates, dl_aux, *_):
+        logits, idx, top1 = ctx.saved_tensors
+        lib = native.lib()
+        dg = dgates.contiguous().float() if dgates is not None else None
+        dl = dl_aux.reshape(1).contiguous().float() if dl_aux is not None else None
+        return lib.gate_backward(logits, idx, dg, dl, top1, ctx.normalize), None, None, None
+
+
+def fused_gate(logits, top_k, capacity, normalize):
+    """(gates [K,S] fp32, l_aux scalar fp32, idx, loc, slot_map) — differentiable in logits."""
+    return _FusedGate.apply(logits, int(top_k), int(capacity), bool(normalize))
+
+
+class _FusedExperts(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, gates, w1, b1, w2, b2, meta):
+        lib = native.lib()
+        st, idx, loc, slot_map = meta['state'], meta['idx'], meta['loc'], meta['slot_map']
+        tr = st.tr
+        W, rank = tr.world, tr.rank
+        E, C, d, K = meta['E'], meta['C'], meta['degree'], meta['K']
+        E_l, Cc = E // W, C // d
+        S, M = x.shape
+        H, O = w1.size(2), w2.size(2)
+        R = W * Cc                                  # rows per expert per chunk
+        act = meta['act']
+        postscore = meta['postscore']
+        bs = st.acquire((E_l, W, C, M, O))
+        bases = bs.block.bases_ptr
+        budget, status = tr.budget_ms, tr.status_ptr
+        gates_f = gates.detach().contiguous()
+
+        # ---- dispatch: push my tokens into the experts' home ranks ---------------------------
+        ctas = _send_ctas(E_l * Cc, d * W)
+        lib.scatter_push(x, slot_map, None if postscore else gates_f, K, E, C, bases, bs.off_x,
+                         bs.flag_off(PH_DISPATCH), W, rank, d, ctas)
+        bs.arrived[PH_DISPATCH] += ctas
+        want_x = bs.arrived[PH_DISPATCH]
+
+        recv_x = bs.view(bs.off_x, (d, E_l, R, M))
+        pre = torch.empty((d, E_l, R, H), dtype=x.dtype, device=x.device)
+        h = torch.empty_like(pre)
+        push_arrivals = lib.gemm_push_arrivals(E_l, R, O, Cc, rank)
+        for j in range(d):
+            # GEMM 1: rows of source rank s are readable once flag[j][s] has arrived
+            grouped_gemm(recv_x[j], False, w1, True, EPI_BIAS_ACT, act, bias=b1, aux=pre[j], out=h[j],
+                         gate_flags_ptr=bs.flag_ptr(PH_DISPATCH, j), gate_rows=Cc, gate_want=want_x,
+                         budget_ms=budget, status_ptr=status)
+            # GEMM 2: epilogue pushes rows to the token owners' combine buffers
+            grouped_gemm(h[j], False, w2, True, EPI_PUSH, 0, bias=b2,
+                         heap_bases_ptr=bases, push_data_off=bs.off_y,
+                         push_flag_off=bs.flag_off(PH_COMBINE), push_rows=Cc, push_C=C, push_c0=j * Cc,
+                         push_chunk=j, W=W, my_rank=rank, budget_ms=budget, status_ptr=status)
+        bs.arrived[PH_COMBINE] += push_arrivals
+        want_y = bs.arrived[PH_COMBINE]
+
+        # ---- combine: wait for every (chunk, expert rank) flag, gate-weighted sum over k ---------
+        # flags of chunks 0..d-1 are consecutive: [d][W]
+        out = lib.gather_wait(bs.block.local_ptr + (bs.off_y - bs.block.offset), x.dtype, O, idx, loc,
+                              gates_f if postscore else None, C, bs.flag_ptr(PH_COMBINE, 0), d * W, want_y,
+                              budget, status)
+
+        ctx.meta, ctx.bs = meta, bs
+        ctx.save_for_backward(x, gates_f, w1, w2, pre, h)
+        ctx.dims = (W, rank, E, C, d, K, E_l, Cc, S, M, H, O, R)
+        ctx.lease = _Lease(bs)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        lib = native.lib()
+        meta, bs = ctx.meta, ctx.bs
+        x, gates_f, w1, w2, pre, h = ctx.saved_tensors
+        W, rank, E, C, d, K, E_l, Cc, S, M, H, O, R = ctx.dims
+        st, idx, loc, slot_map = meta['state'], meta['idx'], meta['loc'], meta['slot_map']
+        tr = st.tr
+        act, postscore = meta['act'], meta['postscore']
+        bases = bs.block.bases_ptr
+        budget, status = tr.budget_ms, tr.status_ptr
+        dout = dout.contiguous()
+
+        recv_y = bs.view(bs.off_y, (E * C, O))
+        dgates = None
+        if postscore and ctx.needs_input_grad[1]:
+            dgates = lib.dispatch_gate_grad(recv_y, dout, idx, loc, C)
+
+        # ---- combine backward: push dY (gate-weighted) to the experts' home ranks ------------
+        ctas = _send_ctas(E_l * Cc, d * W)
+        lib.scatter_push(dout, slot_map, gates_f if postscore else None, K, E, C, bases, bs.off_dy,
+                         bs.flag_off(PH_COMBINE_BWD), W, rank, d, ctas)
+        bs.arrived[PH_COMBINE_BWD] += ctas
+        want_dy = bs.arrived[PH_COMBINE_BWD]
+
+        recv_dy = bs.view(bs.off_dy, (d, E_l, R, O))
+        recv_x = bs.view(bs.off_x, (d, E_l, R, M))
+        dh = torch.empty_like(pre)
+        push_arrivals = lib.gemm_push_arrivals(E_l, R, M, Cc, rank)
+        for j in range(d):
+            grouped_gemm(recv_dy[j], False, w2, False, EPI_DACT, act, aux=pre[j], out=dh[j],
+                         gate_flags_ptr=bs.flag_ptr(PH_COMBINE_BWD, j), gate_rows=Cc, gate_want=want_dy,
+                         budget_ms=budget, status_ptr=status)
+            grouped_gemm(dh[j], False, w1, False, EPI_PUSH, 0,
+                         heap_bases_ptr=bases, push_data_off=bs.off_dx,
+                         push_flag_off=bs.flag_off(PH_DISPATCH_BWD), push_rows=Cc, push_C=C, push_c0=j * Cc,
+                         push_chunk=j, W=W, my_rank=rank, budget_ms=budget, status_ptr=status)
+        bs.arrived[PH_DISPATCH_BWD] += push_arrivals
+        want_dx = bs.arrived[PH_DISPATCH_BWD]
+
+        # ---- weight / bias gradients: contract over all chunks in one launch each ---------------
+        dw2 = grouped_gemm(h, True, recv_dy, True, EPI_STORE)
+        dw1 = grouped_gemm(recv_x, True, dh, True, EPI_STORE)
+        db2 = lib.colsum(recv_dy.view(d * E_l, R, O)).view(d, E_l, O).sum(0).to(w2.dtype)
+        db1 = lib.colsum(dh.view(d * E_l, R, H)).view(d, E_l, H).sum(0).to(w1.dtype)
+
+        # ---- dispatch backward: wait for the returned slots, gather (gate-weighted if pre-score)
+        dx = lib.gather_wait(bs.block.local_ptr + (bs.off_dx - bs.block.offset), dout.dtype, M, idx, loc,
+                             None if postscore else gates_f, C, bs.flag_ptr(PH_DISPATCH_BWD, 0), d * W,
+                             want_dx, budget, status)
+        if not postscore and ctx.needs_input_grad[1]:
+            recv_dx = bs.view(bs.off_dx, (E * C, M))
+            dgates = lib.dispatch_gate_grad(recv_dx, x, idx, loc, C)
+        return dx, dgates, dw1, db1, dw2, db2, None
+
+
+def forward(layer, x, gctx, top_k, capacity_factor, degree):
+    """Run the fused path for ``layer`` on tokens ``x [S, M]``; returns ``(y [S, O], l_aux)``."""
+    if layer._fused is None:
+        layer._fused = FusedState(layer)
+    st = layer._fused
+    S, M = x.shape
+    E = layer.num_global_experts
+    top_k = min(int(top_k), E)
+
+    with torch.autocast('cuda', enabled=False):
+        logits = gctx(x)
+        if layer.training and gctx.gate_noise > 0:
+            logits = logits + gctx.gate_noise * torch.randn_like(logits) / E
+    capacity = top_k * int(capacity_factor * ((S + E - 1) // E))
+    align = 4 * layer.sharded_count * degree
+    if capacity % align:
+        capacity += align - capacity % align
+
+    gates, l_aux, idx, loc, slot_map = fused_gate(logits, top_k, capacity, layer.normalize_gate)
+    ex = layer.experts
+    meta = dict(state=st, idx=idx, loc=loc, slot_map=slot_map, E=E, C=capacity, degree=degree, K=top_k,
+                act=ACT_CODES[ex.act_name], postscore=layer.is_postscore)
+    y = _FusedExperts.apply(x.contiguous(), gates, ex.batched_fc1_w, ex.batched_fc1_bias,
+                            ex.batched_fc2_w, ex.batched_fc2_bias, meta)
+    layer.last_stats = dict(capacity=capacity, degree=degree, path='fused')
+    return y, l_aux.to(logits.dtype)
