@@ -2,7 +2,7 @@
 //
 //   D[g] (M x N) = A[g] (M x K) . B[g] (K x N)          g = 0 .. groups-1, fp32 accumulate
 //
-// Hand-written tcgen05 pipeline, one persistent CTA per SM, 192 threads in three roles:
+// Hand-written tcgen05 pipeline, one persistent CTA per SM, 320 threads in three roles:
 //   warp 0      TMA producer: cp.async.bulk.tensor (4-D maps, 128-byte swizzle) into a 4-stage
 //               shared-memory ring, completion on mbarriers.  When the A operand is a receive
 //               buffer that peer GPUs fill, the producer first acquire-waits (bounded) on the
@@ -12,7 +12,7 @@
 //               per instruction, accumulating in TMEM (2 x 256 columns, double buffered so the
 //               epilogue of tile i overlaps the main loop of tile i+1); tcgen05.commit releases
 //               ring stages and publishes the accumulator.
-//   warps 2..5  epilogue: tcgen05.ld 32x32b -> registers -> bias / activation / activation
+//   warps 2..9  epilogue: tcgen05.ld 32x32b -> registers -> bias / activation / activation
 //               backward -> bf16 -> swizzled shared-memory staging -> full-line 16-byte stores,
 //               either to local memory or straight into the combine buffer of the rank that
 //               owns the token ("push"), followed by a release-add on that rank's flag.
@@ -46,12 +46,12 @@ constexpr int BM = 128, BN = 256, BK = 64;
 constexpr int UMMA_K = 16;
 constexpr int kStages = 4;
 constexpr int kAccStages = 2;
-constexpr int kThreads = 192;
-constexpr int kEpiWarps = 4;
+constexpr int kThreads = 320;
+constexpr int kEpiWarps = 8;
 constexpr uint32_t kABytes = BM * BK * 2;          // 16 KiB
 constexpr uint32_t kBBytes = BN * BK * 2;          // 32 KiB
 constexpr uint32_t kStageBytes = kABytes + kBBytes;
-constexpr uint32_t kStagingPerWarp = 2 * 32 * 128; // two 32-row x 128-byte tiles
+constexpr uint32_t kStagingPerWarp = 32 * 128;     // one 32-row x 128-byte tile
 constexpr uint32_t kSmemRing = kStages * kStageBytes;
 constexpr uint32_t kSmemStaging = kEpiWarps * kStagingPerWarp;
 constexpr uint32_t kSmemBias = BN * 4;
@@ -137,7 +137,7 @@ __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void epi_bar_sync() {
-  asm volatile("bar.sync 1, 128;" ::: "memory");
+  asm volatile("bar.sync 1, 256;" ::: "memory");
 }
 
 // Shared-memory matrix descriptor, 128-byte swizzle, Blackwell descriptor version 1.
@@ -203,11 +203,30 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, Ctl* ct
   return true;
 }
 
+// Gaussian CDF and PDF at x with one exp and one reciprocal: erf by the Abramowitz-Stegun 7.1.26
+// rational approximation (|error| < 1.5e-7, far below bf16 resolution); exp(-x^2/2) serves both.
+__device__ __forceinline__ void gauss_cdf_pdf(float x, float& cdf, float& pdf) {
+  const float z = fabsf(x) * 0.70710678118654752f;
+  const float e = __expf(-z * z);
+  const float t = __frcp_rn(fmaf(0.3275911f, z, 1.f));
+  float poly = fmaf(t, 1.061405429f, -1.453152027f);
+  poly = fmaf(poly, t, 1.421413741f);
+  poly = fmaf(poly, t, -0.284496736f);
+  poly = fmaf(poly, t, 0.254829592f);
+  const float erf_abs = 1.f - poly * t * e;
+  cdf = 0.5f * (1.f + copysignf(erf_abs, x));
+  pdf = 0.3989422804014327f * e;
+}
+
 __device__ __forceinline__ float act_fwd(float x, int act) {
   switch (act) {
     case kActRelu: return fmaxf(x, 0.f);
-    case kActGelu: return 0.5f * x * (1.f + erff(x * 0.70710678118654752f));
-    case kActSilu: return x / (1.f + __expf(-x));
+    case kActGelu: {
+      float cdf, pdf;
+      gauss_cdf_pdf(x, cdf, pdf);
+      return x * cdf;
+    }
+    case kActSilu: return x * __frcp_rn(1.f + __expf(-x));
     default: return x;
   }
 }
@@ -215,13 +234,13 @@ __device__ __forceinline__ float act_bwd(float x, int act) {
   switch (act) {
     case kActRelu: return x > 0.f ? 1.f : 0.f;
     case kActGelu: {
-      const float cdf = 0.5f * (1.f + erff(x * 0.70710678118654752f));
-      const float pdf = 0.3989422804014327f * __expf(-0.5f * x * x);
-      return cdf + x * pdf;
+      float cdf, pdf;
+      gauss_cdf_pdf(x, cdf, pdf);
+      return fmaf(x, pdf, cdf);
     }
     case kActSilu: {
-      const float s = 1.f / (1.f + __expf(-x));
-      return s * (1.f + x * (1.f - s));
+      const float sg = __frcp_rn(1.f + __expf(-x));
+      return sg * (1.f + x * (1.f - sg));
     }
     default: return 1.f;
   }
@@ -232,7 +251,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const KernelParams p) {
@@ -348,12 +367,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------------ epilogue warps
+    // ------------------------------------------------------------------ epilogue warps (8)
+    // Warp pairs share a TMEM lane quarter (warp % 4); each warp of a pair drains one 128-column
+    // half of the accumulator, in two 64-column slabs.
+    const int ewarp = warp - 2;                   // 0..7
     const int q = warp & 3;                       // TMEM lane quarter this warp may read
-    const int ewarp = warp - 2;
+    const int half = ewarp >> 2;
     uint8_t* st0 = staging + ewarp * kStagingPerWarp;
-    uint8_t* st1 = st0 + 32 * 128;
-    const int etid = threadIdx.x - 64;            // 0..127
+    const int etid = threadIdx.x - 64;            // 0..255
     uint32_t acc = 0, acc_phase = 0, iter = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
@@ -362,15 +383,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const int g = tile / (nt_count * mt_count);
       const int m0 = mt * BM, n0 = nt * BN;
 
-      // All four epilogue warps take the same exit decision: a warp that timed out raises the
-      // flag of this iteration's parity before the barrier, everyone reads it after the barrier.
+      // All epilogue warps take the same exit decision: a warp that timed out raises the flag of
+      // this iteration's parity before the barrier, everyone reads it after the barrier.
       bool got = mbar_wait(smem_u32(&ctl->acc_full[acc]), acc_phase, ctl, p.budget_ns, p.status, 2, acc);
       got = __all_sync(0xffffffffu, got);
       if (!got && lane == 0) ctl->epi_abort[iter & 1] = 1;
       epi_bar_sync();                              // also: previous tile's readers of bias_s are done
       if (ctl->epi_abort[iter & 1]) { ok = false; break; }
       ++iter;
-      for (int i = etid; i < BN; i += 128) {
+      for (int i = etid; i < BN; i += kEpiWarps * 32) {
         float b = 0.f;
         if (p.bias != nullptr && n0 + i < p.N) b = __bfloat162float(p.bias[(long long)g * p.bias_group_stride + n0 + i]);
         bias_s[i] = b;
@@ -378,45 +399,45 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       epi_bar_sync();
       tc_fence_after();
 
-      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + half * 128;
+      const int my_m = m0 + q * 32 + lane;         // the accumulator row this thread holds
 
 #pragma unroll 1
-      for (int c64 = 0; c64 < BN / 64; ++c64) {
-        const int nb = n0 + c64 * 64;              // first global column of this 64-wide slab
+      for (int s2 = 0; s2 < 2; ++s2) {
+        const int c0 = half * 128 + s2 * 64;       // first accumulator column of this slab
+        const int nb = n0 + c0;                    // first global column
         if (nb >= p.N) break;
-        uint32_t v[64];
-        tmem_ld32(t_row + c64 * 64, v);
-        tmem_ld32(t_row + c64 * 64 + 32, v + 32);
-        tmem_ld_wait();
 
-        // optional input slab (pre-activation) for the activation backward
-        if (p.epilogue == kEpiDAct) {
+        // activation backward: fetch this thread's 64 pre-activations (one 128-byte line) early
+        uint4 pre[8];
+        if constexpr (EPI == kEpiDAct) {
+          const __nv_bfloat16* arow = p.aux + (long long)g * p.aux_group_stride + (long long)my_m * p.aux_row_stride + nb;
 #pragma unroll
-          for (int it = 0; it < 8; ++it) {
-            const int r = it * 4 + (lane >> 3), c = lane & 7;
-            const int m = m0 + q * 32 + r;
-            uint4 val = make_uint4(0, 0, 0, 0);
-            if (m < p.M && nb + c * 8 < p.N)
-              val = *reinterpret_cast<const uint4*>(p.aux + (long long)g * p.aux_group_stride + (long long)m * p.aux_row_stride + nb + c * 8);
-            *reinterpret_cast<uint4*>(st1 + r * 128 + ((c ^ (r & 7)) << 4)) = val;
+          for (int c = 0; c < 8; ++c) {
+            pre[c] = make_uint4(0, 0, 0, 0);
+            if (my_m < p.M && nb + c * 8 < p.N) pre[c] = __ldg(reinterpret_cast<const uint4*>(arow + c * 8));
           }
-          __syncwarp();
         }
+
+        uint32_t v[64];
+        tmem_ld32(t_row + s2 * 64, v);
+        tmem_ld32(t_row + s2 * 64 + 32, v + 32);
+        tmem_ld_wait();
 
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           float f[8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[c * 8 + i]) + bias_s[c64 * 64 + c * 8 + i];
-          uint4 outv, auxv;
-          if (p.epilogue == kEpiBiasAct) {
-            auxv = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+          for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[c * 8 + i]) + bias_s[c0 + c * 8 + i];
+          if constexpr (EPI == kEpiBiasAct) {
+            if (p.aux != nullptr && my_m < p.M && nb + c * 8 < p.N) {
+              const uint4 auxv = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+              *reinterpret_cast<uint4*>(p.aux + (long long)g * p.aux_group_stride + (long long)my_m * p.aux_row_stride + nb + c * 8) = auxv;
+            }
 #pragma unroll
             for (int i = 0; i < 8; ++i) f[i] = act_fwd(f[i], p.activation);
-            *reinterpret_cast<uint4*>(st1 + lane * 128 + ((c ^ (lane & 7)) << 4)) = auxv;
-          } else if (p.epilogue == kEpiDAct) {
-            const uint4 pre = *reinterpret_cast<const uint4*>(st1 + lane * 128 + ((c ^ (lane & 7)) << 4));
-            const __nv_bfloat162* ph = reinterpret_cast<const __nv_bfloat162*>(&pre);
+          } else if constexpr (EPI == kEpiDAct) {
+            const __nv_bfloat162* ph = reinterpret_cast<const __nv_bfloat162*>(&pre[c]);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               const float2 pf = __bfloat1622float2(ph[i]);
@@ -424,7 +445,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               f[2 * i + 1] *= act_bwd(pf.y, p.activation);
             }
           }
-          outv = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+          const uint4 outv = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
           *reinterpret_cast<uint4*>(st0 + lane * 128 + ((c ^ (lane & 7)) << 4)) = outv;
         }
         __syncwarp();
@@ -436,7 +457,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           const int m = m0 + q * 32 + r;
           if (m < p.M && nb + c * 8 < p.N) {
             const uint4 val = *reinterpret_cast<const uint4*>(st0 + r * 128 + ((c ^ (r & 7)) << 4));
-            if (p.epilogue == kEpiPush) {
+            if constexpr (EPI == kEpiPush) {
               const int s = m / p.push_rows, cc = m - s * p.push_rows;
               __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(
                   reinterpret_cast<uint8_t*>(p.heap_bases[s]) + p.push_data_off);
@@ -444,10 +465,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               *reinterpret_cast<uint4*>(base + drow * p.N + nb + c * 8) = val;
             } else {
               *reinterpret_cast<uint4*>(p.D + (long long)g * p.d_group_stride + (long long)m * p.d_row_stride + nb + c * 8) = val;
-              if (p.epilogue == kEpiBiasAct && p.aux != nullptr) {
-                const uint4 a = *reinterpret_cast<const uint4*>(st1 + r * 128 + ((c ^ (r & 7)) << 4));
-                *reinterpret_cast<uint4*>(p.aux + (long long)g * p.aux_group_stride + (long long)m * p.aux_row_stride + nb + c * 8) = a;
-              }
             }
           }
         }
@@ -460,7 +477,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       if (lane == 0) mbar_arrive(smem_u32(&ctl->acc_empty[acc]));
       if (++acc == kAccStages) { acc = 0; acc_phase ^= 1u; }
 
-      if (p.epilogue == kEpiPush) {
+      if constexpr (EPI == kEpiPush) {
         epi_bar_sync();                            // every row of the tile has been stored
         if (etid == 0) {
           __threadfence_system();
@@ -522,10 +539,10 @@ bool make_map(CUtensorMap* map, const GemmOperand& op, int groups, int box_rows)
   return r == CUDA_SUCCESS;
 }
 
-template <bool A_MN, bool B_MN>
-cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const KernelParams& kp, int ctas,
-                           cudaStream_t stream) {
-  auto kern = grouped_gemm_kernel<A_MN, B_MN>;
+template <bool A_MN, bool B_MN, int EPI>
+cudaError_t launch_epi(const CUtensorMap& ta, const CUtensorMap& tb, const KernelParams& kp, int ctas,
+                       cudaStream_t stream) {
+  auto kern = grouped_gemm_kernel<A_MN, B_MN, EPI>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTotal);
@@ -534,6 +551,18 @@ cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const K
   }
   kern<<<ctas, kThreads, kSmemTotal, stream>>>(ta, tb, kp);
   return cudaGetLastError();
+}
+
+template <bool A_MN, bool B_MN>
+cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const KernelParams& kp, int ctas,
+                           cudaStream_t stream) {
+  switch (kp.epilogue) {
+    case kEpiStore: return launch_epi<A_MN, B_MN, kEpiStore>(ta, tb, kp, ctas, stream);
+    case kEpiBiasAct: return launch_epi<A_MN, B_MN, kEpiBiasAct>(ta, tb, kp, ctas, stream);
+    case kEpiDAct: return launch_epi<A_MN, B_MN, kEpiDAct>(ta, tb, kp, ctas, stream);
+    case kEpiPush: return launch_epi<A_MN, B_MN, kEpiPush>(ta, tb, kp, ctas, stream);
+    default: return cudaErrorInvalidValue;
+  }
 }
 
 }  // namespace
