@@ -371,6 +371,28 @@ Tensor gather_wait_op(int64_t disp_ptr, at::ScalarType dtype, int64_t M, const T
   return out;
 }
 
+// ---- stand-alone transfers --------------------------------------------------------------------
+void xfer_op(int64_t src_ptr, const Tensor& msgs, int64_t ctas_per_msg, int64_t heap_bases_ptr, int64_t flag_off,
+             int64_t wait_flags_ptr, const c10::optional<Tensor>& wait_idx, int64_t want, int64_t budget_ms,
+             int64_t status_ptr, int64_t local_dst_ptr) {
+  count_launch(1);
+  TORCH_CHECK(msgs.is_cuda() && msgs.scalar_type() == at::kLong && msgs.is_contiguous() && msgs.dim() == 2 &&
+              msgs.size(1) == 5, "msgs must be a contiguous CUDA int64 [n, 5] tensor");
+  c10::cuda::CUDAGuard guard(msgs.device());
+  const int n_wait = (wait_idx.has_value() && wait_idx->defined()) ? wait_idx->numel() : 0;
+  launch_xfer(reinterpret_cast<const void*>(src_ptr), reinterpret_cast<const long long*>(msgs.data_ptr<int64_t>()),
+              msgs.size(0), ctas_per_msg, reinterpret_cast<const unsigned long long*>(heap_bases_ptr), flag_off,
+              reinterpret_cast<const unsigned long long*>(wait_flags_ptr), n_wait ? wait_idx->data_ptr<int>() : nullptr,
+              n_wait, want, (unsigned long long)budget_ms * 1000000ull, reinterpret_cast<int*>(status_ptr),
+              reinterpret_cast<void*>(local_dst_ptr), cur_stream());
+}
+
+void wait_flags_op(int64_t flags_ptr, int64_t n, int64_t want, int64_t budget_ms, int64_t status_ptr) {
+  count_launch(1);
+  launch_wait_flags(reinterpret_cast<const unsigned long long*>(flags_ptr), n, want,
+                    (unsigned long long)budget_ms * 1000000ull, reinterpret_cast<int*>(status_ptr), cur_stream());
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -390,6 +412,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("colsum", &colsum_op);
   m.def("scatter_push", &scatter_push_op);
   m.def("gather_wait", &gather_wait_op);
+  m.def("xfer", &xfer_op);
+  m.def("wait_flags", &wait_flags_op);
   m.def("gemm_push_arrivals", &gemm_push_arrivals);
   m.def("launch_count", [] { return (long long)g_launches.load(); });
 

@@ -74,6 +74,15 @@ template <class T>
 void launch_int8_decode(const unsigned char* q, const float* scale, const float* bias, T* out, int R,
                         int M, cudaStream_t stream);
 
+// ---- kernels/a2a.cu --------------------------------------------------------------------------
+// msgs: device int64 [n_msgs][5] = (dest rank or -1, flag index or -1, src_off, dst_off, bytes).
+void launch_xfer(const void* src_base, const long long* msgs, int n_msgs, int ctas_per_msg,
+                 const unsigned long long* heap_bases, unsigned long long flag_off,
+                 const unsigned long long* wait_flags, const int* wait_idx, int n_wait, unsigned long long want,
+                 unsigned long long budget_ns, int* status, void* local_dst, cudaStream_t stream);
+void launch_wait_flags(const unsigned long long* flags, int n, unsigned long long want, unsigned long long budget_ns,
+                       int* status, cudaStream_t stream);
+
 // ---- kernels/gemm_tcgen05.cu -----------------------------------------------------------------
 // Grouped bf16 GEMM  D[g] (Mg x N) = A[g] (Mg x K) . B[g] (K x N), fp32 accumulation in TMEM.
 enum GemmEpilogue : int {

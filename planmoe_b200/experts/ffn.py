@@ -122,6 +122,20 @@ class FusedExpertsNetwork(torch.nn.Module):
             from ..ops import gemm
             return gemm.expert_ffn(x, w1, b1, w2, b2, self.act_name)
 
+        zero_group = getattr(ctx, 'ffn_zero_group', None) if ctx is not None else None
+        if zero_group is not None and not ctx.use_model_parallel:
+            # 'data' sharding: this rank holds a slice of an expert's slots; rebuild the full expert
+            # from the shards of its group (gradients flow back through a reduce-scatter).
+            from ..impls.communicate import PrimAllgather
+
+            def gather(t, dim):
+                t = t.transpose(0, dim).contiguous()
+                return PrimAllgather.apply(t, True, zero_group).transpose(0, dim)
+            w1, b1, w2 = gather(w1, 2), gather(b1, 1), gather(w2, 1)
+            b2 = gather(b2, 1)[:, :w2.size(2)]
+            y = torch.matmul(self.activation_fn(torch.matmul(x, w1) + b1.unsqueeze(1)), w2)
+            return y + b2.unsqueeze(1)
+
         y = torch.matmul(x, w1) + b1.unsqueeze(1)
         y = self.activation_fn(y)
         y = torch.matmul(y, w2)
