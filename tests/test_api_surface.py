@@ -1,0 +1,185 @@
+"""Public API surface: package aliases, facades, launcher command construction, scheduler, the
+reference-named native functions, codecs and comm registries on CPU."""
+
+import json
+import os
+import sys
+
+import pytest
+import torch
+
+
+def test_alias_packages_expose_the_same_modules():
+    import planmoe
+    import schemoe
+    import planmoe_b200
+    from schemoe.moe import moe_layer as a
+    from planmoe.moe import moe_layer as b
+    assert a is b is planmoe_b200.moe.moe_layer
+    import planmoe.impls.communicate as c1
+    import planmoe_b200.impls.communicate as c2
+    assert c1 is c2
+    from planmoe import net, system, jit, moe
+    for name in ('get_world_size', 'get_world_rank', 'create_groups_from_world', 'barrier', 'simple_all_reduce',
+                 'simple_all_to_all', 'simple_split', 'simple_reduce_scatter', 'simple_all_gather', 'all_to_all',
+                 'all_to_all_single', 'all_gather', 'zero_gather', 'zero_scatter', 'spatial_split',
+                 'reduce_scatter', 'allreduce_forward', 'allreduce_backward', 'TutelDistributedOptimizer'):
+        assert hasattr(net, name), name
+    for name in ('init_affinity_at_program_beginning', 'init_data_model_parallel', 'cache', 'LocalCache',
+                 'get_local_session', 'record_time', 'TUTEL_CUDA_SANDBOX'):
+        assert hasattr(system, name), name
+    for name in ('moe_layer', 'top_k_routing', 'extract_critical', 'fast_encode', 'fast_decode', 'fast_dispatcher',
+                 'fast_cumsum_sub_one'):
+        assert hasattr(moe, name), name
+    assert callable(jit.create_cuda_kernel)
+    from planmoe.gates.top import Gate  # noqa: F401
+    from planmoe.gates.cosine_top import Gate as G2  # noqa: F401
+    from planmoe.experts.ffn import ExpertModule  # noqa: F401
+    from planmoe.impls.overlap import a2a_ffn_overlap_forward  # noqa: F401
+    import schemoe_custom_kernel as k
+    for name in ('compress_operation', 'comm_operation', 'decompress_operation', 'clear_ptr_lst', 'init_nccl',
+                 'get_nccl_unique_id', 'get_nccl_unique_id_size', 'invoke', 'inject_source', 'invoke_cpu_fp32',
+                 'invoke_cpu_fp64', 'update_sdk_home', 'current_stream_acquire', 'nccl_stream_release'):
+        assert hasattr(k, name), name
+
+
+def test_system_cache_and_timer():
+    from planmoe_b200 import system
+    system.cache().reset()
+    system.cache().set('a', 1)
+    system.cache().set('b', 2)
+    assert system.cache().get('a') == 1 and sorted(system.cache().get()) == [1, 2]
+    assert system.record_time(is_cuda=False) > 0
+    with pytest.raises(Exception):
+        system.LocalCache.reset()
+        del system.init_data_model_parallel.__dict__['default_env']
+        system.get_local_session()
+    system.init_affinity_at_program_beginning()
+
+
+def test_fifo_pipeline_single_rank_roundtrip():
+    import schemoe_custom_kernel as k
+    x = torch.relu(torch.randn(4, 8, 32))
+    k.clear_ptr_lst()
+    parts = []
+    for c in x.split(4, dim=1):
+        t = k.compress_operation(c.contiguous(), 'int8', 'naive')
+        parts.append(k.comm_operation(t))
+    outs = [k.decompress_operation(p) for p in parts]
+    y = torch.cat(outs, dim=1)
+    assert (y - x).abs().max() <= (x.max() - x.min()) / 255 * 0.51 + 1e-6
+    k.clear_ptr_lst()
+    assert torch.equal(k.decompress_operation(k.comm_operation(k.compress_operation(x, 'nonsense', 'nonsense'))), x)
+
+
+def test_cpu_sparse_invoke_matches_torch():
+    import schemoe_custom_kernel as k
+    S, M, E, C = 10, 6, 3, 4
+    x = torch.randn(S, M)
+    idx = torch.randint(0, E, (S,), dtype=torch.int32)
+    loc = torch.zeros(S, dtype=torch.int32)
+    cnt = [0] * E
+    for t in range(S):
+        loc[t] = cnt[int(idx[t])]; cnt[int(idx[t])] += 1
+    g = torch.rand(S)
+    disp = torch.zeros(E * C, M)
+    k.invoke_cpu_fp32([g, idx, loc, x, disp], [S, M, C], 0)
+    ref = torch.zeros(E * C, M)
+    for t in range(S):
+        if loc[t] < C:
+            ref[int(idx[t]) * C + int(loc[t])] += g[t] * x[t]
+    assert torch.allclose(disp, ref, atol=1e-6)
+    back = torch.empty(S, M)
+    k.invoke_cpu_fp32([g, idx, loc, back, disp], [S, M, C], 1)
+    gg = torch.empty(S)
+    k.invoke_cpu_fp32([gg, idx, loc, x, disp], [S, M, C], 2)
+    for t in range(S):
+        if loc[t] < C:
+            row = disp[int(idx[t]) * C + int(loc[t])]
+            assert torch.allclose(back[t], g[t] * row, atol=1e-6)
+            assert abs(float(gg[t]) - float((row * x[t]).sum())) < 1e-4
+        else:
+            assert float(back[t].abs().sum()) == 0 and float(gg[t]) == 0
+
+
+def test_launcher_commands():
+    from planmoe_b200.launcher import run, execl
+    cmd, env = run.build_command(['-m', 'planmoe_b200.examples.pre_test', '--encode', 'int8'],
+                                 {'OMPI_COMM_WORLD_SIZE': '2', 'OMPI_COMM_WORLD_RANK': '1', 'LOCAL_SIZE': '4',
+                                  'MASTER_ADDR': 'hostA'})
+    assert '--nproc_per_node=4' in cmd and '--nnodes=2' in cmd and '--node_rank=1' in cmd
+    assert '--master_addr=hostA' in cmd and cmd[-3:] == ['planmoe_b200.examples.pre_test', '--encode', 'int8']
+    assert 'planmoe_b200.launcher.execl' in cmd and env['LOCAL_SIZE'] == '4'
+    cmd, env = execl.build_command(['python', 'x.py'], {'LOCAL_RANK': '3', 'TUTEL_CUDA_SANDBOX': '2', 'LOCAL_SIZE': '8'})
+    assert env['CUDA_VISIBLE_DEVICES'] == '3' and cmd[-2:] == ['python', 'x.py']
+
+
+def test_adaptive_scheduler_picks_fastest_and_caches(tmp_path, monkeypatch):
+    from planmoe_b200.parallel import scheduler
+    monkeypatch.setenv('PLANMOE_PLAN_CACHE', str(tmp_path / 'plans.json'))
+    sch = scheduler.AdaptiveScheduler('k1', candidates=(1, 2, 4), warmup=1, samples=2)
+    cost = {1: 3.0, 2: 1.0, 4: 2.0}
+    import time
+    x = torch.zeros(1)
+    seen = []
+    fake = [0.0]
+    monkeypatch.setattr(time, 'perf_counter', lambda: fake[0])
+    while sch.frozen is None:
+        d = sch.next_degree()
+        if sch.frozen is not None:
+            break
+        seen.append(d)
+        sch.begin_step(x)
+        fake[0] += cost[d] * 1e-3
+        sch.end_step(x)
+    assert sch.frozen == 2 and set(seen) == {1, 2, 4}
+    assert json.load(open(tmp_path / 'plans.json'))['k1']['degree'] == 2
+    again = scheduler.AdaptiveScheduler('k1', candidates=(1, 2, 4))
+    assert again.next_degree() == 2 and again.report['source'] == 'cache'
+
+
+def test_layer_with_auto_degree_runs_on_cpu(tmp_path, monkeypatch):
+    from planmoe_b200 import moe
+    monkeypatch.setenv('PLANMOE_PLAN_CACHE', str(tmp_path / 'plans.json'))
+    layer = moe.moe_layer({'type': 'top', 'k': 2}, 32, experts={'type': 'ffn', 'count_per_node': 2,
+                                                            'hidden_size_per_expert': 32},
+                          a2a_ffn_overlap_degree='auto')
+    x = torch.randn(64, 32)
+    ys = [layer(x) for _ in range(30)]
+    assert layer._scheduler.frozen in (1, 2, 4, 8)
+    assert torch.allclose(ys[0], ys[-1], atol=1e-5)
+
+
+def test_comm_and_codec_registries():
+    from planmoe_b200.parallel import codecs, comms
+    assert isinstance(codecs.get_compressor('bogus'), codecs.NoCompressor)
+    assert isinstance(comms.get_comm('bogus'), comms.NaiveComm)
+    for name in ('naive', 'pipe', 'dd', 'hetu', 'nccl'):
+        c = comms.get_comm(name)
+        t = torch.arange(6.)
+        assert torch.equal(c.all_to_all(t), t)           # a world of one rank is the identity
+
+    class Half(codecs.AbstractCompressor):
+        name = 'half'
+
+        def compress(self, t, world_size=1):
+            return codecs.Packed([t.half()], t.dtype)
+
+        def decompress(self, packed):
+            return packed.wires[0].to(packed.meta)
+    codecs.register_compressor('half', Half)
+    from planmoe_b200.impls.overlap import ChunkHandle
+    x = torch.randn(4, 4)
+    assert torch.allclose(ChunkHandle('half', 'naive', None).launch(x).finish(), x, atol=1e-2)
+
+
+def test_pre_test_example_runs_on_cpu(tmp_path):
+    from planmoe_b200.examples import pre_test
+    mean, err = pre_test.main(['--device', 'cpu', '--dtype', 'float32', '--batch_size', '2', '--num_tokens', '16',
+                               '--model_dim', '32', '--hidden_size', '32', '--num_steps', '3',
+                               '--a2a_ffn_overlap_degree', '2', '--log', str(tmp_path / 't.log')])
+    assert err == 0.0 and mean > 0
+    mean, _ = pre_test.main(['--device', 'cpu', '--dtype', 'float32', '--batch_size', '2', '--num_tokens', '16',
+                             '--model_dim', '32', '--hidden_size', '32', '--num_steps', '2', '--layer',
+                             '--log', str(tmp_path / 't.log')])
+    assert mean > 0
