@@ -15,6 +15,7 @@
 #include "planmoe.h"
 #include "runtime/symm_heap.h"
 #include "runtime/jit.h"
+#include "codec/codecs.h"
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -371,6 +372,80 @@ Tensor gather_wait_op(int64_t disp_ptr, at::ScalarType dtype, int64_t M, const T
   return out;
 }
 
+// ---- ZFP / LZ codecs (CPU or CUDA by the tensor's device) ------------------------------------------
+int elem_code(at::ScalarType t) {
+  if (t == at::kFloat) return 0;
+  if (t == at::kBFloat16) return 1;
+  if (t == at::kHalf) return 2;
+  TORCH_CHECK(false, "zfp codec: unsupported dtype ", t);
+}
+
+Tensor zfp_encode_op(const Tensor& x, int64_t rate) {
+  TORCH_CHECK(x.dim() == 3 && x.is_contiguous(), "zfp_encode expects a contiguous [lead, rows, M] tensor");
+  TORCH_CHECK(rate == 4 || rate == 8 || rate == 16, "zfp rate must be 4, 8 or 16 bits per value");
+  TORCH_CHECK(x.size(2) % 4 == 0, "zfp codec needs the last dim to be a multiple of 4");
+  const int64_t lead = x.size(0), rows = x.size(1), M = x.size(2);
+  const int64_t bytes = (int64_t)zfp_stream_bytes(rows, M, rate);
+  Tensor out = torch::empty({lead, bytes}, x.options().dtype(at::kByte));
+  if (x.is_cuda()) {
+    count_launch(1);
+    c10::cuda::CUDAGuard guard(x.device());
+    launch_zfp_encode(x.data_ptr(), elem_code(x.scalar_type()), out.data_ptr<uint8_t>(), lead, rows, M, rate, cur_stream());
+  } else {
+    zfp_encode_cpu(x.data_ptr(), elem_code(x.scalar_type()), out.data_ptr<uint8_t>(), lead, rows, M, rate);
+  }
+  return out;
+}
+
+Tensor zfp_decode_op(const Tensor& stream, int64_t lead, int64_t rows, int64_t M, int64_t rate, at::ScalarType dtype) {
+  TORCH_CHECK(stream.is_contiguous() && stream.scalar_type() == at::kByte);
+  TORCH_CHECK(stream.numel() == lead * (int64_t)zfp_stream_bytes(rows, M, rate), "zfp stream size mismatch");
+  Tensor out = torch::empty({lead, rows, M}, stream.options().dtype(dtype));
+  if (stream.is_cuda()) {
+    count_launch(1);
+    c10::cuda::CUDAGuard guard(stream.device());
+    launch_zfp_decode(stream.data_ptr<uint8_t>(), out.data_ptr(), elem_code(dtype), lead, rows, M, rate, cur_stream());
+  } else {
+    zfp_decode_cpu(stream.data_ptr<uint8_t>(), out.data_ptr(), elem_code(dtype), lead, rows, M, rate);
+  }
+  return out;
+}
+
+std::vector<Tensor> lz_encode_op(const Tensor& raw, int64_t sym) {
+  TORCH_CHECK(raw.dim() == 2 && raw.is_contiguous() && raw.scalar_type() == at::kByte);
+  TORCH_CHECK((sym == 2 || sym == 4) && raw.size(1) % sym == 0 && raw.size(1) % 16 == 0,
+              "lz codec: slice bytes must be a multiple of 16 and of the symbol size");
+  const int64_t slices = raw.size(0), raw_bytes = raw.size(1);
+  const int64_t cap = (int64_t)lz_payload_capacity(raw_bytes);
+  Tensor payload = torch::empty({slices, cap}, raw.options());
+  Tensor sizes = torch::empty({slices}, raw.options().dtype(at::kInt));
+  if (raw.is_cuda()) {
+    count_launch(3);
+    c10::cuda::CUDAGuard guard(raw.device());
+    Tensor scratch = torch::empty({(int64_t)lz_scratch_bytes(slices, raw_bytes)}, raw.options());
+    launch_lz_encode(raw.data_ptr<uint8_t>(), payload.data_ptr<uint8_t>(), sizes.data_ptr<int>(),
+                     scratch.data_ptr<uint8_t>(), slices, raw_bytes, cap, sym, cur_stream());
+  } else {
+    lz_encode_cpu(raw.data_ptr<uint8_t>(), payload.data_ptr<uint8_t>(), sizes.data_ptr<int>(), slices, raw_bytes, cap, sym);
+  }
+  return {payload, sizes};
+}
+
+Tensor lz_decode_op(const Tensor& payload, const Tensor& sizes, int64_t raw_bytes, int64_t sym) {
+  TORCH_CHECK(payload.dim() == 2 && payload.is_contiguous() && payload.scalar_type() == at::kByte);
+  const int64_t slices = payload.size(0);
+  Tensor raw = torch::empty({slices, raw_bytes}, payload.options());
+  if (payload.is_cuda()) {
+    count_launch(1);
+    c10::cuda::CUDAGuard guard(payload.device());
+    launch_lz_decode(payload.data_ptr<uint8_t>(), raw.data_ptr<uint8_t>(), slices, raw_bytes, payload.size(1), sym,
+                     cur_stream());
+  } else {
+    lz_decode_cpu(payload.data_ptr<uint8_t>(), raw.data_ptr<uint8_t>(), slices, raw_bytes, payload.size(1), sym);
+  }
+  return raw;
+}
+
 // ---- stand-alone transfers --------------------------------------------------------------------
 void xfer_op(int64_t src_ptr, const Tensor& msgs, int64_t ctas_per_msg, int64_t heap_bases_ptr, int64_t flag_off,
              int64_t wait_flags_ptr, const c10::optional<Tensor>& wait_idx, int64_t want, int64_t budget_ms,
@@ -412,6 +487,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("colsum", &colsum_op);
   m.def("scatter_push", &scatter_push_op);
   m.def("gather_wait", &gather_wait_op);
+  m.def("zfp_encode", &zfp_encode_op);
+  m.def("zfp_decode", &zfp_decode_op);
+  m.def("lz_encode", &lz_encode_op);
+  m.def("lz_decode", &lz_decode_op);
   m.def("xfer", &xfer_op);
   m.def("wait_flags", &wait_flags_op);
   m.def("gemm_push_arrivals", &gemm_push_arrivals);

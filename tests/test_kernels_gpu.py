@@ -212,3 +212,90 @@ def test_cumsum_sub_one():
     from planmoe_b200.jit_kernels.gating import fast_cumsum_sub_one
     m = (torch.rand(1337, 24, device='cuda') > 0.7).int()
     assert torch.equal(fast_cumsum_sub_one(m), torch.cumsum(m, 0).int() - 1)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_zfp_cuda_stream_is_bit_identical_to_cpu_oracle(dtype):
+    torch.manual_seed(0)
+    x = F.relu(torch.randn(4, 130, 256)).to(dtype)
+    for rate in (4, 8, 16):
+        s_cpu = _lib().zfp_encode(x, rate)
+        s_gpu = _lib().zfp_encode(x.cuda(), rate)
+        assert torch.equal(s_gpu.cpu(), s_cpu)
+        y_cpu = _lib().zfp_decode(s_cpu, 4, 130, 256, rate, dtype)
+        y_gpu = _lib().zfp_decode(s_gpu, 4, 130, 256, rate, dtype)
+        assert torch.equal(y_gpu.cpu(), y_cpu)
+
+
+@pytest.mark.parametrize("sym", [2, 4])
+def test_lz_cuda_matches_cpu_oracle_and_roundtrips(sym):
+    torch.manual_seed(0)
+    x = F.relu(torch.randn(4, 8192)).to(torch.bfloat16 if sym == 2 else torch.float32)
+    raw = x.view(torch.uint8).reshape(4, -1).contiguous()
+    p_cpu, n_cpu = _lib().lz_encode(raw, sym)
+    p_gpu, n_gpu = _lib().lz_encode(raw.cuda(), sym)
+    assert torch.equal(n_gpu.cpu(), n_cpu)
+    for s in range(4):
+        n = int(n_cpu[s])
+        assert torch.equal(p_gpu[s, :n].cpu(), p_cpu[s, :n])
+    back = _lib().lz_decode(p_gpu, n_gpu, raw.size(1), sym)
+    assert torch.equal(back.cpu(), raw)
+    assert int(n_cpu.max()) < raw.size(1)
+
+
+def test_codec_objects_on_cuda():
+    from planmoe_b200.parallel import codecs
+    x = F.relu(torch.randn(4, 64, 256, device='cuda')).to(torch.bfloat16)
+    for name, tol in (('no', 0.0), ('lz', 0.0), ('int8', 0.02), ('zfp', 0.08)):
+        c = codecs.get_compressor(name)
+        y = c.decompress(c.compress(x, world_size=4))
+        err = ((y.float() - x.float()).abs().max() / x.float().abs().max()).item()
+        assert err <= tol, (name, err)
+
+
+def test_bounded_flag_wait_reports_timeout_instead_of_hanging():
+    """A wait on a flag that nothing sets gives up after its budget and records a status code."""
+    lib = _lib()
+    st = lib.StatusWord()
+    flags = torch.zeros(4, dtype=torch.int64, device='cuda')
+    lib.wait_flags(flags.data_ptr(), 4, 1, 50, st.device_ptr())          # 50 ms budget
+    torch.cuda.synchronize()
+    code = st.read()
+    assert code[0] == 1 and code[2] == 1 and code[3] == 0
+    st.clear()
+    flags.fill_(5)
+    lib.wait_flags(flags.data_ptr(), 4, 1, 50, st.device_ptr())
+    torch.cuda.synchronize()
+    assert st.read()[0] == 0
+
+
+def test_gemm_flag_gate_times_out_cleanly_and_context_survives():
+    """Flag-gated GEMM whose flags never arrive: the kernel aborts through the status word, frees its
+    TMEM and returns; a normal GEMM afterwards still works."""
+    from planmoe_b200.ops import gemm
+    lib = _lib()
+    st = lib.StatusWord()
+    flags = torch.zeros(8, dtype=torch.int64, device='cuda')
+    A, B = _rand(1, 256, 128), _rand(1, 128, 256)
+    gemm.grouped_gemm(A, False, B, True, gate_flags_ptr=flags.data_ptr(), gate_rows=128, gate_want=1,
+                      budget_ms=100, status_ptr=st.device_ptr())
+    torch.cuda.synchronize()
+    assert st.read()[0] in (1, 2)
+    out = gemm.grouped_gemm(A, False, B, True)
+    gemm.check_status()
+    _check(out, _ref_gemm(A, False, B, True))
+
+
+def test_user_jit_kernel_runs_on_current_stream():
+    from planmoe_b200 import jit
+    fn = jit.create_cuda_kernel('''
+      __global__ void scale_add(float* x, float* y, int n, int k) {
+        // [thread_extent] blockIdx.x = 4
+        // [thread_extent] threadIdx.x = 256
+        for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) y[i] = x[i] * @factor@ + k;
+      }''', {'factor': 3})
+    x = torch.arange(5000, dtype=torch.float32, device='cuda')
+    y = torch.zeros_like(x)
+    fn(x, y, extra=[5000, 7])
+    torch.cuda.synchronize()
+    assert torch.equal(y, x * 3 + 7)
