@@ -16,6 +16,8 @@
 #include "runtime/symm_heap.h"
 #include "runtime/jit.h"
 #include "codec/codecs.h"
+#include "codec/abstract.h"
+#include "comm/abstract.h"
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -446,6 +448,38 @@ Tensor lz_decode_op(const Tensor& payload, const Tensor& sizes, int64_t raw_byte
   return raw;
 }
 
+// ---- C++ extension points: run a registered comm / codec on tensors -----------------------------
+Tensor native_comm_all_to_all_op(const std::string& name, const Tensor& t, int64_t world_size, int64_t world_rank,
+                                 int64_t local_size, int64_t heap_bases_ptr) {
+  CommContext ctx;
+  ctx.world_size = world_size; ctx.world_rank = world_rank; ctx.local_size = local_size;
+  ctx.local_rank = local_size > 0 ? world_rank % local_size : 0;
+  ctx.heap_bases = reinterpret_cast<const unsigned long long*>(heap_bases_ptr);
+  auto comm = make_comm(name, ctx);
+  TORCH_CHECK(comm != nullptr, "no native comm registered under `", name, "`");
+  Tensor in = t.contiguous();
+  Tensor out = torch::empty_like(in);
+  cudaStream_t s = in.is_cuda() ? cur_stream() : nullptr;
+  comm->all_to_all(in.data_ptr(), out.data_ptr(), in.numel() * in.element_size(), s);
+  return out;
+}
+
+Tensor native_codec_roundtrip_op(const std::string& name, const Tensor& t, int64_t parts, bool decode, int64_t out_bytes) {
+  auto codec = make_compressor(name);
+  TORCH_CHECK(codec != nullptr, "no native compressor registered under `", name, "`");
+  Tensor in = t.contiguous();
+  const size_t bytes = decode ? (size_t)out_bytes : in.numel() * in.element_size();
+  cudaStream_t s = in.is_cuda() ? cur_stream() : nullptr;
+  if (!decode) {
+    Tensor wire = torch::empty({(int64_t)codec->wire_bytes(bytes, parts)}, in.options().dtype(at::kByte));
+    codec->compress(in.data_ptr(), wire.data_ptr(), bytes, parts, in.element_size(), in.size(-1), s);
+    return wire;
+  }
+  Tensor out = torch::empty({out_bytes}, in.options().dtype(at::kByte));
+  codec->decompress(in.data_ptr(), out.data_ptr(), bytes, parts, 1, 1, s);
+  return out;
+}
+
 // ---- stand-alone transfers --------------------------------------------------------------------
 void xfer_op(int64_t src_ptr, const Tensor& msgs, int64_t ctas_per_msg, int64_t heap_bases_ptr, int64_t flag_off,
              int64_t wait_flags_ptr, const c10::optional<Tensor>& wait_idx, int64_t want, int64_t budget_ms,
@@ -491,6 +525,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("zfp_decode", &zfp_decode_op);
   m.def("lz_encode", &lz_encode_op);
   m.def("lz_decode", &lz_decode_op);
+  m.def("native_comm_names", &comm_names);
+  m.def("native_compressor_names", &compressor_names);
+  m.def("native_comm_all_to_all", &native_comm_all_to_all_op);
+  m.def("native_codec_run", &native_codec_roundtrip_op);
   m.def("xfer", &xfer_op);
   m.def("wait_flags", &wait_flags_op);
   m.def("gemm_push_arrivals", &gemm_push_arrivals);

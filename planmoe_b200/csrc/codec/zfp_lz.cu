@@ -173,6 +173,7 @@ lz_scan_kernel(const int* blk_sizes, uint8_t* payload, int* sizes, long long raw
   }
   if (threadIdx.x == 0) {
     hdr[1 + nb] = carry;
+    for (long long w = 2 + nb; w < lz_header_bytes(nb) / 4; ++w) hdr[w] = 0;   // header padding
     sizes[s] = (int)(lz_header_bytes(nb) + carry);
   }
 }
@@ -230,6 +231,7 @@ void lz_encode_cpu(const uint8_t* raw, uint8_t* payload, int* sizes, long long s
       off += (uint32_t)n;
     }
     hdr[1 + nb] = off;
+    for (long long w = 2 + nb; w < lz_header_bytes(nb) / 4; ++w) hdr[w] = 0;   // header padding
     sizes[s] = (int)(lz_header_bytes(nb) + off);
   }
 }

@@ -165,9 +165,34 @@ def register_compressor(name, factory):
     _REGISTRY[name] = factory
 
 
+class NativeCompressor(AbstractCompressor):
+    """Bridge to a codec registered in C++ (``planmoe::register_compressor``)."""
+
+    def __init__(self, name):
+        self.name = name
+
+    def compress(self, t, world_size=1):
+        wire = native.lib().native_codec_run(self.name, t.contiguous(), max(int(world_size), 1), False, 0)
+        return Packed([wire.view(max(int(world_size), 1), -1)], (t.dtype, tuple(t.shape)))
+
+    def decompress(self, packed):
+        dtype, shape = packed.meta
+        n = 1
+        for s in shape:
+            n *= s
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        raw = native.lib().native_codec_run(self.name, packed.wires[0].contiguous().view(-1), 1, True, nbytes)
+        return raw.view(dtype).view(shape)
+
+
 def get_compressor(name):
     factory = _REGISTRY.get(name)
-    return factory() if factory is not None else NoCompressor()
+    if factory is not None:
+        return factory()
+    lib = native.maybe_lib()
+    if lib is not None and name in lib.native_compressor_names():
+        return NativeCompressor(name)
+    return NoCompressor()
 
 
 register_compressor('no', NoCompressor)

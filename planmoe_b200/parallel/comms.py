@@ -197,8 +197,28 @@ def register_comm(name, factory):
     _REGISTRY[name] = factory
 
 
+class NativeComm(AbstractComm):
+    """Bridge to an all-to-all algorithm registered in C++ (``planmoe::register_comm``)."""
+
+    def __init__(self, name, group=None):
+        super().__init__(group)
+        self.name = name
+
+    def all_to_all(self, t):
+        from ..ops import native
+        bases = self._transport().segments[0].bases_device_ptr() if self._use_transport(t) else 0
+        return native.lib().native_comm_all_to_all(self.name, t, self.world_size, self.world_rank,
+                                                   self.local_size, bases)
+
+
 def get_comm(name, group=None):
-    factory = _REGISTRY.get(name, NaiveComm)
+    factory = _REGISTRY.get(name)
+    if factory is None:
+        from ..ops import native
+        lib = native.maybe_lib()
+        if lib is not None and name in lib.native_comm_names():
+            return NativeComm(name, group)
+        factory = NaiveComm
     return factory(group)
 
 

@@ -183,3 +183,17 @@ def test_pre_test_example_runs_on_cpu(tmp_path):
                              '--model_dim', '32', '--hidden_size', '32', '--num_steps', '2', '--layer',
                              '--log', str(tmp_path / 't.log')])
     assert mean > 0
+
+
+def test_cpp_extension_point_registries():
+    """Comm / codec objects registered from C++ are reachable by name from the Python layer."""
+    from planmoe_b200.ops import native
+    from planmoe_b200.parallel import codecs, comms
+    lib = native.lib()
+    assert 'native_flat' in lib.native_comm_names() and 'native_copy' in lib.native_compressor_names()
+    x = torch.randn(4, 6)
+    c = comms.get_comm('native_flat')
+    assert isinstance(c, comms.NativeComm) and torch.equal(c.all_to_all(x), x)
+    k = codecs.get_compressor('native_copy')
+    assert isinstance(k, codecs.NativeCompressor)
+    assert torch.equal(k.decompress(k.compress(x, 2)), x)
