@@ -197,3 +197,36 @@ def test_cpp_extension_point_registries():
     k = codecs.get_compressor('native_copy')
     assert isinstance(k, codecs.NativeCompressor)
     assert torch.equal(k.decompress(k.compress(x, 2)), x)
+
+
+def test_integration_helpers():
+    import argparse
+    from types import SimpleNamespace
+    from planmoe_b200.examples.megatron import planmoe_megatron as pm
+    from planmoe_b200.examples.fairseq_moe import planmoe_fairseq as pf
+    args = pm.add_planmoe_args(argparse.ArgumentParser()).parse_args(
+        ['--schemoe', '--schemoe-overlap-degree', '2', '--schemoe-compress-name', 'int8'])
+    assert args.schemoe and args.schemoe_comm_name == 'naive'
+    cfg = SimpleNamespace(hidden_size=32, ffn_hidden_size=64, num_moe_experts=4, expert_model_parallel_size=1,
+                          moe_router_topk=2, moe_expert_capacity_factor=2.0)
+    layer = pm.maybe_replace_mlp(SimpleNamespace(mlp=None), cfg, args)
+    out, bias = layer.mlp(torch.randn(2, 8, 32))
+    assert out.shape == (2, 8, 32) and bias is None
+    assert all(p.allreduce is False for p in layer.mlp.moe.experts.parameters())
+    os.environ['MOE'] = '2'
+    try:
+        assert pf.build_ffn(0, 16, 32) is None
+        moe = pf.build_ffn(1, 16, 32)
+        y = pf.ffn_forward(moe, torch.randn(6, 16))
+        total = pf.add_aux_loss(torch.tensor(1.0), sample_size=6)
+        assert y.shape == (6, 16) and float(total) > 1.0
+    finally:
+        os.environ.pop('MOE')
+    p = torch.nn.Parameter(torch.ones(3))
+    p.grad = torch.tensor([1.0, float('inf'), float('nan')])
+    os.environ['NO_OVERFLOW'] = '1'
+    try:
+        pf.sanitize_grads([p])
+    finally:
+        os.environ.pop('NO_OVERFLOW')
+    assert p.grad.tolist() == [1.0, 0.0, 0.0]
