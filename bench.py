@@ -115,15 +115,13 @@ def build_ours(args, device, group_world):
     from planmoe_b200 import moe
     degree = args.degree if args.degree in ('auto',) else int(args.degree)
     layer = moe.moe_layer(
-        gate_type={'type': 'top', 'k': CFG['top_k'], 'capacity_factor': CFG['capacity_factor'], 'fp32_gate': True},
+        gate_type={'type': 'top', 'k': CFG['top_k'], 'capacity_factor': CFG['capacity_factor'], 'fp32_gate': False},
         model_dim=CFG['model_dim'],
         experts={'type': 'ffn', 'count_per_node': CFG['local_experts'], 'hidden_size_per_expert': CFG['hidden'],
                  'activation_fn': 'gelu'},
         seeds=(1, 2 + (torch.distributed.get_rank() if group_world > 1 else 0), 3),
         a2a_ffn_overlap_degree=degree, compress_name=args.compress, comm_name=args.comm)
-    layer = layer.to(device).to(torch.bfloat16)
-    layer.gates[0].wg.float()
-    return layer
+    return layer.to(device).to(torch.bfloat16)
 
 
 class RefTorchLayer:
@@ -136,7 +134,7 @@ class RefTorchLayer:
         torch.manual_seed(2)
         M, H, El = CFG['model_dim'], CFG['hidden'], CFG['local_experts']
         self.world = world
-        self.wg = torch.nn.Parameter(torch.randn(El * world, M, device=device) * 0.02)
+        self.wg = torch.nn.Parameter((torch.randn(El * world, M, device=device) * 0.02).bfloat16())
         self.w1 = torch.nn.Parameter((torch.randn(El, M, H, device=device) * 0.02).bfloat16())
         self.b1 = torch.nn.Parameter(torch.zeros(El, H, device=device).bfloat16())
         self.w2 = torch.nn.Parameter((torch.randn(El, H, M, device=device) * 0.02).bfloat16())
@@ -152,7 +150,7 @@ class RefTorchLayer:
         from planmoe_b200.ops import dispatch as D
         from planmoe_b200.impls import fast_dispatch as FD
         W = self.world
-        scores = F.softmax(x.float() @ self.wg.t(), dim=1)
+        scores = F.softmax((x @ self.wg.t()).float(), dim=1)
         from planmoe_b200.jit_kernels import gating
         gating.use_fast_cumsum = False
         crit, l_aux = FD.extract_critical(scores, CFG['top_k'], capacity_factor=CFG['capacity_factor'], alignment=4)

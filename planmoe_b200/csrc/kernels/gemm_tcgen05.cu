@@ -408,14 +408,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const int nb = n0 + c0;                    // first global column
         if (nb >= p.N) break;
 
-        // activation backward: fetch this thread's 64 pre-activations (one 128-byte line) early
+        // activation backward: the warp fetches its 32 x 64 slab of pre-activations with full-line
+        // loads (4 rows x 128 bytes per instruction), issued before the TMEM load so that the two
+        // latencies overlap, and transposes it through the staging tile into one row per thread.
         uint4 pre[8];
         if constexpr (EPI == kEpiDAct) {
-          const __nv_bfloat16* arow = p.aux + (long long)g * p.aux_group_stride + (long long)my_m * p.aux_row_stride + nb;
 #pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            pre[c] = make_uint4(0, 0, 0, 0);
-            if (my_m < p.M && nb + c * 8 < p.N) pre[c] = __ldg(reinterpret_cast<const uint4*>(arow + c * 8));
+          for (int it = 0; it < 8; ++it) {
+            const int r = it * 4 + (lane >> 3), c = lane & 7;
+            const int m = m0 + q * 32 + r;
+            pre[it] = make_uint4(0, 0, 0, 0);
+            if (m < p.M && nb + c * 8 < p.N)
+              pre[it] = __ldg(reinterpret_cast<const uint4*>(
+                  p.aux + (long long)g * p.aux_group_stride + (long long)m * p.aux_row_stride + nb + c * 8));
           }
         }
 
@@ -423,6 +428,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         tmem_ld32(t_row + s2 * 64, v);
         tmem_ld32(t_row + s2 * 64 + 32, v + 32);
         tmem_ld_wait();
+
+        if constexpr (EPI == kEpiDAct) {
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int r = it * 4 + (lane >> 3), c = lane & 7;
+            *reinterpret_cast<uint4*>(st0 + r * 128 + ((c ^ (r & 7)) << 4)) = pre[it];
+          }
+          __syncwarp();
+#pragma unroll
+          for (int c = 0; c < 8; ++c)
+            pre[c] = *reinterpret_cast<const uint4*>(st0 + lane * 128 + ((c ^ (lane & 7)) << 4));
+          __syncwarp();
+        }
 
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
