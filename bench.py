@@ -212,11 +212,12 @@ def main():
     x_dev = host_x.to(device, non_blocking=True)
     host_loss = torch.zeros(1, dtype=torch.float32).pin_memory()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    target = torch.zeros(S, M, dtype=torch.bfloat16, device=device)
 
     def step(x):
         opt.zero_grad(set_to_none=True)
         y = layer(x)
-        loss = y.float().pow(2).mean() + 0.01 * y.l_aux.float()
+        loss = torch.nn.functional.mse_loss(y, target) + 0.01 * y.l_aux.to(y.dtype)
         loss.backward()
         opt.step()
         return loss

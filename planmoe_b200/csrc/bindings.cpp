@@ -329,8 +329,8 @@ Tensor colsum_op(const Tensor& x) {
   c10::cuda::CUDAGuard guard(x.device());
   const int groups = x.size(0), N = x.size(2);
   const int64_t rows = x.size(1);
-  TORCH_CHECK(N % 2 == 0);
-  const int64_t slabs = (rows + 255) / 256;
+  TORCH_CHECK(N % 8 == 0 && x.stride(1) % 8 == 0 && x.stride(0) % 8 == 0, "colsum needs 16-byte aligned rows");
+  const int64_t slabs = colsum_slabs(rows);
   Tensor buf = torch::empty({(int64_t)groups * N * (1 + slabs)}, x.options().dtype(at::kFloat));
   launch_colsum_bf16(x.data_ptr(), buf.data_ptr<float>(), groups, rows, N, x.stride(1), x.stride(0), cur_stream());
   return buf.narrow(0, 0, (int64_t)groups * N).view({groups, N});

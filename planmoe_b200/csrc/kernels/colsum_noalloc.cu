@@ -1,6 +1,6 @@
 // Column sums of a bf16 [groups][rows][N] tensor with library-owned scratch (see the header for
-// who this is for and what the limits are).  Same two-stage, fixed-order reduction as the regular
-// column-sum kernels, so results are bit-identical to them.
+// who this is for and what the limits are).  Two-stage reduction in a fixed order: slabs of 256
+// rows, then the slab partials in slab order, so results are reproducible run to run.
 
 #include "kernels/colsum_noalloc.h"
 

@@ -19,18 +19,18 @@
 
 namespace planmoe {
 
-constexpr int kGateThreads = 256;
+constexpr int kGateThreads = 64;    // small blocks: 8192 tokens still fill most SMs
 constexpr int kGateWarps = kGateThreads / 32;
 constexpr int kMaxE = 64;   // experts handled by the fused gate (per-thread register row)
 constexpr int kMaxK = 4;
 
-template <class T>
+template <class T, int ME>
 __device__ __forceinline__ void load_row(const T* row, int E, float* v) {
 #pragma unroll
-  for (int e = 0; e < kMaxE; ++e) v[e] = (e < E) ? to_f32(row[e]) : -INFINITY;
+  for (int e = 0; e < ME; ++e) v[e] = (e < E) ? to_f32(row[e]) : -INFINITY;
 }
 
-template <class T>
+template <class T, int ME>
 __global__ void __launch_bounds__(kGateThreads)
 gate_stats_kernel(const T* __restrict__ logits, int S, int E, int K,
                   int* __restrict__ idx,          // [K][S]
@@ -48,27 +48,27 @@ gate_stats_kernel(const T* __restrict__ logits, int S, int E, int K,
   for (int i = tid; i < kGateWarps * kMaxK * kMaxE; i += kGateThreads) (&warp_cnt[0][0][0])[i] = 0;
   __syncthreads();
 
-  float p[kMaxE];
+  float p[ME];
   int pick[kMaxK];
   if (live) {
-    load_row(logits + (size_t)t * E, E, p);
+    load_row<T, ME>(logits + (size_t)t * E, E, p);
     float mx = -INFINITY;
 #pragma unroll
-    for (int e = 0; e < kMaxE; ++e) mx = fmaxf(mx, p[e]);
+    for (int e = 0; e < ME; ++e) mx = fmaxf(mx, p[e]);
     float sum = 0.f;
 #pragma unroll
-    for (int e = 0; e < kMaxE; ++e) { p[e] = (e < E) ? expf(p[e] - mx) : 0.f; sum += p[e]; }
+    for (int e = 0; e < ME; ++e) { p[e] = (e < E) ? expf(p[e] - mx) : 0.f; sum += p[e]; }
     const float inv = 1.f / sum;
 #pragma unroll
-    for (int e = 0; e < kMaxE; ++e) p[e] *= inv;
+    for (int e = 0; e < ME; ++e) p[e] *= inv;
   } else {
 #pragma unroll
-    for (int e = 0; e < kMaxE; ++e) p[e] = 0.f;
+    for (int e = 0; e < ME; ++e) p[e] = 0.f;
   }
 
   // per-expert score sums: warp shuffle reduce, fixed order
 #pragma unroll
-  for (int e = 0; e < kMaxE; ++e) {
+  for (int e = 0; e < ME; ++e) {
     if (e < E) {
       float s = warp_sum(p[e]);
       if (lane == 0) score_sum[warp][e] = s;
@@ -80,7 +80,7 @@ gate_stats_kernel(const T* __restrict__ logits, int S, int E, int K,
     int best = -1;
     float bv = -1.f;
 #pragma unroll
-    for (int e = 0; e < kMaxE; ++e) {
+    for (int e = 0; e < ME; ++e) {
       if (e < E && !((taken >> e) & 1ull) && p[e] > bv) { bv = p[e]; best = e; }
     }
     pick[k] = live ? best : -1;
@@ -176,7 +176,7 @@ gate_assign_kernel(int S, int E, int K, int C, int normalize, float eps,
   }
 }
 
-template <class T>
+template <class T, int ME>
 __global__ void __launch_bounds__(kGateThreads)
 gate_bwd_kernel(const T* __restrict__ logits, int S, int E, int K, int normalize, float eps,
                 const int* __restrict__ idx, const float* __restrict__ dgates,   // [K][S] or null
@@ -184,17 +184,17 @@ gate_bwd_kernel(const T* __restrict__ logits, int S, int E, int K, int normalize
                 const int* __restrict__ top1_count, T* __restrict__ dlogits) {
   const int t = blockIdx.x * kGateThreads + threadIdx.x;
   if (t >= S) return;
-  float p[kMaxE];
-  load_row(logits + (size_t)t * E, E, p);
+  float p[ME];
+  load_row<T, ME>(logits + (size_t)t * E, E, p);
   float mx = -INFINITY;
 #pragma unroll
-  for (int e = 0; e < kMaxE; ++e) mx = fmaxf(mx, p[e]);
+  for (int e = 0; e < ME; ++e) mx = fmaxf(mx, p[e]);
   float sum = 0.f;
 #pragma unroll
-  for (int e = 0; e < kMaxE; ++e) { p[e] = (e < E) ? expf(p[e] - mx) : 0.f; sum += p[e]; }
+  for (int e = 0; e < ME; ++e) { p[e] = (e < E) ? expf(p[e] - mx) : 0.f; sum += p[e]; }
   const float inv = 1.f / sum;
 #pragma unroll
-  for (int e = 0; e < kMaxE; ++e) p[e] *= inv;
+  for (int e = 0; e < ME; ++e) p[e] *= inv;
 
   // d(score): loss part for every expert, gate part for the picked ones
   const float lw = dl_aux ? dl_aux[0] * (float)E / ((float)S * (float)S) : 0.f;
@@ -205,7 +205,7 @@ gate_bwd_kernel(const T* __restrict__ logits, int S, int E, int K, int normalize
     pk[k] = idx[(size_t)k * S + t];
     float s = 0.f;
 #pragma unroll
-    for (int e = 0; e < kMaxE; ++e) s = (e == pk[k]) ? p[e] : s;
+    for (int e = 0; e < ME; ++e) s = (e == pk[k]) ? p[e] : s;
     ds_pick[k] = s;    // temporarily the score
     denom += s;
   }
@@ -223,10 +223,10 @@ gate_bwd_kernel(const T* __restrict__ logits, int S, int E, int K, int normalize
       ds_pick[k] = dg;
     }
   }
-  float ds[kMaxE];
+  float ds[ME];
   float inner = 0.f;
 #pragma unroll
-  for (int e = 0; e < kMaxE; ++e) {
+  for (int e = 0; e < ME; ++e) {
     float d = 0.f;
     if (e < E) {
       d = lw * (float)top1_count[e];
@@ -237,7 +237,7 @@ gate_bwd_kernel(const T* __restrict__ logits, int S, int E, int K, int normalize
   }
   T* out = dlogits + (size_t)t * E;
 #pragma unroll
-  for (int e = 0; e < kMaxE; ++e)
+  for (int e = 0; e < ME; ++e)
     if (e < E) out[e] = from_f32<T>(p[e] * (ds[e] - inner));
 }
 
@@ -248,8 +248,14 @@ void launch_gate_forward(const T* logits, int S, int E, int K, int C, bool norma
                          float* ws_blk_score, cudaStream_t stream) {
   const int nblk = (S + kGateThreads - 1) / kGateThreads;
   cudaMemsetAsync(slot_map, 0xFF, sizeof(int) * (size_t)E * C, stream);
-  gate_stats_kernel<T><<<nblk, kGateThreads, 0, stream>>>(logits, S, E, K, idx, raw_gate, ws_rank,
-                                                         ws_blk_count, ws_blk_score);
+  if (E <= 8)
+    gate_stats_kernel<T, 8><<<nblk, kGateThreads, 0, stream>>>(logits, S, E, K, idx, raw_gate, ws_rank, ws_blk_count, ws_blk_score);
+  else if (E <= 16)
+    gate_stats_kernel<T, 16><<<nblk, kGateThreads, 0, stream>>>(logits, S, E, K, idx, raw_gate, ws_rank, ws_blk_count, ws_blk_score);
+  else if (E <= 32)
+    gate_stats_kernel<T, 32><<<nblk, kGateThreads, 0, stream>>>(logits, S, E, K, idx, raw_gate, ws_rank, ws_blk_count, ws_blk_score);
+  else
+    gate_stats_kernel<T, 64><<<nblk, kGateThreads, 0, stream>>>(logits, S, E, K, idx, raw_gate, ws_rank, ws_blk_count, ws_blk_score);
   gate_assign_kernel<<<nblk, kGateThreads, 0, stream>>>(S, E, K, C, normalize ? 1 : 0, eps, idx,
                                                       raw_gate, ws_rank, ws_blk_count, ws_blk_score,
                                                       nblk, loc, gates, slot_map, top1_count, l_aux);
@@ -260,8 +266,15 @@ void launch_gate_backward(const T* logits, int S, int E, int K, bool normalize, 
                           const int* idx, const float* dgates, const float* dl_aux,
                           const int* top1_count, T* dlogits, cudaStream_t stream) {
   const int nblk = (S + kGateThreads - 1) / kGateThreads;
-  gate_bwd_kernel<T><<<nblk, kGateThreads, 0, stream>>>(logits, S, E, K, normalize ? 1 : 0, eps, idx,
-                                                       dgates, dl_aux, top1_count, dlogits);
+  const int nz = normalize ? 1 : 0;
+  if (E <= 8)
+    gate_bwd_kernel<T, 8><<<nblk, kGateThreads, 0, stream>>>(logits, S, E, K, nz, eps, idx, dgates, dl_aux, top1_count, dlogits);
+  else if (E <= 16)
+    gate_bwd_kernel<T, 16><<<nblk, kGateThreads, 0, stream>>>(logits, S, E, K, nz, eps, idx, dgates, dl_aux, top1_count, dlogits);
+  else if (E <= 32)
+    gate_bwd_kernel<T, 32><<<nblk, kGateThreads, 0, stream>>>(logits, S, E, K, nz, eps, idx, dgates, dl_aux, top1_count, dlogits);
+  else
+    gate_bwd_kernel<T, 64><<<nblk, kGateThreads, 0, stream>>>(logits, S, E, K, nz, eps, idx, dgates, dl_aux, top1_count, dlogits);
 }
 
 int gate_workspace_blocks(int S) { return (S + kGateThreads - 1) / kGateThreads; }

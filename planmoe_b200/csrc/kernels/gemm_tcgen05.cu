@@ -12,8 +12,8 @@
 //               per instruction, accumulating in TMEM (2 x 256 columns, double buffered so the
 //               epilogue of tile i overlaps the main loop of tile i+1); tcgen05.commit releases
 //               ring stages and publishes the accumulator.
-//   warps 2..9  epilogue: tcgen05.ld 32x32b -> registers -> bias / activation / activation
-//               backward -> bf16 -> swizzled shared-memory staging -> full-line 16-byte stores,
+//   warps 2..9  epilogue: tcgen05.ld 32x32b -> registers -> bias / activation (saving its
+//               derivative) / multiply by a saved derivative -> bf16 -> swizzled shared-memory staging -> full-line 16-byte stores,
 //               either to local memory or straight into the combine buffer of the rank that
 //               owns the token ("push"), followed by a release-add on that rank's flag.
 //
@@ -218,31 +218,24 @@ __device__ __forceinline__ void gauss_cdf_pdf(float x, float& cdf, float& pdf) {
   pdf = 0.3989422804014327f * e;
 }
 
-__device__ __forceinline__ float act_fwd(float x, int act) {
+// Activation value and derivative in one go (they share the transcendental work).
+__device__ __forceinline__ void act_both(float x, int act, float& out, float& deriv) {
   switch (act) {
-    case kActRelu: return fmaxf(x, 0.f);
+    case kActRelu: out = fmaxf(x, 0.f); deriv = x > 0.f ? 1.f : 0.f; break;
     case kActGelu: {
       float cdf, pdf;
       gauss_cdf_pdf(x, cdf, pdf);
-      return x * cdf;
-    }
-    case kActSilu: return x * __frcp_rn(1.f + __expf(-x));
-    default: return x;
-  }
-}
-__device__ __forceinline__ float act_bwd(float x, int act) {
-  switch (act) {
-    case kActRelu: return x > 0.f ? 1.f : 0.f;
-    case kActGelu: {
-      float cdf, pdf;
-      gauss_cdf_pdf(x, cdf, pdf);
-      return fmaf(x, pdf, cdf);
+      out = x * cdf;
+      deriv = fmaf(x, pdf, cdf);
+      break;
     }
     case kActSilu: {
       const float sg = __frcp_rn(1.f + __expf(-x));
-      return sg * (1.f + x * (1.f - sg));
+      out = x * sg;
+      deriv = sg * (1.f + x * (1.f - sg));
+      break;
     }
-    default: return 1.f;
+    default: out = x; deriv = 1.f; break;
   }
 }
 
@@ -383,6 +376,23 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const int g = tile / (nt_count * mt_count);
       const int m0 = mt * BM, n0 = nt * BN;
 
+      // Activation backward: the 32 x 64 slab of saved activation derivatives this warp needs first
+      // is requested before the accumulator is awaited, so its latency hides behind the main loop.
+      // Loads are full-line (4 rows x 128 bytes per instruction).
+      uint4 araw[8];
+      auto load_aux_slab = [&](int nb) {
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+          const int r = it * 4 + (lane >> 3), c = lane & 7;
+          const int m = m0 + q * 32 + r;
+          araw[it] = make_uint4(0, 0, 0, 0);
+          if (m < p.M && nb + c * 8 < p.N)
+            araw[it] = __ldg(reinterpret_cast<const uint4*>(
+                p.aux + (long long)g * p.aux_group_stride + (long long)m * p.aux_row_stride + nb + c * 8));
+        }
+      };
+      if constexpr (EPI == kEpiDAct) load_aux_slab(n0 + half * 128);
+
       // All epilogue warps take the same exit decision: a warp that timed out raises the flag of
       // this iteration's parity before the barrier, everyone reads it after the barrier.
       bool got = mbar_wait(smem_u32(&ctl->acc_full[acc]), acc_phase, ctl, p.budget_ns, p.status, 2, acc);
@@ -400,7 +410,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       tc_fence_after();
 
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + half * 128;
-      const int my_m = m0 + q * 32 + lane;         // the accumulator row this thread holds
+
+      // coalesced write-out of the staging tile: each instruction stores 4 rows x 128 bytes
+      auto write_out = [&](__nv_bfloat16* dst, long long row_stride, long long group_stride, int nb) {
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+          const int r = it * 4 + (lane >> 3), c = lane & 7;
+          const int m = m0 + q * 32 + r;
+          if (m < p.M && nb + c * 8 < p.N) {
+            const uint4 val = *reinterpret_cast<const uint4*>(st0 + r * 128 + ((c ^ (r & 7)) << 4));
+            *reinterpret_cast<uint4*>(dst + (long long)g * group_stride + (long long)m * row_stride + nb + c * 8) = val;
+          }
+        }
+      };
 
 #pragma unroll 1
       for (int s2 = 0; s2 < 2; ++s2) {
@@ -408,83 +430,77 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const int nb = n0 + c0;                    // first global column
         if (nb >= p.N) break;
 
-        // activation backward: the warp fetches its 32 x 64 slab of pre-activations with full-line
-        // loads (4 rows x 128 bytes per instruction), issued before the TMEM load so that the two
-        // latencies overlap, and transposes it through the staging tile into one row per thread.
-        uint4 pre[8];
-        if constexpr (EPI == kEpiDAct) {
-#pragma unroll
-          for (int it = 0; it < 8; ++it) {
-            const int r = it * 4 + (lane >> 3), c = lane & 7;
-            const int m = m0 + q * 32 + r;
-            pre[it] = make_uint4(0, 0, 0, 0);
-            if (m < p.M && nb + c * 8 < p.N)
-              pre[it] = __ldg(reinterpret_cast<const uint4*>(
-                  p.aux + (long long)g * p.aux_group_stride + (long long)m * p.aux_row_stride + nb + c * 8));
-          }
-        }
-
         uint32_t v[64];
         tmem_ld32(t_row + s2 * 64, v);
         tmem_ld32(t_row + s2 * 64 + 32, v + 32);
-        tmem_ld_wait();
 
+        uint4 dact[8];
         if constexpr (EPI == kEpiDAct) {
+          // transpose the fetched slab through the staging tile into one row per thread
 #pragma unroll
           for (int it = 0; it < 8; ++it) {
             const int r = it * 4 + (lane >> 3), c = lane & 7;
-            *reinterpret_cast<uint4*>(st0 + r * 128 + ((c ^ (r & 7)) << 4)) = pre[it];
+            *reinterpret_cast<uint4*>(st0 + r * 128 + ((c ^ (r & 7)) << 4)) = araw[it];
           }
           __syncwarp();
 #pragma unroll
           for (int c = 0; c < 8; ++c)
-            pre[c] = *reinterpret_cast<const uint4*>(st0 + lane * 128 + ((c ^ (lane & 7)) << 4));
+            dact[c] = *reinterpret_cast<const uint4*>(st0 + lane * 128 + ((c ^ (lane & 7)) << 4));
           __syncwarp();
+          if (s2 == 0 && nb + 64 < p.N) load_aux_slab(nb + 64);     // prefetch the second slab
         }
+        tmem_ld_wait();
 
+        uint4 opk[8];
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           float f[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[c * 8 + i]) + bias_s[c0 + c * 8 + i];
           if constexpr (EPI == kEpiBiasAct) {
-            if (p.aux != nullptr && my_m < p.M && nb + c * 8 < p.N) {
-              const uint4 auxv = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
-              *reinterpret_cast<uint4*>(p.aux + (long long)g * p.aux_group_stride + (long long)my_m * p.aux_row_stride + nb + c * 8) = auxv;
-            }
+            float d[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) f[i] = act_fwd(f[i], p.activation);
+            for (int i = 0; i < 8; ++i) act_both(f[i], p.activation, f[i], d[i]);
+            // derivative goes through the staging tile first; the activation waits in registers
+            *reinterpret_cast<uint4*>(st0 + lane * 128 + ((c ^ (lane & 7)) << 4)) =
+                make_uint4(pack_bf16(d[0], d[1]), pack_bf16(d[2], d[3]), pack_bf16(d[4], d[5]), pack_bf16(d[6], d[7]));
           } else if constexpr (EPI == kEpiDAct) {
-            const __nv_bfloat162* ph = reinterpret_cast<const __nv_bfloat162*>(&pre[c]);
+            const __nv_bfloat162* ph = reinterpret_cast<const __nv_bfloat162*>(&dact[c]);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-              const float2 pf = __bfloat1622float2(ph[i]);
-              f[2 * i] *= act_bwd(pf.x, p.activation);
-              f[2 * i + 1] *= act_bwd(pf.y, p.activation);
+              const float2 df = __bfloat1622float2(ph[i]);
+              f[2 * i] *= df.x;
+              f[2 * i + 1] *= df.y;
             }
           }
-          const uint4 outv = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
-          *reinterpret_cast<uint4*>(st0 + lane * 128 + ((c ^ (lane & 7)) << 4)) = outv;
+          opk[c] = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
         }
+        if constexpr (EPI == kEpiBiasAct) {
+          __syncwarp();
+          if (p.aux != nullptr) write_out(p.aux, p.aux_row_stride, p.aux_group_stride, nb);
+          __syncwarp();
+        }
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          *reinterpret_cast<uint4*>(st0 + lane * 128 + ((c ^ (lane & 7)) << 4)) = opk[c];
         __syncwarp();
 
-        // full-line write-out: each instruction stores 4 rows x 128 bytes
+        if constexpr (EPI == kEpiPush) {
 #pragma unroll
-        for (int it = 0; it < 8; ++it) {
-          const int r = it * 4 + (lane >> 3), c = lane & 7;
-          const int m = m0 + q * 32 + r;
-          if (m < p.M && nb + c * 8 < p.N) {
-            const uint4 val = *reinterpret_cast<const uint4*>(st0 + r * 128 + ((c ^ (r & 7)) << 4));
-            if constexpr (EPI == kEpiPush) {
+          for (int it = 0; it < 8; ++it) {
+            const int r = it * 4 + (lane >> 3), c = lane & 7;
+            const int m = m0 + q * 32 + r;
+            if (m < p.M && nb + c * 8 < p.N) {
+              const uint4 val = *reinterpret_cast<const uint4*>(st0 + r * 128 + ((c ^ (r & 7)) << 4));
               const int s = m / p.push_rows, cc = m - s * p.push_rows;
               __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(
                   reinterpret_cast<uint8_t*>(p.heap_bases[s]) + p.push_data_off);
               const long long drow = ((long long)p.my_rank * p.groups + g) * p.push_C + p.push_c0 + cc;
               *reinterpret_cast<uint4*>(base + drow * p.N + nb + c * 8) = val;
-            } else {
-              *reinterpret_cast<uint4*>(p.D + (long long)g * p.d_group_stride + (long long)m * p.d_row_stride + nb + c * 8) = val;
             }
           }
+        } else {
+          write_out(p.D, p.d_row_stride, p.d_group_stride, nb);
         }
         __syncwarp();
       }
@@ -641,25 +657,34 @@ cudaError_t launch_grouped_gemm(const GemmArgs& a, cudaStream_t stream) {
 // Two-stage and deterministic: every CTA reduces a row slab, partials are added in slab order.
 // ---------------------------------------------------------------------------------------------
 namespace {
-constexpr int kColsumSlab = 256;
+constexpr int kColsumSlab = 32;
 
 __global__ void __launch_bounds__(256)
 colsum_partial_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ partial, long long rows, int N,
                       long long row_stride, long long group_stride, int slabs) {
-  // grid: (N/ (256*2) rounded up, slabs, groups); each thread owns 2 adjacent columns
-  const int col = (blockIdx.x * 256 + threadIdx.x) * 2;
+  // grid: (ceil(N / 2048), slabs, groups); each thread owns 8 adjacent columns (one 16-byte load per row)
+  const int col = (blockIdx.x * 256 + threadIdx.x) * 8;
   if (col >= N) return;
   const int slab = blockIdx.y, g = blockIdx.z;
   const long long r0 = (long long)slab * kColsumSlab;
   const long long r1 = r0 + kColsumSlab < rows ? r0 + kColsumSlab : rows;
   const __nv_bfloat16* base = x + (long long)g * group_stride + col;
-  float a0 = 0.f, a1 = 0.f;
+  float a[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) a[i] = 0.f;
+#pragma unroll 4
   for (long long r = r0; r < r1; ++r) {
-    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(base + r * row_stride));
-    a0 += f.x; a1 += f.y;
+    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(base + r * row_stride));
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(h[i]);
+      a[2 * i] += f.x; a[2 * i + 1] += f.y;
+    }
   }
   float* dst = partial + ((long long)g * slabs + slab) * N + col;
-  dst[0] = a0; dst[1] = a1;
+  *reinterpret_cast<float4*>(dst) = make_float4(a[0], a[1], a[2], a[3]);
+  *reinterpret_cast<float4*>(dst + 4) = make_float4(a[4], a[5], a[6], a[7]);
 }
 
 __global__ void colsum_final_kernel(const float* __restrict__ partial, float* __restrict__ out, int N, int slabs) {
@@ -672,13 +697,15 @@ __global__ void colsum_final_kernel(const float* __restrict__ partial, float* __
 }
 }  // namespace
 
-// `out` must have room for groups*N floats followed by groups*slabs*N floats of scratch, where
-// slabs = ceil(rows / 256); see colsum_scratch_floats().
+int colsum_slabs(long long rows) { return (int)((rows + kColsumSlab - 1) / kColsumSlab); }
+
+// `out` must have room for groups*N floats followed by groups*colsum_slabs(rows)*N floats of scratch.
+// N must be a multiple of 8 and rows of x 16-byte aligned.
 void launch_colsum_bf16(const void* x, float* out, int groups, long long rows, int N, long long row_stride,
                         long long group_stride, cudaStream_t stream) {
-  const int slabs = (int)((rows + kColsumSlab - 1) / kColsumSlab);
+  const int slabs = colsum_slabs(rows);
   float* partial = out + (long long)groups * N;
-  dim3 g1((N / 2 + 255) / 256, slabs, groups);
+  dim3 g1((N / 8 + 255) / 256, slabs, groups);
   colsum_partial_kernel<<<g1, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), partial, rows, N,
                                               row_stride, group_stride, slabs);
   dim3 g2((N + 255) / 256, groups);

@@ -87,8 +87,8 @@ void launch_wait_flags(const unsigned long long* flags, int n, unsigned long lon
 // Grouped bf16 GEMM  D[g] (Mg x N) = A[g] (Mg x K) . B[g] (K x N), fp32 accumulation in TMEM.
 enum GemmEpilogue : int {
   kEpiStore = 0,    // D = acc (+ bias)
-  kEpiBiasAct = 1,  // aux = acc + bias ; D = act(aux)
-  kEpiDAct = 2,     // D = acc * act'(aux)
+  kEpiBiasAct = 1,  // t = acc + bias ; D = act(t) ; aux = act'(t)
+  kEpiDAct = 2,     // D = acc * aux      (aux = a saved activation derivative)
   kEpiPush = 3,     // (acc + bias) stored into the origin ranks' combine buffers + flags
 };
 enum Activation : int { kActIdentity = 0, kActRelu = 1, kActGelu = 2, kActSilu = 3 };
@@ -109,7 +109,7 @@ struct GemmArgs {
   int groups, M, N, K;             // per-group problem; K is per chunk when chunks > 1
   int epilogue, activation;
   void* D; long long d_row_stride, d_group_stride;          // bf16 output
-  void* aux; long long aux_row_stride, aux_group_stride;    // bf16 pre-activation (in or out)
+  void* aux; long long aux_row_stride, aux_group_stride;    // bf16 activation derivative (in or out)
   const void* bias; long long bias_group_stride;            // bf16 [groups][N] or null
   // flag-gated A rows (A is a receive buffer filled by peers): rows [s*gate_rows, (s+1)*gate_rows)
   // of every group become readable when gate_flags[s] >= gate_want.
@@ -129,6 +129,7 @@ cudaError_t launch_grouped_gemm(const GemmArgs& args, cudaStream_t stream);
 int gemm_push_arrivals(int groups, int M, int N, int push_rows, int s);
 
 // Column sums of a bf16 [groups][rows][N] tensor -> fp32 [groups][N] (bias gradients).
+int colsum_slabs(long long rows);
 void launch_colsum_bf16(const void* x, float* out, int groups, long long rows, int N,
                         long long row_stride, long long group_stride, cudaStream_t stream);
 

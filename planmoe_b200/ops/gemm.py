@@ -3,7 +3,7 @@
 ``grouped_gemm`` exposes the kernel of ``csrc/kernels/gemm_tcgen05.cu``: bf16 operands
 ``[groups, rows, cols]`` (optionally a leading split-K ``chunks`` dim), each either K-major or
 MN-major, fp32 accumulation in TMEM, and one of four epilogues (store, bias+activation with the
-pre-activation saved, activation-backward, push to peer ranks).
+activation's derivative saved, multiply by a saved derivative, push to peer ranks).
 
 ``expert_ffn`` is ``act(x @ W1 + b1) @ W2 + b2`` for all local experts with a hand-written
 backward: six GEMM launches (2 forward, 2 dgrad, 2 wgrad) on the same kernel, activation and its

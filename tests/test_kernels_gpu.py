@@ -76,18 +76,18 @@ def test_gemm_epilogues(act):
     bias = _rand(G, N)
     code = gemm.ACT_CODES[act]
     fn = {'relu': F.relu, 'gelu': F.gelu, 'silu': F.silu, 'identity': lambda v: v}[act]
-    pre = torch.empty(G, M, N, device='cuda', dtype=torch.bfloat16)
-    h = gemm.grouped_gemm(A, False, B, True, gemm.EPI_BIAS_ACT, code, bias=bias, aux=pre)
+    dact = torch.empty(G, M, N, device='cuda', dtype=torch.bfloat16)
+    h = gemm.grouped_gemm(A, False, B, True, gemm.EPI_BIAS_ACT, code, bias=bias, aux=dact)
     gemm.check_status()
-    ref_pre = _ref_gemm(A, False, B, True) + bias.float()[:, None, :]
-    _check(pre, ref_pre)
-    _check(h, fn(ref_pre))
-    # activation backward: D = (A.B) * act'(aux)
-    p32 = pre.float().requires_grad_(True)
-    fn(p32).sum().backward()
-    d = gemm.grouped_gemm(A, False, B, True, gemm.EPI_DACT, code, aux=pre)
+    ref_pre = (_ref_gemm(A, False, B, True) + bias.float()[:, None, :]).requires_grad_(True)
+    ref_h = fn(ref_pre)
+    ref_h.sum().backward()
+    _check(h, ref_h.detach())
+    _check(dact, ref_pre.grad)                    # the epilogue saves act'(A.B + bias)
+    # activation backward: D = (A.B) * aux
+    d = gemm.grouped_gemm(A, False, B, True, gemm.EPI_DACT, code, aux=dact)
     gemm.check_status()
-    _check(d, _ref_gemm(A, False, B, True) * p32.grad)
+    _check(d, _ref_gemm(A, False, B, True) * dact.float())
 
 
 def test_gemm_split_k_chunks():
