@@ -252,7 +252,7 @@ struct GemmOpts {
   int64_t gate_flags_ptr = 0, gate_rows = 0, gate_want = 0;
   // push
   int64_t heap_bases_ptr = 0, push_data_off = 0, push_flag_off = 0, push_rows = 0, push_C = 0, push_c0 = 0,
-          push_chunk = 0, W = 1, my_rank = 0;
+          push_chunk = 0, W = 1, my_rank = 0, chunk_groups = 0;
   int64_t budget_ms = 0, status_ptr = 0, max_ctas = 0;
 };
 
@@ -279,7 +279,8 @@ Tensor grouped_gemm_op(const Tensor& A, bool a_mn, const Tensor& B, bool b_mn, c
   g.A = operand_of(A, a_mn);
   g.B = operand_of(B, b_mn);
   const int groups = A.size(A.dim() - 3);
-  TORCH_CHECK(B.size(B.dim() - 3) == groups, "group count mismatch");
+  TORCH_CHECK(o.chunk_groups > 0 ? (groups % o.chunk_groups == 0 && B.size(B.dim() - 3) == o.chunk_groups)
+                                 : B.size(B.dim() - 3) == groups, "group count mismatch");
   g.groups = groups;
   g.M = a_mn ? g.A.cols : g.A.rows;
   g.K = a_mn ? g.A.rows : g.A.cols;
@@ -307,7 +308,8 @@ Tensor grouped_gemm_op(const Tensor& A, bool a_mn, const Tensor& B, bool b_mn, c
   }
   if (o.bias.has_value() && o.bias->defined()) {
     const Tensor& b = *o.bias;
-    TORCH_CHECK(b.scalar_type() == at::kBFloat16 && b.is_contiguous() && b.numel() == (int64_t)groups * g.N);
+    TORCH_CHECK(b.scalar_type() == at::kBFloat16 && b.is_contiguous() &&
+                b.numel() == (int64_t)(o.chunk_groups > 0 ? o.chunk_groups : groups) * g.N);
     g.bias = b.data_ptr(); g.bias_group_stride = g.N;
   }
   g.gate_flags = reinterpret_cast<const unsigned long long*>(o.gate_flags_ptr);
@@ -315,6 +317,7 @@ Tensor grouped_gemm_op(const Tensor& A, bool a_mn, const Tensor& B, bool b_mn, c
   g.heap_bases = reinterpret_cast<const unsigned long long*>(o.heap_bases_ptr);
   g.push_data_off = o.push_data_off; g.push_flag_off = o.push_flag_off; g.push_rows = o.push_rows;
   g.push_C = o.push_C; g.push_c0 = o.push_c0; g.push_chunk = o.push_chunk; g.W = o.W; g.my_rank = o.my_rank;
+  g.chunk_groups = o.chunk_groups;
   g.budget_ns = (unsigned long long)o.budget_ms * 1000000ull;
   g.status = reinterpret_cast<int*>(o.status_ptr);
   g.max_ctas = o.max_ctas;
@@ -339,14 +342,15 @@ Tensor colsum_op(const Tensor& x) {
 // ---- push / wait wrappers for the fused MoE path ------------------------------------------------
 void scatter_push_op(const Tensor& x, const Tensor& slot_map, const c10::optional<Tensor>& gates, int64_t K, int64_t E,
                      int64_t C, int64_t heap_bases_ptr, int64_t data_off, int64_t flag_off, int64_t W, int64_t my_rank,
-                     int64_t chunks, int64_t ctas_per_msg) {
+                     int64_t chunks, int64_t ctas, int64_t chunk_begin, int64_t chunk_count) {
   count_launch(1);
   TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.is_contiguous());
   c10::cuda::CUDAGuard guard(x.device());
   PushArgs pa{};
   pa.heap_bases = reinterpret_cast<const unsigned long long*>(heap_bases_ptr);
   pa.data_off = data_off; pa.flag_off = flag_off; pa.scale_off = 0;
-  pa.W = W; pa.my_rank = my_rank; pa.chunks = chunks; pa.ctas_per_msg = ctas_per_msg;
+  pa.W = W; pa.my_rank = my_rank; pa.chunks = chunks; pa.ctas_per_msg = ctas;
+  pa.chunk_begin = chunk_begin; pa.chunk_count = chunk_count;
   TORCH_CHECK(E % W == 0 && C % chunks == 0);
   const int S = x.size(0), M = x.size(1);
   DISPATCH_FLOAT(x, "scatter_push", [&] {
@@ -553,6 +557,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_readwrite("push_chunk", &GemmOpts::push_chunk)
       .def_readwrite("W", &GemmOpts::W)
       .def_readwrite("my_rank", &GemmOpts::my_rank)
+      .def_readwrite("chunk_groups", &GemmOpts::chunk_groups)
       .def_readwrite("budget_ms", &GemmOpts::budget_ms)
       .def_readwrite("status_ptr", &GemmOpts::status_ptr)
       .def_readwrite("max_ctas", &GemmOpts::max_ctas);

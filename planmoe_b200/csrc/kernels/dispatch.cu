@@ -49,22 +49,28 @@ struct PushGeom {
   unsigned long long flag_off;           // byte offset of the u64 flag array [chunks][W]
   unsigned long long scale_off;          // byte offset of the fp32 (scale,bias) rows (int8 mode)
   int W, my_rank, E_local, C, chunks;
+  int chunk_begin, chunk_count;          // chunks served by this launch
 };
 
 template <class T, bool QUANT>
-__global__ void __launch_bounds__(kRowThreads)
+__global__ void __launch_bounds__(kRowThreads, 6)
 scatter_rows_kernel(const T* __restrict__ x, const int* __restrict__ slot_map,
                     const float* __restrict__ gates, T* __restrict__ local_out, int K, int S,
                     int M, PushGeom g) {
-  // grid: (ctas_per_msg, W, chunks); message (r, j) = slots of rank r's experts in chunk j.
-  // The chunk is the slowest grid dimension so that chunk 0 leaves first for every destination.
-  const int r = blockIdx.y, j = blockIdx.z;
+  // 1-D persistent grid.  Chunks are served in order (chunk 0 leaves first for every destination),
+  // destinations start at my right-hand neighbour so that ranks do not all hit the same peer at once.
+  // After a chunk has been stored for all destinations the CTA fences once and adds one arrival to the
+  // chunk's flag on every destination: a flag is complete when all gridDim.x CTAs have arrived.
+  // The register bound keeps one such CTA co-resident with a GEMM CTA on the same SM.
   const int Cc = g.C / g.chunks;
   const int rows = g.E_local * Cc;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int V = Vec16<T>::N;
   const int nvec = M / V;
 
+  for (int j = g.chunk_begin; j < g.chunk_begin + g.chunk_count; ++j) {
+  for (int rr = 0; rr < g.W; ++rr) {
+  const int r = g.heap_bases != nullptr ? (g.my_rank + 1 + rr) % g.W : rr;
   unsigned char* dst_base;
   if (g.heap_bases != nullptr) {
     dst_base = reinterpret_cast<unsigned char*>(g.heap_bases[r]) + g.data_off;
@@ -146,15 +152,19 @@ scatter_rows_kernel(const T* __restrict__ x, const int* __restrict__ slot_map,
     }
   }
 
+  }  // destinations
+
   if (g.heap_bases != nullptr && g.flag_off != ~0ull) {
     __syncthreads();
-    if (threadIdx.x == 0) {
-      __threadfence_system();
+    if (threadIdx.x == 0) __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < g.W) {
       unsigned long long* flags = reinterpret_cast<unsigned long long*>(
-          reinterpret_cast<unsigned char*>(g.heap_bases[r]) + g.flag_off);
+          reinterpret_cast<unsigned char*>(g.heap_bases[threadIdx.x]) + g.flag_off);
       red_release_sys_add(flags + (size_t)j * g.W + g.my_rank, 1ull);
     }
   }
+  }  // chunks
 }
 
 template <class T>
@@ -165,21 +175,21 @@ void launch_scatter_rows(const T* x, const int* slot_map, const float* gates, T*
   int ctas;
   if (push == nullptr) {
     g.heap_bases = nullptr; g.data_off = 0; g.flag_off = ~0ull; g.scale_off = 0;
-    g.W = 1; g.my_rank = 0; g.E_local = E; g.C = C; g.chunks = 1;
+    g.W = 1; g.my_rank = 0; g.E_local = E; g.C = C; g.chunks = 1; g.chunk_begin = 0; g.chunk_count = 1;
     ctas = (E * C + kRowWarps - 1) / kRowWarps;
-    if (ctas > 148 * 8) ctas = 148 * 8;
+    if (ctas > 148 * 6) ctas = 148 * 6;
   } else {
     g.heap_bases = push->heap_bases; g.data_off = push->data_off; g.flag_off = push->flag_off;
     g.scale_off = push->scale_off;
     g.W = push->W; g.my_rank = push->my_rank; g.E_local = E / push->W; g.C = C; g.chunks = push->chunks;
-    ctas = push->ctas_per_msg;
+    g.chunk_begin = push->chunk_begin; g.chunk_count = push->chunk_count > 0 ? push->chunk_count : push->chunks;
+    ctas = push->ctas_per_msg;       // total CTAs of the persistent grid (= arrivals per flag)
   }
   if (ctas < 1) ctas = 1;
-  dim3 grid(ctas, g.W, g.chunks);
   if (quant)
-    scatter_rows_kernel<T, true><<<grid, kRowThreads, 0, stream>>>(x, slot_map, gates, local_out, K, S, M, g);
+    scatter_rows_kernel<T, true><<<ctas, kRowThreads, 0, stream>>>(x, slot_map, gates, local_out, K, S, M, g);
   else
-    scatter_rows_kernel<T, false><<<grid, kRowThreads, 0, stream>>>(x, slot_map, gates, local_out, K, S, M, g);
+    scatter_rows_kernel<T, false><<<ctas, kRowThreads, 0, stream>>>(x, slot_map, gates, local_out, K, S, M, g);
 }
 
 // ------------------------------------------------------------------------------------------

@@ -56,7 +56,9 @@ constexpr uint32_t kSmemRing = kStages * kStageBytes;
 constexpr uint32_t kSmemStaging = kEpiWarps * kStagingPerWarp;
 constexpr uint32_t kSmemBias = BN * 4;
 constexpr uint32_t kSmemBars = 256;
-constexpr uint32_t kSmemTotal = kSmemRing + kSmemStaging + kSmemBias + kSmemBars + 1024;  // + align slack
+// No alignment slack: the dynamic shared array is declared 1024-byte aligned.  The total leaves room
+// on the SM for one small co-resident CTA of a copy kernel (shared memory is reserved per CTA in KiB).
+constexpr uint32_t kSmemTotal = kSmemRing + kSmemStaging + kSmemBias + kSmemBars;
 constexpr uint32_t kTmemCols = 512;
 
 // ---------------------------------------------------------------------------------------------
@@ -171,6 +173,9 @@ struct KernelParams {
   const unsigned long long* gate_flags; int gate_rows; unsigned long long gate_want;
   const unsigned long long* heap_bases; unsigned long long push_data_off, push_flag_off;
   int push_rows, push_C, push_c0, push_chunk, W, my_rank;
+  // chunk_groups > 0: groups are [chunk][expert] with chunk_groups experts; weights / bias are indexed
+  // by the expert, flags and push offsets by the chunk.
+  int chunk_groups;
   unsigned long long budget_ns; int* status;
 };
 
@@ -248,8 +253,12 @@ template <bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const KernelParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if ((smem_u32(smem) & 1023u) != 0u) {            // swizzled tiles need 1024-byte aligned stages
+    if (threadIdx.x == 0) report_status(p.status, kStatusBadArgument, 1024, (int)(smem_u32(smem) & 1023u), 0);
+    return;
+  }
   uint8_t* ring = smem;
   uint8_t* staging = smem + kSmemRing;
   float* bias_s = reinterpret_cast<float*>(smem + kSmemRing + kSmemStaging);
@@ -289,11 +298,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const int mt = (tile / nt_count) % mt_count;
         const int g = tile / (nt_count * mt_count);
         const int m0 = mt * BM, n0 = nt * BN;
+        const int gb = p.chunk_groups > 0 ? g % p.chunk_groups : g;      // group of the B operand
         if (p.gate_flags != nullptr) {
           const int last_row = min(m0 + BM, p.M) - 1;
           const int s_lo = m0 / p.gate_rows, s_hi = last_row / p.gate_rows;
           for (int s = s_lo; s <= s_hi && ok; ++s)
-            ok = wait_flag_ge(p.gate_flags + s, p.gate_want, p.budget_ns, p.status, s);
+            ok = wait_flag_ge(p.gate_flags + (p.chunk_groups > 0 ? (g / p.chunk_groups) * p.W : 0) + s, p.gate_want,
+                              p.budget_ns, p.status, s);
           if (!ok) { ctl->abort = 1; break; }
           fence_proxy_async();   // peers' generic-proxy stores -> this thread's async-proxy loads
         }
@@ -313,10 +324,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             for (int i = 0; i < BM / 64; ++i) tma_load_4d(sa + i * (64 * BK * 2), &tmA, full, m0 + i * 64, k0, g, chunk);
           }
           if constexpr (!B_MN) {
-            tma_load_4d(sb, &tmB, full, k0, n0, g, chunk);
+            tma_load_4d(sb, &tmB, full, k0, n0, gb, chunk);
           } else {
 #pragma unroll
-            for (int i = 0; i < BN / 64; ++i) tma_load_4d(sb + i * (64 * BK * 2), &tmB, full, n0 + i * 64, k0, g, chunk);
+            for (int i = 0; i < BN / 64; ++i) tma_load_4d(sb + i * (64 * BK * 2), &tmB, full, n0 + i * 64, k0, gb, chunk);
           }
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
@@ -403,7 +414,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       ++iter;
       for (int i = etid; i < BN; i += kEpiWarps * 32) {
         float b = 0.f;
-        if (p.bias != nullptr && n0 + i < p.N) b = __bfloat162float(p.bias[(long long)g * p.bias_group_stride + n0 + i]);
+        if (p.bias != nullptr && n0 + i < p.N)
+          b = __bfloat162float(p.bias[(long long)(p.chunk_groups > 0 ? g % p.chunk_groups : g) * p.bias_group_stride + n0 + i]);
         bias_s[i] = b;
       }
       epi_bar_sync();
@@ -495,7 +507,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               const int s = m / p.push_rows, cc = m - s * p.push_rows;
               __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(
                   reinterpret_cast<uint8_t*>(p.heap_bases[s]) + p.push_data_off);
-              const long long drow = ((long long)p.my_rank * p.groups + g) * p.push_C + p.push_c0 + cc;
+              const int el = p.chunk_groups > 0 ? g % p.chunk_groups : g;
+              const int nel = p.chunk_groups > 0 ? p.chunk_groups : p.groups;
+              const int c_base = p.chunk_groups > 0 ? (g / p.chunk_groups) * p.push_rows : p.push_c0;
+              const long long drow = ((long long)p.my_rank * nel + el) * p.push_C + c_base + cc;
               *reinterpret_cast<uint4*>(base + drow * p.N + nb + c * 8) = val;
             }
           }
@@ -520,7 +535,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           for (int s = s_lo; s <= s_hi; ++s) {
             unsigned long long* flags = reinterpret_cast<unsigned long long*>(
                 reinterpret_cast<uint8_t*>(p.heap_bases[s]) + p.push_flag_off);
-            red_release_sys_add(flags + (long long)p.push_chunk * p.W + p.my_rank, 1ull);
+            const int chunk = p.chunk_groups > 0 ? g / p.chunk_groups : p.push_chunk;
+            red_release_sys_add(flags + (long long)chunk * p.W + p.my_rank, 1ull);
           }
         }
       }
@@ -619,7 +635,8 @@ cudaError_t launch_grouped_gemm(const GemmArgs& a, cudaStream_t stream) {
 
   CUtensorMap ta, tb;
   if (!make_map(&ta, a.A, a.groups, a.A.mn_major ? BK : BM)) return cudaErrorInvalidValue;
-  if (!make_map(&tb, a.B, a.groups, a.B.mn_major ? BK : BN)) return cudaErrorInvalidValue;
+  const int b_groups = a.chunk_groups > 0 ? a.chunk_groups : a.groups;
+  if (!make_map(&tb, a.B, b_groups, a.B.mn_major ? BK : BN)) return cudaErrorInvalidValue;
 
   KernelParams kp{};
   kp.groups = a.groups; kp.M = a.M; kp.N = a.N; kp.K = a.K;
@@ -632,6 +649,7 @@ cudaError_t launch_grouped_gemm(const GemmArgs& a, cudaStream_t stream) {
   kp.heap_bases = a.heap_bases; kp.push_data_off = a.push_data_off; kp.push_flag_off = a.push_flag_off;
   kp.push_rows = a.push_rows > 0 ? a.push_rows : a.M; kp.push_C = a.push_C; kp.push_c0 = a.push_c0;
   kp.push_chunk = a.push_chunk; kp.W = a.W; kp.my_rank = a.my_rank;
+  kp.chunk_groups = a.chunk_groups;
   kp.budget_ns = a.budget_ns ? a.budget_ns : 20000000000ull;
   kp.status = a.status;
 

@@ -27,7 +27,9 @@ struct PushArgs {
   unsigned long long data_off;           // destination buffer
   unsigned long long flag_off;           // u64 flags [chunks][W] on the destination rank
   unsigned long long scale_off;          // fp32 (range, lo) per row, int8 mode only
-  int W, my_rank, chunks, ctas_per_msg;
+  int W, my_rank, chunks;
+  int ctas_per_msg;                      // CTAs of the persistent grid = arrivals each flag receives
+  int chunk_begin, chunk_count;          // chunks served by this launch (count 0 = all)
 };
 struct WaitArgs {
   const unsigned long long* flags;  // local device pointer, n_flags consecutive u64
@@ -119,6 +121,11 @@ struct GemmArgs {
   // and flag (push_flag_off)[push_chunk * W + my_rank] on rank s is incremented once per tile.
   const unsigned long long* heap_bases; unsigned long long push_data_off, push_flag_off;
   int push_rows, push_C, push_c0, push_chunk, W, my_rank;
+  // chunk_groups > 0: the `groups` of A / D / aux are [chunk][expert] with chunk_groups experts per
+  // chunk; B and bias are indexed by the expert (group % chunk_groups); gate flags are
+  // gate_flags[chunk * W + s]; pushed rows land at column offset chunk * push_rows and signal
+  // flag [chunk * W + my_rank].  One launch then covers all pipeline chunks.
+  int chunk_groups;
   unsigned long long budget_ns; int* status;
   int max_ctas;                    // 0 = one per SM
 };

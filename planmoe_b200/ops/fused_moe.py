@@ -78,6 +78,13 @@ class FusedState:
         self.tr = T.get_transport(layer.group)
         self.sets = {}
         self.turn = {}
+        self._comm = None
+
+    def comm_stream(self):
+        """Side stream of the dispatch / combine-backward copy kernels."""
+        if self._comm is None:
+            self._comm = torch.cuda.Stream(device=self.tr.device)
+        return self._comm
 
     def acquire(self, key):
         ring = self.sets.setdefault(key, [])
@@ -99,9 +106,9 @@ class FusedState:
         return bs
 
 
-def _send_ctas(rows_per_msg, n_msgs):
-    """CTAs per (chunk, destination) message: about four waves of 148 SMs in total."""
-    return max(1, min((rows_per_msg + 7) // 8, max(1, 592 // max(n_msgs, 1))))
+def _send_ctas():
+    """CTAs of the persistent dispatch kernel: one per SM, so that each can sit next to a GEMM CTA."""
+    return int(torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count)
 
 
 class _Lease:
@@ -159,29 +166,37 @@ class _FusedExperts(torch.autograd.Function):
         budget, status = tr.budget_ms, tr.status_ptr
         gates_f = gates.detach().contiguous()
 
-        # ---- dispatch: push my tokens into the experts' home ranks ---------------------------
-        ctas = _send_ctas(E_l * Cc, d * W)
-        lib.scatter_push(x, slot_map, None if postscore else gates_f, K, E, C, bases, bs.off_x,
-                         bs.flag_off(PH_DISPATCH), W, rank, d, ctas)
+        # ---- dispatch: push my tokens into the experts' home ranks, on the side stream ------------
+        # The copy kernel and the GEMM below run concurrently: the GEMM starts a tile as soon as the
+        # flags of the source ranks it reads have arrived, chunk by chunk.
+        ctas = _send_ctas()
+        cur = torch.cuda.current_stream()
+        comm = st.comm_stream()
+        comm.wait_stream(cur)
+        with torch.cuda.stream(comm):
+            lib.scatter_push(x, slot_map, None if postscore else gates_f, K, E, C, bases, bs.off_x,
+                             bs.flag_off(PH_DISPATCH), W, rank, d, ctas, 0, d)
+        for t in (x, slot_map, gates_f):
+            t.record_stream(comm)
         bs.arrived[PH_DISPATCH] += ctas
         want_x = bs.arrived[PH_DISPATCH]
 
-        recv_x = bs.view(bs.off_x, (d, E_l, R, M))
-        pre = torch.empty((d, E_l, R, H), dtype=x.dtype, device=x.device)
-        h = torch.empty_like(pre)
+        recv_x = bs.view(bs.off_x, (d * E_l, R, M))
+        dact = torch.empty((d * E_l, R, H), dtype=x.dtype, device=x.device)
+        h = torch.empty_like(dact)
         push_arrivals = lib.gemm_push_arrivals(E_l, R, O, Cc, rank)
-        for j in range(d):
-            # GEMM 1: rows of source rank s are readable once flag[j][s] has arrived
-            grouped_gemm(recv_x[j], False, w1, True, EPI_BIAS_ACT, act, bias=b1, aux=pre[j], out=h[j],
-                         gate_flags_ptr=bs.flag_ptr(PH_DISPATCH, j), gate_rows=Cc, gate_want=want_x,
-                         budget_ms=budget, status_ptr=status)
-            # GEMM 2: epilogue pushes rows to the token owners' combine buffers
-            grouped_gemm(h[j], False, w2, True, EPI_PUSH, 0, bias=b2,
-                         heap_bases_ptr=bases, push_data_off=bs.off_y,
-                         push_flag_off=bs.flag_off(PH_COMBINE), push_rows=Cc, push_C=C, push_c0=j * Cc,
-                         push_chunk=j, W=W, my_rank=rank, budget_ms=budget, status_ptr=status)
+        # GEMM 1 over all chunks: rows of (chunk j, source s) are readable once flag[j][s] has arrived
+        grouped_gemm(recv_x, False, w1, True, EPI_BIAS_ACT, act, bias=b1, aux=dact, out=h,
+                     gate_flags_ptr=bs.flag_ptr(PH_DISPATCH, 0), gate_rows=Cc, gate_want=want_x,
+                     chunk_groups=E_l, W=W, my_rank=rank, budget_ms=budget, status_ptr=status)
+        # GEMM 2 over all chunks: the epilogue pushes rows to the token owners' combine buffers
+        grouped_gemm(h, False, w2, True, EPI_PUSH, 0, bias=b2,
+                     heap_bases_ptr=bases, push_data_off=bs.off_y,
+                     push_flag_off=bs.flag_off(PH_COMBINE), push_rows=Cc, push_C=C,
+                     chunk_groups=E_l, W=W, my_rank=rank, budget_ms=budget, status_ptr=status)
         bs.arrived[PH_COMBINE] += push_arrivals
         want_y = bs.arrived[PH_COMBINE]
+        cur.wait_stream(comm)
 
         # ---- combine: wait for every (chunk, expert rank) flag, gate-weighted sum over k ---------
         # flags of chunks 0..d-1 are consecutive: [d][W]
@@ -190,7 +205,7 @@ class _FusedExperts(torch.autograd.Function):
                               budget, status)
 
         ctx.meta, ctx.bs = meta, bs
-        ctx.save_for_backward(x, gates_f, w1, w2, pre, h)
+        ctx.save_for_backward(x, gates_f, w1, w2, dact, h)
         ctx.dims = (W, rank, E, C, d, K, E_l, Cc, S, M, H, O, R)
         ctx.lease = _Lease(bs)
         return out
@@ -199,7 +214,7 @@ class _FusedExperts(torch.autograd.Function):
     def backward(ctx, dout):
         lib = native.lib()
         meta, bs = ctx.meta, ctx.bs
-        x, gates_f, w1, w2, pre, h = ctx.saved_tensors
+        x, gates_f, w1, w2, dact, h = ctx.saved_tensors
         W, rank, E, C, d, K, E_l, Cc, S, M, H, O, R = ctx.dims
         st, idx, loc, slot_map = meta['state'], meta['idx'], meta['loc'], meta['slot_map']
         tr = st.tr
@@ -213,33 +228,40 @@ class _FusedExperts(torch.autograd.Function):
         if postscore and ctx.needs_input_grad[1]:
             dgates = lib.dispatch_gate_grad(recv_y, dout, idx, loc, C)
 
-        # ---- combine backward: push dY (gate-weighted) to the experts' home ranks ------------
-        ctas = _send_ctas(E_l * Cc, d * W)
-        lib.scatter_push(dout, slot_map, gates_f if postscore else None, K, E, C, bases, bs.off_dy,
-                         bs.flag_off(PH_COMBINE_BWD), W, rank, d, ctas)
+        # ---- combine backward: push dY (gate-weighted) to the experts' home ranks (side stream) ---
+        ctas = _send_ctas()
+        cur = torch.cuda.current_stream()
+        comm = st.comm_stream()
+        comm.wait_stream(cur)
+        with torch.cuda.stream(comm):
+            lib.scatter_push(dout, slot_map, gates_f if postscore else None, K, E, C, bases, bs.off_dy,
+                             bs.flag_off(PH_COMBINE_BWD), W, rank, d, ctas, 0, d)
+        dout.record_stream(comm)
         bs.arrived[PH_COMBINE_BWD] += ctas
         want_dy = bs.arrived[PH_COMBINE_BWD]
 
-        recv_dy = bs.view(bs.off_dy, (d, E_l, R, O))
-        recv_x = bs.view(bs.off_x, (d, E_l, R, M))
-        dh = torch.empty_like(pre)
+        recv_dy = bs.view(bs.off_dy, (d * E_l, R, O))
+        recv_x = bs.view(bs.off_x, (d * E_l, R, M))
+        dh = torch.empty_like(dact)
         push_arrivals = lib.gemm_push_arrivals(E_l, R, M, Cc, rank)
-        for j in range(d):
-            grouped_gemm(recv_dy[j], False, w2, False, EPI_DACT, act, aux=pre[j], out=dh[j],
-                         gate_flags_ptr=bs.flag_ptr(PH_COMBINE_BWD, j), gate_rows=Cc, gate_want=want_dy,
-                         budget_ms=budget, status_ptr=status)
-            grouped_gemm(dh[j], False, w1, False, EPI_PUSH, 0,
-                         heap_bases_ptr=bases, push_data_off=bs.off_dx,
-                         push_flag_off=bs.flag_off(PH_DISPATCH_BWD), push_rows=Cc, push_C=C, push_c0=j * Cc,
-                         push_chunk=j, W=W, my_rank=rank, budget_ms=budget, status_ptr=status)
+        # dH = (dY . W2^T) * act'  — flag-gated on the arriving dY rows
+        grouped_gemm(recv_dy, False, w2, False, EPI_DACT, act, aux=dact, out=dh,
+                     gate_flags_ptr=bs.flag_ptr(PH_COMBINE_BWD, 0), gate_rows=Cc, gate_want=want_dy,
+                     chunk_groups=E_l, W=W, my_rank=rank, budget_ms=budget, status_ptr=status)
+        # dX slots = dH . W1^T, pushed back to the token owners
+        grouped_gemm(dh, False, w1, False, EPI_PUSH, 0,
+                     heap_bases_ptr=bases, push_data_off=bs.off_dx,
+                     push_flag_off=bs.flag_off(PH_DISPATCH_BWD), push_rows=Cc, push_C=C,
+                     chunk_groups=E_l, W=W, my_rank=rank, budget_ms=budget, status_ptr=status)
         bs.arrived[PH_DISPATCH_BWD] += push_arrivals
         want_dx = bs.arrived[PH_DISPATCH_BWD]
+        cur.wait_stream(comm)
 
         # ---- weight / bias gradients: contract over all chunks in one launch each ---------------
-        dw2 = grouped_gemm(h, True, recv_dy, True, EPI_STORE)
-        dw1 = grouped_gemm(recv_x, True, dh, True, EPI_STORE)
-        db2 = lib.colsum(recv_dy.view(d * E_l, R, O)).view(d, E_l, O).sum(0).to(w2.dtype)
-        db1 = lib.colsum(dh.view(d * E_l, R, H)).view(d, E_l, H).sum(0).to(w1.dtype)
+        dw2 = grouped_gemm(h.view(d, E_l, R, H), True, recv_dy.view(d, E_l, R, O), True, EPI_STORE)
+        dw1 = grouped_gemm(recv_x.view(d, E_l, R, M), True, dh.view(d, E_l, R, H), True, EPI_STORE)
+        db2 = lib.colsum(recv_dy).view(d, E_l, O).sum(0).to(w2.dtype)
+        db1 = lib.colsum(dh).view(d, E_l, H).sum(0).to(w1.dtype)
 
         # ---- dispatch backward: wait for the returned slots, gather (gate-weighted if pre-score)
         dx = lib.gather_wait(bs.block.local_ptr + (bs.off_dx - bs.block.offset), dout.dtype, M, idx, loc,
