@@ -44,17 +44,54 @@ def parse():
 
 
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+    """SM clock and throttle reasons of one GPU, sampled while the timed region runs.
+
+    Reads NVML from a background thread every 5 ms (a timed region of a few tens of milliseconds
+    still gets samples); falls back to ``nvidia-smi -lms 200`` when NVML cannot be loaded.  Only
+    reads: no clock, power or mode setting is touched."""
     Q = ('index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,'
          'clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,'
          'clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap')
 
-    def __init__(self, gpu_index):
+    def __init__(self, gpu_index, uuid=None):
         self.idx = gpu_index
+        self.uuid = uuid
         self.proc = None
         self.path = None
+        self.thread = None
+        self.samples = []          # (sm_mhz, reasons bitmask)
+        self.max_mhz = None
+        self._stop = False
+
+    def _nvml_loop(self, nv, h):
+        while not self._stop:
+            try:
+                self.samples.append((nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM),
+                                     nv.nvmlDeviceGetCurrentClocksEventReasons(h)))
+            except Exception:
+                pass
+            time.sleep(0.005)
 
     def start(self):
+        try:
+            import threading
+            import pynvml as nv
+            nv.nvmlInit()
+            h = None
+            if self.uuid:
+                try:
+                    h = nv.nvmlDeviceGetHandleByUUID(('GPU-' + str(self.uuid)).encode())
+                except Exception:
+                    h = None
+            if h is None:
+                h = nv.nvmlDeviceGetHandleByIndex(self.idx)
+            self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+            self.nv = nv
+            self.thread = threading.Thread(target=self._nvml_loop, args=(nv, h), daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
         try:
             fd, self.path = tempfile.mkstemp(suffix='.csv')
             os.close(fd)
@@ -67,6 +104,24 @@ class ClockSampler:
 
     def stop(self):
         res = {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': [], 'samples': 0}
+        if self.thread is not None:
+            self._stop = True
+            self.thread.join(timeout=2)
+            nv = self.nv
+            bits = {'hw_slowdown': nv.nvmlClocksEventReasonHwSlowdown,
+                    'hw_thermal_slowdown': nv.nvmlClocksEventReasonHwThermalSlowdown,
+                    'sw_thermal_slowdown': nv.nvmlClocksEventReasonSwThermalSlowdown,
+                    'sw_power_cap': nv.nvmlClocksEventReasonSwPowerCap}
+            sm = [float(c) for c, _ in self.samples]
+            reasons = set()
+            for _, r in self.samples:
+                for n, b in bits.items():
+                    if r & b:
+                        reasons.add(n)
+            if sm:
+                res.update(sm_mhz=statistics.median(sm), sm_max_mhz=self.max_mhz, reasons=sorted(reasons),
+                           samples=len(sm), source='nvml')
+            return res
         if self.proc is None:
             return res
         try:
@@ -95,7 +150,8 @@ class ClockSampler:
                     reasons.add(n)
         if sm:
             hi = sorted(sm)[len(sm) // 2:]          # upper half = samples under load
-            res.update(sm_mhz=statistics.median(hi), sm_max_mhz=mx, reasons=sorted(reasons), samples=len(sm))
+            res.update(sm_mhz=statistics.median(hi), sm_max_mhz=mx, reasons=sorted(reasons), samples=len(sm),
+                       source='nvidia-smi')
         return res
 
 
@@ -230,9 +286,13 @@ def main():
     for _ in range(max(args.warmup, 3)):
         step(x_dev)
     barrier()
+    if args.impl == 'ours':
+        # a bounded wait that expired during warm-up ends the run here instead of timing garbage
+        from planmoe_b200.parallel import transport
+        transport.get_transport(None).check()
 
     # ---- device-timed region -------------------------------------------------------------
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(local_rank, getattr(torch.cuda.get_device_properties(device), 'uuid', None))
     if rank == 0:
         sampler.start()
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
@@ -246,6 +306,7 @@ def main():
         ends[i].record()
     barrier()
     launches = launch_count() - l0
+    clocks = sampler.stop() if rank == 0 else None
     ms = sum(s.elapsed_time(e) for s, e in zip(starts, ends))
 
     # ---- end-to-end region: pinned H2D of the input + D2H of the loss, every step ---------------
@@ -262,7 +323,6 @@ def main():
     e2e_e.record()
     barrier()
     e2e_ms = e2e_s.elapsed_time(e2e_e)
-    clocks = sampler.stop() if rank == 0 else None
 
     if args.impl == 'ours':
         from planmoe_b200.parallel import transport

@@ -254,6 +254,10 @@ struct GemmOpts {
   int64_t heap_bases_ptr = 0, push_data_off = 0, push_flag_off = 0, push_rows = 0, push_C = 0, push_c0 = 0,
           push_chunk = 0, W = 1, my_rank = 0, chunk_groups = 0;
   int64_t budget_ms = 0, status_ptr = 0, max_ctas = 0;
+  // dispatch send fused into the launch (copy role)
+  c10::optional<Tensor> copy_x, copy_slot_map, copy_gates;
+  int64_t copy_K = 0, copy_E_local = 0, copy_C = 0, copy_chunks = 0, copy_ctas = 0, copy_data_off = 0,
+          copy_flag_off = 0;
 };
 
 GemmOperand operand_of(const Tensor& t, bool mn_major) {
@@ -322,6 +326,27 @@ Tensor grouped_gemm_op(const Tensor& A, bool a_mn, const Tensor& B, bool b_mn, c
   g.status = reinterpret_cast<int*>(o.status_ptr);
   g.max_ctas = o.max_ctas;
   if (o.epilogue == kEpiPush) TORCH_CHECK(g.heap_bases != nullptr, "push epilogue needs heap bases");
+  if (o.copy_ctas > 0) {
+    TORCH_CHECK(o.copy_x.has_value() && o.copy_slot_map.has_value(), "copy role needs x and slot_map");
+    const Tensor& cx = *o.copy_x;
+    const Tensor& sm = *o.copy_slot_map;
+    TORCH_CHECK(cx.is_cuda() && cx.scalar_type() == at::kBFloat16 && cx.dim() == 2 && cx.is_contiguous(),
+                "copy role: x must be contiguous bf16 [S, M]");
+    TORCH_CHECK(sm.is_cuda() && sm.scalar_type() == at::kInt && sm.is_contiguous(), "copy role: slot_map must be int32");
+    TORCH_CHECK(g.heap_bases != nullptr && o.copy_K > 0 && o.copy_E_local > 0 && o.copy_C > 0 && o.copy_chunks > 0,
+                "copy role: incomplete geometry");
+    TORCH_CHECK(sm.numel() == o.copy_E_local * o.W * o.copy_C, "copy role: slot_map size");
+    g.copy.x = cx.data_ptr(); g.copy.slot_map = sm.data_ptr<int>();
+    g.copy.S = cx.size(0); g.copy.M = cx.size(1);
+    if (o.copy_gates.has_value() && o.copy_gates->defined()) {
+      const Tensor& cg = *o.copy_gates;
+      TORCH_CHECK(cg.is_cuda() && cg.scalar_type() == at::kFloat && cg.is_contiguous() &&
+                  cg.numel() == o.copy_K * cx.size(0), "copy role: gates must be fp32 [K, S]");
+      g.copy.gates = cg.data_ptr<float>();
+    }
+    g.copy.K = o.copy_K; g.copy.E_local = o.copy_E_local; g.copy.C = o.copy_C; g.copy.chunks = o.copy_chunks;
+    g.copy.ctas = o.copy_ctas; g.copy.data_off = o.copy_data_off; g.copy.flag_off = o.copy_flag_off;
+  }
   check_cuda(launch_grouped_gemm(g, cur_stream()), "grouped_gemm");
   return out;
 }
@@ -560,7 +585,17 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_readwrite("chunk_groups", &GemmOpts::chunk_groups)
       .def_readwrite("budget_ms", &GemmOpts::budget_ms)
       .def_readwrite("status_ptr", &GemmOpts::status_ptr)
-      .def_readwrite("max_ctas", &GemmOpts::max_ctas);
+      .def_readwrite("max_ctas", &GemmOpts::max_ctas)
+      .def_readwrite("copy_x", &GemmOpts::copy_x)
+      .def_readwrite("copy_slot_map", &GemmOpts::copy_slot_map)
+      .def_readwrite("copy_gates", &GemmOpts::copy_gates)
+      .def_readwrite("copy_K", &GemmOpts::copy_K)
+      .def_readwrite("copy_E_local", &GemmOpts::copy_E_local)
+      .def_readwrite("copy_C", &GemmOpts::copy_C)
+      .def_readwrite("copy_chunks", &GemmOpts::copy_chunks)
+      .def_readwrite("copy_ctas", &GemmOpts::copy_ctas)
+      .def_readwrite("copy_data_off", &GemmOpts::copy_data_off)
+      .def_readwrite("copy_flag_off", &GemmOpts::copy_flag_off);
   m.def("grouped_gemm", &grouped_gemm_op);
   m.def("tensor_from_ptr", [](int64_t ptr, int64_t nbytes, int64_t device) {
     return torch::from_blob(reinterpret_cast<void*>(ptr), {nbytes},

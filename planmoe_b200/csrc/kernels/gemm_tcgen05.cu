@@ -177,6 +177,7 @@ struct KernelParams {
   // by the expert, flags and push offsets by the chunk.
   int chunk_groups;
   unsigned long long budget_ns; int* status;
+  GemmArgs::CopyJob copy;        // copy.ctas > 0: the first copy.ctas CTAs run the dispatch send
 };
 
 struct Ctl {
@@ -249,6 +250,95 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Copy role: the dispatch send, run by the first copy.ctas CTAs of the launch while the other CTAs
+// compute.  Slot-major gather of token rows (optionally gate-weighted), stored with full-line
+// 16-byte stores straight into the receive buffer [chunk][E_local][W_src][C/chunks][M] of the rank
+// that owns the expert.  Chunks leave in order; after a chunk has been stored for every destination
+// the CTA fences once and adds one arrival to the (chunk, my_rank) flag of every destination.  The
+// role never waits on anything, so it cannot be part of a circular wait.  Each warp keeps two rows
+// (up to 16 x 16 bytes per lane) in flight to cover the load latency.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint4 scale_bf16x8(uint4 v, float g) {
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 f = __bfloat1622float2(h[i]);
+    h[i] = __floats2bfloat162_rn(f.x * g, f.y * g);
+  }
+  return v;
+}
+
+__device__ __noinline__ void copy_role(const KernelParams& p) {
+  const GemmArgs::CopyJob& c = p.copy;
+  constexpr int kWarps = kThreads / 32;
+  constexpr int U = 8;                               // 16-byte vectors per lane per row and pass
+  const int Cc = c.C / c.chunks;
+  const int rows = c.E_local * Cc;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nvec = c.M >> 3;
+  const int wid = blockIdx.x * kWarps + warp, nw = c.ctas * kWarps;
+  const uint4* x = reinterpret_cast<const uint4*>(c.x);
+
+  for (int j = 0; j < c.chunks; ++j) {
+    for (int rr = 0; rr < p.W; ++rr) {
+      // destinations start at my right-hand neighbour, staggered by CTA so that all links are busy
+      const int r = (p.my_rank + 1 + rr + (int)blockIdx.x) % p.W;
+      uint4* dst_base = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.heap_bases[r]) + c.data_off);
+      for (int row0 = wid; row0 < rows; row0 += 2 * nw) {
+        const uint4* src[2];
+        uint4* dst[2];
+        float gw[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int row = row0 + h * nw;
+          src[h] = nullptr; dst[h] = nullptr; gw[h] = 1.f;
+          if (row < rows) {
+            const int el = row / Cc, cc = row - el * Cc;
+            const int owner = c.slot_map[(size_t)(r * c.E_local + el) * c.C + j * Cc + cc];
+            dst[h] = dst_base + ((((size_t)j * c.E_local + el) * p.W + p.my_rank) * Cc + cc) * nvec;
+            if (owner >= 0) {
+              const int t = owner / c.K, k = owner - t * c.K;
+              src[h] = x + (size_t)t * nvec;
+              if (c.gates != nullptr) gw[h] = c.gates[(size_t)k * c.S + t];
+            }
+          }
+        }
+        for (int v0 = 0; v0 < nvec; v0 += 32 * U) {
+          uint4 buf[2][U];
+#pragma unroll
+          for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int i = 0; i < U; ++i) {
+              const int v = v0 + i * 32 + lane;
+              buf[h][i] = make_uint4(0, 0, 0, 0);
+              if (src[h] != nullptr && v < nvec) buf[h][i] = __ldg(src[h] + v);
+            }
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            if (dst[h] == nullptr) continue;
+            const bool scaled = gw[h] != 1.f;
+#pragma unroll
+            for (int i = 0; i < U; ++i) {
+              const int v = v0 + i * 32 + lane;
+              if (v < nvec) dst[h][v] = scaled ? scale_bf16x8(buf[h][i], gw[h]) : buf[h][i];
+            }
+          }
+        }
+      }
+    }
+    // chunk j stored everywhere: publish it
+    __syncthreads();
+    if (threadIdx.x == 0) __threadfence_system();
+    __syncthreads();
+    if ((int)threadIdx.x < p.W) {
+      unsigned long long* flags = reinterpret_cast<unsigned long long*>(
+          reinterpret_cast<uint8_t*>(p.heap_bases[threadIdx.x]) + c.flag_off);
+      red_release_sys_add(flags + (size_t)j * p.W + p.my_rank, 1ull);
+    }
+  }
+}
+
 template <bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -259,6 +349,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (threadIdx.x == 0) report_status(p.status, kStatusBadArgument, 1024, (int)(smem_u32(smem) & 1023u), 0);
     return;
   }
+  if ((int)blockIdx.x < p.copy.ctas) {             // dispatch send fused into this launch
+    copy_role(p);
+    return;
+  }
+  const int cta = (int)blockIdx.x - p.copy.ctas, ncta = (int)gridDim.x - p.copy.ctas;
   uint8_t* ring = smem;
   uint8_t* staging = smem + kSmemRing;
   float* bias_s = reinterpret_cast<float*>(smem + kSmemRing + kSmemStaging);
@@ -293,7 +388,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+      for (int tile = cta; tile < tiles && ok; tile += ncta) {
         const int nt = tile % nt_count;
         const int mt = (tile / nt_count) % mt_count;
         const int g = tile / (nt_count * mt_count);
@@ -341,7 +436,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       constexpr uint32_t idesc = make_idesc(A_MN, B_MN);
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+      for (int tile = cta; tile < tiles && ok; tile += ncta) {
         ok = mbar_wait(smem_u32(&ctl->acc_empty[acc]), acc_phase ^ 1u, ctl, p.budget_ns, p.status, 1, 100 + acc);
         if (!ok) break;
         tc_fence_after();
@@ -381,7 +476,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int etid = threadIdx.x - 64;            // 0..255
     uint32_t acc = 0, acc_phase = 0, iter = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+    for (int tile = cta; tile < tiles && ok; tile += ncta) {
       const int nt = tile % nt_count;
       const int mt = (tile / nt_count) % mt_count;
       const int g = tile / (nt_count * mt_count);
@@ -652,6 +747,14 @@ cudaError_t launch_grouped_gemm(const GemmArgs& a, cudaStream_t stream) {
   kp.chunk_groups = a.chunk_groups;
   kp.budget_ns = a.budget_ns ? a.budget_ns : 20000000000ull;
   kp.status = a.status;
+  kp.copy = a.copy;
+  if (kp.copy.ctas > 0) {
+    if (kp.copy.x == nullptr || kp.copy.slot_map == nullptr || a.heap_bases == nullptr || (kp.copy.M % 8) ||
+        kp.copy.chunks <= 0 || (kp.copy.C % kp.copy.chunks) || (reinterpret_cast<uintptr_t>(kp.copy.x) % 16))
+      return cudaErrorInvalidValue;
+  } else {
+    kp.copy.ctas = 0;
+  }
 
   static int sm_count = 0;
   if (sm_count == 0) {
@@ -661,8 +764,15 @@ cudaError_t launch_grouped_gemm(const GemmArgs& a, cudaStream_t stream) {
     if (sm_count <= 0) sm_count = 148;
   }
   const int tiles = a.groups * ((a.M + BM - 1) / BM) * ((a.N + BN - 1) / BN);
+  // Copy-role CTAs come first in the grid (they are dispatched first and never wait); together with
+  // the compute CTAs they fill the machine once, so all of them are resident at the same time.
   int ctas = a.max_ctas > 0 ? a.max_ctas : sm_count;
+  if (kp.copy.ctas > 0) {
+    if (kp.copy.ctas > ctas - 1) kp.copy.ctas = ctas - 1;
+    ctas -= kp.copy.ctas;
+  }
   if (ctas > tiles) ctas = tiles;
+  ctas += kp.copy.ctas;
 
   if (!a.A.mn_major && a.B.mn_major) return launch_variant<false, true>(ta, tb, kp, ctas, stream);
   if (!a.A.mn_major && !a.B.mn_major) return launch_variant<false, false>(ta, tb, kp, ctas, stream);

@@ -128,6 +128,19 @@ struct GemmArgs {
   int chunk_groups;
   unsigned long long budget_ns; int* status;
   int max_ctas;                    // 0 = one per SM
+  // Fused dispatch send ("copy role"): copy.ctas > 0 adds that many CTAs to the same launch.  They
+  // gather token rows of copy.x by slot map (optionally gate-weighted) and store them straight into
+  // the receive buffer of the rank that owns each expert, chunk by chunk, then release-add the
+  // (chunk, my_rank) flag on every destination (copy.ctas arrivals per flag).  The GEMM CTAs of the
+  // launch are the flag-gated consumers of the same exchange, so the transfer and the math overlap
+  // inside one kernel.  Uses heap_bases / W / my_rank above.
+  struct CopyJob {
+    const void* x;                 // bf16 [S][M]
+    const int* slot_map;           // [E_global * C] -> token * K + k, or -1
+    const float* gates;            // fp32 [K][S] or null
+    int K, S, M, E_local, C, chunks, ctas;
+    unsigned long long data_off, flag_off;   // destination buffer / u64 flags [chunks][W] in the heap
+  } copy;
 };
 
 // Returns cudaSuccess or the launch / tensor-map error.

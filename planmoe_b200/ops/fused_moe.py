@@ -28,6 +28,8 @@ Flags are never reset: each use adds a known number of arrivals, receivers wait 
 cumulative count.
 """
 
+import os
+
 import torch
 import torch.nn.functional as F
 
@@ -60,6 +62,10 @@ class _BufferSet:
         self.arrived = [0, 0, 0, 0]               # cumulative arrivals expected per flag, per phase
         self.held = False
 
+    def off_of(self, phase):
+        """Heap offset of the receive buffer the given phase writes."""
+        return (self.off_x, self.off_y, self.off_dy, self.off_dx)[phase]
+
     def flag_off(self, phase):
         return self.off_flags + phase * MAX_CHUNKS * self.W * 8
 
@@ -78,13 +84,6 @@ class FusedState:
         self.tr = T.get_transport(layer.group)
         self.sets = {}
         self.turn = {}
-        self._comm = None
-
-    def comm_stream(self):
-        """Side stream of the dispatch / combine-backward copy kernels."""
-        if self._comm is None:
-            self._comm = torch.cuda.Stream(device=self.tr.device)
-        return self._comm
 
     def acquire(self, key):
         ring = self.sets.setdefault(key, [])
@@ -106,9 +105,43 @@ class FusedState:
         return bs
 
 
-def _send_ctas():
-    """CTAs of the persistent dispatch kernel: one per SM, so that each can sit next to a GEMM CTA."""
-    return int(torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count)
+_SM_COUNT = {}
+
+
+def _sm_count():
+    dev = torch.cuda.current_device()
+    if dev not in _SM_COUNT:
+        _SM_COUNT[dev] = int(torch.cuda.get_device_properties(dev).multi_processor_count)
+    return _SM_COUNT[dev]
+
+
+def _copy_ctas(world):
+    """CTAs of a flag-gated GEMM launch that run the dispatch send (copy role) instead of computing.
+    0 = no overlap: a separate copy kernel runs first on the whole machine, which is the faster choice
+    with one rank, where nothing crosses NVLink.  With peers the copy CTAs and the compute CTAs belong to
+    one launch, so they are resident together by construction and the transfer overlaps the math."""
+    env = os.environ.get('PLANMOE_COPY_CTAS')
+    if env is not None:
+        return max(0, min(int(env), _sm_count() - 1))
+    return 0 if world <= 1 else 20
+
+
+def _send_and_gemm(lib, bs, phase, src, slot_map, gates, K, E, C, W, rank, d, gemm):
+    """Dispatch-style push of ``src`` plus the flag-gated GEMM that consumes it.  ``gemm(want, **copy)``
+    enqueues the GEMM gated on ``want`` arrivals per (chunk, source) flag."""
+    bases = bs.block.bases_ptr
+    n_copy = _copy_ctas(W)
+    if n_copy == 0:
+        ctas = 4 * _sm_count()
+        lib.scatter_push(src, slot_map, gates, K, E, C, bases, bs.off_of(phase), bs.flag_off(phase), W, rank, d,
+                         ctas, 0, d)
+        bs.arrived[phase] += ctas
+        gemm(bs.arrived[phase])
+    else:
+        bs.arrived[phase] += n_copy
+        gemm(bs.arrived[phase], heap_bases_ptr=bases, copy_x=src, copy_slot_map=slot_map, copy_gates=gates,
+             copy_K=K, copy_E_local=E // W, copy_C=C, copy_chunks=d, copy_ctas=n_copy,
+             copy_data_off=bs.off_of(phase), copy_flag_off=bs.flag_off(phase))
 
 
 class _Lease:
@@ -166,29 +199,20 @@ class _FusedExperts(torch.autograd.Function):
         budget, status = tr.budget_ms, tr.status_ptr
         gates_f = gates.detach().contiguous()
 
-        # ---- dispatch: push my tokens into the experts' home ranks, on the side stream ------------
-        # The copy kernel and the GEMM below run concurrently: the GEMM starts a tile as soon as the
-        # flags of the source ranks it reads have arrived, chunk by chunk.
-        ctas = _send_ctas()
-        cur = torch.cuda.current_stream()
-        comm = st.comm_stream()
-        comm.wait_stream(cur)
-        with torch.cuda.stream(comm):
-            lib.scatter_push(x, slot_map, None if postscore else gates_f, K, E, C, bases, bs.off_x,
-                             bs.flag_off(PH_DISPATCH), W, rank, d, ctas, 0, d)
-        for t in (x, slot_map, gates_f):
-            t.record_stream(comm)
-        bs.arrived[PH_DISPATCH] += ctas
-        want_x = bs.arrived[PH_DISPATCH]
-
+        # ---- dispatch + GEMM 1 ---------------------------------------------------------------------
+        # The copy kernel stores my tokens into the experts' home ranks chunk by chunk; GEMM 1 covers all
+        # chunks in one launch and starts a tile as soon as the flags of the (chunk, source) rows it reads
+        # have arrived.  With more than one rank the two run concurrently.
         recv_x = bs.view(bs.off_x, (d * E_l, R, M))
         dact = torch.empty((d * E_l, R, H), dtype=x.dtype, device=x.device)
         h = torch.empty_like(dact)
+
+        def gemm1(want, **copy):
+            grouped_gemm(recv_x, False, w1, True, EPI_BIAS_ACT, act, bias=b1, aux=dact, out=h,
+                         gate_flags_ptr=bs.flag_ptr(PH_DISPATCH, 0), gate_rows=Cc, gate_want=want,
+                         chunk_groups=E_l, W=W, my_rank=rank, budget_ms=budget, status_ptr=status, **copy)
+        _send_and_gemm(lib, bs, PH_DISPATCH, x, slot_map, None if postscore else gates_f, K, E, C, W, rank, d, gemm1)
         push_arrivals = lib.gemm_push_arrivals(E_l, R, O, Cc, rank)
-        # GEMM 1 over all chunks: rows of (chunk j, source s) are readable once flag[j][s] has arrived
-        grouped_gemm(recv_x, False, w1, True, EPI_BIAS_ACT, act, bias=b1, aux=dact, out=h,
-                     gate_flags_ptr=bs.flag_ptr(PH_DISPATCH, 0), gate_rows=Cc, gate_want=want_x,
-                     chunk_groups=E_l, W=W, my_rank=rank, budget_ms=budget, status_ptr=status)
         # GEMM 2 over all chunks: the epilogue pushes rows to the token owners' combine buffers
         grouped_gemm(h, False, w2, True, EPI_PUSH, 0, bias=b2,
                      heap_bases_ptr=bases, push_data_off=bs.off_y,
@@ -196,7 +220,6 @@ class _FusedExperts(torch.autograd.Function):
                      chunk_groups=E_l, W=W, my_rank=rank, budget_ms=budget, status_ptr=status)
         bs.arrived[PH_COMBINE] += push_arrivals
         want_y = bs.arrived[PH_COMBINE]
-        cur.wait_stream(comm)
 
         # ---- combine: wait for every (chunk, expert rank) flag, gate-weighted sum over k ---------
         # flags of chunks 0..d-1 are consecutive: [d][W]
@@ -228,26 +251,19 @@ class _FusedExperts(torch.autograd.Function):
         if postscore and ctx.needs_input_grad[1]:
             dgates = lib.dispatch_gate_grad(recv_y, dout, idx, loc, C)
 
-        # ---- combine backward: push dY (gate-weighted) to the experts' home ranks (side stream) ---
-        ctas = _send_ctas()
-        cur = torch.cuda.current_stream()
-        comm = st.comm_stream()
-        comm.wait_stream(cur)
-        with torch.cuda.stream(comm):
-            lib.scatter_push(dout, slot_map, gates_f if postscore else None, K, E, C, bases, bs.off_dy,
-                             bs.flag_off(PH_COMBINE_BWD), W, rank, d, ctas, 0, d)
-        dout.record_stream(comm)
-        bs.arrived[PH_COMBINE_BWD] += ctas
-        want_dy = bs.arrived[PH_COMBINE_BWD]
-
+        # ---- combine backward: push dY (gate-weighted) + flag-gated dgrad 2 ---------------------------
         recv_dy = bs.view(bs.off_dy, (d * E_l, R, O))
         recv_x = bs.view(bs.off_x, (d * E_l, R, M))
         dh = torch.empty_like(dact)
+
+        def dgrad2(want, **copy):
+            # dH = (dY . W2^T) * act'
+            grouped_gemm(recv_dy, False, w2, False, EPI_DACT, act, aux=dact, out=dh,
+                         gate_flags_ptr=bs.flag_ptr(PH_COMBINE_BWD, 0), gate_rows=Cc, gate_want=want,
+                         chunk_groups=E_l, W=W, my_rank=rank, budget_ms=budget, status_ptr=status, **copy)
+        _send_and_gemm(lib, bs, PH_COMBINE_BWD, dout, slot_map, gates_f if postscore else None, K, E, C, W, rank, d,
+                       dgrad2)
         push_arrivals = lib.gemm_push_arrivals(E_l, R, M, Cc, rank)
-        # dH = (dY . W2^T) * act'  — flag-gated on the arriving dY rows
-        grouped_gemm(recv_dy, False, w2, False, EPI_DACT, act, aux=dact, out=dh,
-                     gate_flags_ptr=bs.flag_ptr(PH_COMBINE_BWD, 0), gate_rows=Cc, gate_want=want_dy,
-                     chunk_groups=E_l, W=W, my_rank=rank, budget_ms=budget, status_ptr=status)
         # dX slots = dH . W1^T, pushed back to the token owners
         grouped_gemm(dh, False, w1, False, EPI_PUSH, 0,
                      heap_bases_ptr=bases, push_data_off=bs.off_dx,
@@ -255,7 +271,6 @@ class _FusedExperts(torch.autograd.Function):
                      chunk_groups=E_l, W=W, my_rank=rank, budget_ms=budget, status_ptr=status)
         bs.arrived[PH_DISPATCH_BWD] += push_arrivals
         want_dx = bs.arrived[PH_DISPATCH_BWD]
-        cur.wait_stream(comm)
 
         # ---- weight / bias gradients: contract over all chunks in one launch each ---------------
         dw2 = grouped_gemm(h.view(d, E_l, R, H), True, recv_dy.view(d, E_l, R, O), True, EPI_STORE)
