@@ -253,7 +253,7 @@ struct GemmOpts {
   // push
   int64_t heap_bases_ptr = 0, push_data_off = 0, push_flag_off = 0, push_rows = 0, push_C = 0, push_c0 = 0,
           push_chunk = 0, W = 1, my_rank = 0, chunk_groups = 0;
-  int64_t budget_ms = 0, status_ptr = 0, max_ctas = 0;
+  int64_t budget_ms = 0, status_ptr = 0, max_ctas = 0, cta_group = 0;
   // dispatch send fused into the launch (copy role)
   c10::optional<Tensor> copy_x, copy_slot_map, copy_gates;
   int64_t copy_K = 0, copy_E_local = 0, copy_C = 0, copy_chunks = 0, copy_ctas = 0, copy_data_off = 0,
@@ -325,6 +325,7 @@ Tensor grouped_gemm_op(const Tensor& A, bool a_mn, const Tensor& B, bool b_mn, c
   g.budget_ns = (unsigned long long)o.budget_ms * 1000000ull;
   g.status = reinterpret_cast<int*>(o.status_ptr);
   g.max_ctas = o.max_ctas;
+  g.cta_group = o.cta_group;
   if (o.epilogue == kEpiPush) TORCH_CHECK(g.heap_bases != nullptr, "push epilogue needs heap bases");
   if (o.copy_ctas > 0) {
     TORCH_CHECK(o.copy_x.has_value() && o.copy_slot_map.has_value(), "copy role needs x and slot_map");
@@ -586,6 +587,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_readwrite("budget_ms", &GemmOpts::budget_ms)
       .def_readwrite("status_ptr", &GemmOpts::status_ptr)
       .def_readwrite("max_ctas", &GemmOpts::max_ctas)
+      .def_readwrite("cta_group", &GemmOpts::cta_group)
       .def_readwrite("copy_x", &GemmOpts::copy_x)
       .def_readwrite("copy_slot_map", &GemmOpts::copy_slot_map)
       .def_readwrite("copy_gates", &GemmOpts::copy_gates)
@@ -596,6 +598,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_readwrite("copy_ctas", &GemmOpts::copy_ctas)
       .def_readwrite("copy_data_off", &GemmOpts::copy_data_off)
       .def_readwrite("copy_flag_off", &GemmOpts::copy_flag_off);
+  m.def("gemm_grid_ctas", &gemm_grid_ctas, py::arg("groups"), py::arg("M"), py::arg("N"), py::arg("max_ctas") = 0,
+        py::arg("cta_group") = 0);
   m.def("grouped_gemm", &grouped_gemm_op);
   m.def("tensor_from_ptr", [](int64_t ptr, int64_t nbytes, int64_t device) {
     return torch::from_blob(reinterpret_cast<void*>(ptr), {nbytes},

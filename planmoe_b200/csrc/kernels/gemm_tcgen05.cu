@@ -2,7 +2,7 @@
 //
 //   D[g] (M x N) = A[g] (M x K) . B[g] (K x N)          g = 0 .. groups-1, fp32 accumulate
 //
-// Hand-written tcgen05 pipeline, one persistent CTA per SM, 320 threads in three roles:
+// Hand-written tcgen05 pipeline, one persistent CTA per SM, 384 threads in four roles:
 //   warp 0      TMA producer: cp.async.bulk.tensor (4-D maps, 128-byte swizzle) into a 4-stage
 //               shared-memory ring, completion on mbarriers.  When the A operand is a receive
 //               buffer that peer GPUs fill, the producer first acquire-waits (bounded) on the
@@ -16,6 +16,12 @@
 //               derivative) / multiply by a saved derivative -> bf16 -> swizzled shared-memory staging -> full-line 16-byte stores,
 //               either to local memory or straight into the combine buffer of the rank that
 //               owns the token ("push"), followed by a release-add on that rank's flag.
+//   warps 10,11 dispatch send (optional): while the tensor cores work, these two warps of every CTA
+//               gather token rows by slot map and store them straight into the receive buffers of
+//               the ranks that own the experts, chunk by chunk, then release-add the (chunk, rank)
+//               flags there.  The same launch's producers on every rank are the flag-gated
+//               consumers, so the all-to-all and the GEMM that follows it are one kernel and
+//               overlap tile by tile; the copy never waits, so no circular wait can form.
 //
 // Operands may be K-major or MN-major (weights are stored input-major, and the weight-gradient
 // GEMMs contract over the token dimension), so all four FFN GEMM flavours — forward, dgrad,
@@ -42,23 +48,33 @@ namespace planmoe {
 
 namespace {
 
-constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int BM = 128, BN = 256, BK = 64;       // BM = accumulator rows per CTA (TMEM lanes)
 constexpr int UMMA_K = 16;
-constexpr int kStages = 4;
 constexpr int kAccStages = 2;
-constexpr int kThreads = 320;
+constexpr int kThreads = 384;
+constexpr int kCopyWarps = 2;                     // warps 10 and 11
 constexpr int kEpiWarps = 8;
 constexpr uint32_t kABytes = BM * BK * 2;          // 16 KiB
-constexpr uint32_t kBBytes = BN * BK * 2;          // 32 KiB
-constexpr uint32_t kStageBytes = kABytes + kBBytes;
 constexpr uint32_t kStagingPerWarp = 32 * 128;     // one 32-row x 128-byte tile
-constexpr uint32_t kSmemRing = kStages * kStageBytes;
 constexpr uint32_t kSmemStaging = kEpiWarps * kStagingPerWarp;
 constexpr uint32_t kSmemBias = BN * 4;
 constexpr uint32_t kSmemBars = 256;
-// No alignment slack: the dynamic shared array is declared 1024-byte aligned.  The total leaves room
-// on the SM for one small co-resident CTA of a copy kernel (shared memory is reserved per CTA in KiB).
-constexpr uint32_t kSmemTotal = kSmemRing + kSmemStaging + kSmemBias + kSmemBars;
+
+// Per-CTA geometry by CTA-group size CG.  CG = 1: one CTA computes a 128 x 256 tile from a 16 KiB A
+// block and a 32 KiB B block per 64-deep K step.  CG = 2: a cluster of two CTAs computes a 256 x 256
+// tile with one tcgen05.mma.cta_group::2 stream issued by the even CTA; each CTA stages its own 128
+// rows of A and its own 128 of the 256 B columns (16 KiB each), so a K step costs 32 KiB of shared
+// memory traffic per CTA instead of 48 and the ring is 6 deep instead of 4.
+template <int CG> struct Geo {
+  static constexpr int kBRows = BN / CG;                        // B columns staged per CTA
+  static constexpr uint32_t kBBytes = kBRows * BK * 2;
+  static constexpr uint32_t kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = CG == 1 ? 4 : 6;
+  static constexpr uint32_t kSmemRing = kStages * kStageBytes;
+  // No alignment slack: the dynamic shared array is declared 1024-byte aligned.
+  static constexpr uint32_t kSmemTotal = kSmemRing + kSmemStaging + kSmemBias + kSmemBars;
+};
+constexpr int kMaxStages = 6;
 constexpr uint32_t kTmemCols = 512;
 
 // ---------------------------------------------------------------------------------------------
@@ -91,12 +107,23 @@ __device__ __forceinline__ void fence_barrier_init() {
 __device__ __forceinline__ void fence_proxy_async() {
   asm volatile("fence.proxy.async;" ::: "memory");
 }
+// TMA load into this CTA's shared memory.  `bar` is a shared::cluster address: the CTA's own barrier,
+// or (cta_group::2) the barrier of the even CTA of the pair, which collects the bytes of both CTAs.
+// No cluster multicast is used anywhere: every CTA fetches its own tiles.
+template <int CG>
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0,
                                             int c1, int c2, int c3) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%3, %4, %5, %6}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+  if constexpr (CG == 1) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+  } else {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+  }
 }
 __device__ __forceinline__ void tc_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -104,25 +131,66 @@ __device__ __forceinline__ void tc_fence_before() {
 __device__ __forceinline__ void tc_fence_after() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
+template <int CG>
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+  if constexpr (CG == 1)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+  else
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
 }
+template <int CG>
 __device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  if constexpr (CG == 1) asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  else                   asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
 }
+template <int CG>
 __device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+  if constexpr (CG == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+  else                   asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
 }
+template <int CG>
 __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                           uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+  if constexpr (CG == 1) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+  }
 }
+// Arrive on `bar` (a shared::cluster address, possibly in the other CTA of the pair) once every
+// tcgen05.mma issued so far by this thread has completed.
+template <int CG>
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+  if constexpr (CG == 1)
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+  else
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// ---- thread-block cluster helpers (CG = 2) ----
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* v) {
   asm volatile(
@@ -158,9 +226,9 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes
 // Instruction descriptor for kind::f16 with bf16 inputs and fp32 accumulation:
 //   [4,6) D format = 1 (f32), [7,10) A format = 1 (bf16), [10,13) B format = 1 (bf16),
 //   [15] A MN-major, [16] B MN-major, [17,23) N >> 3, [24,29) M >> 4.
-__host__ __device__ constexpr uint32_t make_idesc(bool a_mn, bool b_mn) {
+__host__ __device__ constexpr uint32_t make_idesc(bool a_mn, bool b_mn, int m) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
-         ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+         ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
 struct KernelParams {
@@ -181,8 +249,8 @@ struct KernelParams {
 };
 
 struct Ctl {
-  uint64_t full[kStages];
-  uint64_t empty[kStages];
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
   uint64_t acc_full[kAccStages];
   uint64_t acc_empty[kAccStages];
   uint32_t tmem_base;
@@ -251,13 +319,13 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// Copy role: the dispatch send, run by the first copy.ctas CTAs of the launch while the other CTAs
-// compute.  Slot-major gather of token rows (optionally gate-weighted), stored with full-line
-// 16-byte stores straight into the receive buffer [chunk][E_local][W_src][C/chunks][M] of the rank
-// that owns the expert.  Chunks leave in order; after a chunk has been stored for every destination
-// the CTA fences once and adds one arrival to the (chunk, my_rank) flag of every destination.  The
-// role never waits on anything, so it cannot be part of a circular wait.  Each warp keeps two rows
-// (up to 16 x 16 bytes per lane) in flight to cover the load latency.
+// Copy role (warps 10 and 11 of every CTA): the dispatch send.  Slot-major gather of token rows
+// (optionally gate-weighted), stored with full-line 16-byte stores straight into the receive buffer
+// [chunk][E_local][W_src][C/chunks][M] of the rank that owns the expert.  Chunks leave in order;
+// after a chunk has been stored for every destination the two warps meet on a named barrier, fence
+// once and add one arrival to the (chunk, my_rank) flag of every destination, so a flag is complete
+// after one arrival per CTA of the grid.  The role never waits on another CTA or rank.  Each warp
+// keeps two rows (16 x 16 bytes per lane) in flight to cover the load latency.
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint4 scale_bf16x8(uint4 v, float g) {
   __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
@@ -269,15 +337,15 @@ __device__ __forceinline__ uint4 scale_bf16x8(uint4 v, float g) {
   return v;
 }
 
-__device__ __noinline__ void copy_role(const KernelParams& p) {
+__device__ __noinline__ void copy_role(const KernelParams& p, int cwarp) {
   const GemmArgs::CopyJob& c = p.copy;
-  constexpr int kWarps = kThreads / 32;
   constexpr int U = 8;                               // 16-byte vectors per lane per row and pass
   const int Cc = c.C / c.chunks;
   const int rows = c.E_local * Cc;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int lane = threadIdx.x & 31;
+  const int ctid = cwarp * 32 + lane;                // 0 .. 63 inside the copy group
   const int nvec = c.M >> 3;
-  const int wid = blockIdx.x * kWarps + warp, nw = c.ctas * kWarps;
+  const int wid = (int)blockIdx.x * kCopyWarps + cwarp, nw = (int)gridDim.x * kCopyWarps;
   const uint4* x = reinterpret_cast<const uint4*>(c.x);
 
   for (int j = 0; j < c.chunks; ++j) {
@@ -327,41 +395,43 @@ __device__ __noinline__ void copy_role(const KernelParams& p) {
         }
       }
     }
-    // chunk j stored everywhere: publish it
-    __syncthreads();
-    if (threadIdx.x == 0) __threadfence_system();
-    __syncthreads();
-    if ((int)threadIdx.x < p.W) {
+    // chunk j stored everywhere by this CTA: publish it
+    asm volatile("bar.sync 2, 64;" ::: "memory");
+    if (ctid == 0) __threadfence_system();
+    asm volatile("bar.sync 2, 64;" ::: "memory");
+    if (ctid < p.W) {
       unsigned long long* flags = reinterpret_cast<unsigned long long*>(
-          reinterpret_cast<uint8_t*>(p.heap_bases[threadIdx.x]) + c.flag_off);
+          reinterpret_cast<uint8_t*>(p.heap_bases[ctid]) + c.flag_off);
       red_release_sys_add(flags + (size_t)j * p.W + p.my_rank, 1ull);
     }
   }
 }
 
-template <bool A_MN, bool B_MN, int EPI>
+template <int CG, bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const KernelParams p) {
+  using G = Geo<CG>;
+  constexpr int kStages = G::kStages;
+  constexpr uint32_t kStageBytes = G::kStageBytes;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
   if ((smem_u32(smem) & 1023u) != 0u) {            // swizzled tiles need 1024-byte aligned stages
     if (threadIdx.x == 0) report_status(p.status, kStatusBadArgument, 1024, (int)(smem_u32(smem) & 1023u), 0);
-    return;
+    return;                                        // same address in every CTA: the whole grid returns
   }
-  if ((int)blockIdx.x < p.copy.ctas) {             // dispatch send fused into this launch
-    copy_role(p);
-    return;
-  }
-  const int cta = (int)blockIdx.x - p.copy.ctas, ncta = (int)gridDim.x - p.copy.ctas;
+  // A work unit is one output tile of (CG * 128) x 256, computed by CG CTAs; `unit` / `nunits` number
+  // the CTA groups of the grid and `cr` is this CTA's rank inside its group (0 issues the MMAs).
+  const int cr = CG == 1 ? 0 : (int)cluster_ctarank();
+  const int unit = (int)blockIdx.x / CG, nunits = (int)gridDim.x / CG;
   uint8_t* ring = smem;
-  uint8_t* staging = smem + kSmemRing;
-  float* bias_s = reinterpret_cast<float*>(smem + kSmemRing + kSmemStaging);
-  Ctl* ctl = reinterpret_cast<Ctl*>(smem + kSmemRing + kSmemStaging + kSmemBias);
+  uint8_t* staging = smem + G::kSmemRing;
+  float* bias_s = reinterpret_cast<float*>(smem + G::kSmemRing + kSmemStaging);
+  Ctl* ctl = reinterpret_cast<Ctl*>(smem + G::kSmemRing + kSmemStaging + kSmemBias);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  const int mt_count = (p.M + BM - 1) / BM;
+  const int mt_count = (p.M + BM * CG - 1) / (BM * CG);
   const int nt_count = (p.N + BN - 1) / BN;
   const int tiles = p.groups * mt_count * nt_count;
   const int kb_per_chunk = (p.K + BK - 1) / BK;
@@ -369,17 +439,21 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(smem_u32(&ctl->full[s]), 1); mbar_init(smem_u32(&ctl->empty[s]), 1); }
-    for (int a = 0; a < kAccStages; ++a) { mbar_init(smem_u32(&ctl->acc_full[a]), 1); mbar_init(smem_u32(&ctl->acc_empty[a]), kEpiWarps); }
+    for (int a = 0; a < kAccStages; ++a) {
+      mbar_init(smem_u32(&ctl->acc_full[a]), 1);
+      mbar_init(smem_u32(&ctl->acc_empty[a]), kEpiWarps * CG);     // the epilogue warps of every CTA of the group
+    }
     ctl->abort = 0;
     ctl->epi_abort[0] = ctl->epi_abort[1] = 0;
     fence_barrier_init();
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
-    tmem_relinquish();
+    tmem_alloc<CG>(smem_u32(&ctl->tmem_base), kTmemCols);
+    tmem_relinquish<CG>();
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (CG == 2) cluster_sync_all();       // the partner's barriers are initialised before anyone signals them
   tc_fence_after();
   const uint32_t tmem_base = ctl->tmem_base;
 
@@ -388,13 +462,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      for (int tile = cta; tile < tiles && ok; tile += ncta) {
+      for (int tile = unit; tile < tiles && ok; tile += nunits) {
         const int nt = tile % nt_count;
         const int mt = (tile / nt_count) % mt_count;
         const int g = tile / (nt_count * mt_count);
-        const int m0 = mt * BM, n0 = nt * BN;
+        const int m0 = mt * (BM * CG) + cr * BM;                         // my 128 rows of the tile
+        const int n0 = nt * BN + cr * G::kBRows;                         // my share of the B columns
         const int gb = p.chunk_groups > 0 ? g % p.chunk_groups : g;      // group of the B operand
-        if (p.gate_flags != nullptr) {
+        if (p.gate_flags != nullptr && m0 < p.M) {
           const int last_row = min(m0 + BM, p.M) - 1;
           const int s_lo = m0 / p.gate_rows, s_hi = last_row / p.gate_rows;
           for (int s = s_lo; s <= s_hi && ok; ++s)
@@ -406,23 +481,26 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         for (int kb = 0; kb < kb_total; ++kb) {
           ok = mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1u, ctl, p.budget_ns, p.status, 0, stage);
           if (!ok) break;
-          const uint32_t full = smem_u32(&ctl->full[stage]);
+          // bytes of every CTA of the group complete on the barrier of the CTA that issues the MMAs
+          uint32_t full = smem_u32(&ctl->full[stage]);
+          if constexpr (CG == 2) full = map_to_cta(full, 0);
           const uint32_t sa = smem_u32(ring + stage * kStageBytes);
           const uint32_t sb = sa + kABytes;
           const int chunk = kb / kb_per_chunk;
           const int k0 = (kb - chunk * kb_per_chunk) * BK;
-          mbar_expect_tx(full, kStageBytes);
+          if (cr == 0) mbar_expect_tx(smem_u32(&ctl->full[stage]), kStageBytes * CG);
           if constexpr (!A_MN) {
-            tma_load_4d(sa, &tmA, full, k0, m0, g, chunk);
+            tma_load_4d<CG>(sa, &tmA, full, k0, m0, g, chunk);
           } else {
 #pragma unroll
-            for (int i = 0; i < BM / 64; ++i) tma_load_4d(sa + i * (64 * BK * 2), &tmA, full, m0 + i * 64, k0, g, chunk);
+            for (int i = 0; i < BM / 64; ++i) tma_load_4d<CG>(sa + i * (64 * BK * 2), &tmA, full, m0 + i * 64, k0, g, chunk);
           }
           if constexpr (!B_MN) {
-            tma_load_4d(sb, &tmB, full, k0, n0, gb, chunk);
+            tma_load_4d<CG>(sb, &tmB, full, k0, n0, gb, chunk);
           } else {
 #pragma unroll
-            for (int i = 0; i < BN / 64; ++i) tma_load_4d(sb + i * (64 * BK * 2), &tmB, full, n0 + i * 64, k0, gb, chunk);
+            for (int i = 0; i < G::kBRows / 64; ++i)
+              tma_load_4d<CG>(sb + i * (64 * BK * 2), &tmB, full, n0 + i * 64, k0, gb, chunk);
           }
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
@@ -431,12 +509,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     __syncwarp();
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(A_MN, B_MN);
+    // ------------------------------------------------------------------ MMA issuer (rank 0 of the group)
+    if (lane == 0 && cr == 0) {
+      constexpr uint32_t idesc = make_idesc(A_MN, B_MN, BM * CG);
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;
-      for (int tile = cta; tile < tiles && ok; tile += ncta) {
+      for (int tile = unit; tile < tiles && ok; tile += nunits) {
         ok = mbar_wait(smem_u32(&ctl->acc_empty[acc]), acc_phase ^ 1u, ctl, p.budget_ns, p.status, 1, 100 + acc);
         if (!ok) break;
         tc_fence_after();
@@ -454,17 +532,23 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             else                 adesc = make_desc(sa + k * (UMMA_K * 128), 64 * BK * 2, 1024);
             if constexpr (!B_MN) bdesc = make_desc(sb + k * (UMMA_K * 2), 16, 1024);
             else                 bdesc = make_desc(sb + k * (UMMA_K * 128), 64 * BK * 2, 1024);
-            umma_bf16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_bf16<CG>(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
           }
-          umma_commit(smem_u32(&ctl->empty[stage]));
+          // the ring stage is free again in every CTA of the group once these MMAs have read it
+          umma_commit<CG>(smem_u32(&ctl->empty[stage]));
+          if constexpr (CG == 2) umma_commit<CG>(map_to_cta(smem_u32(&ctl->empty[stage]), 1));
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
-        umma_commit(smem_u32(&ctl->acc_full[acc]));
+        umma_commit<CG>(smem_u32(&ctl->acc_full[acc]));
+        if constexpr (CG == 2) umma_commit<CG>(map_to_cta(smem_u32(&ctl->acc_full[acc]), 1));
         if (++acc == kAccStages) { acc = 0; acc_phase ^= 1u; }
       }
     }
     __syncwarp();
+  } else if (warp >= 2 + kEpiWarps) {
+    // ------------------------------------------------------------------ dispatch send (2 warps)
+    if (p.copy.ctas > 0) copy_role(p, warp - (2 + kEpiWarps));
   } else {
     // ------------------------------------------------------------------ epilogue warps (8)
     // Warp pairs share a TMEM lane quarter (warp % 4); each warp of a pair drains one 128-column
@@ -476,11 +560,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int etid = threadIdx.x - 64;            // 0..255
     uint32_t acc = 0, acc_phase = 0, iter = 0;
     bool ok = true;
-    for (int tile = cta; tile < tiles && ok; tile += ncta) {
+    for (int tile = unit; tile < tiles && ok; tile += nunits) {
       const int nt = tile % nt_count;
       const int mt = (tile / nt_count) % mt_count;
       const int g = tile / (nt_count * mt_count);
-      const int m0 = mt * BM, n0 = nt * BN;
+      const int m0 = mt * (BM * CG) + cr * BM, n0 = nt * BN;
 
       // Activation backward: the 32 x 64 slab of saved activation derivatives this warp needs first
       // is requested before the accumulator is awaited, so its latency hides behind the main loop.
@@ -618,7 +702,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       // accumulator drained: hand the TMEM stage back to the MMA warp
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&ctl->acc_empty[acc]));
+      if (lane == 0) {
+        if constexpr (CG == 1) mbar_arrive(smem_u32(&ctl->acc_empty[acc]));
+        else                   mbar_arrive_cluster(map_to_cta(smem_u32(&ctl->acc_empty[acc]), 0));
+      }
       if (++acc == kAccStages) { acc = 0; acc_phase ^= 1u; }
 
       if constexpr (EPI == kEpiPush) {
@@ -641,9 +728,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   // ---------------------------------------------------------------------- teardown
   tc_fence_before();
   __syncthreads();
+  if constexpr (CG == 2) cluster_sync_all();       // nobody leaves while its partner may still touch it
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, kTmemCols);
+    tmem_dealloc<CG>(tmem_base, kTmemCols);
   }
 }
 
@@ -684,33 +772,116 @@ bool make_map(CUtensorMap* map, const GemmOperand& op, int groups, int box_rows)
   return r == CUDA_SUCCESS;
 }
 
-template <bool A_MN, bool B_MN, int EPI>
+template <int CG, bool A_MN, bool B_MN, int EPI>
 cudaError_t launch_epi(const CUtensorMap& ta, const CUtensorMap& tb, const KernelParams& kp, int ctas,
                        cudaStream_t stream) {
-  auto kern = grouped_gemm_kernel<A_MN, B_MN, EPI>;
+  auto kern = grouped_gemm_kernel<CG, A_MN, B_MN, EPI>;
+  constexpr int smem = (int)Geo<CG>::kSmemTotal;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTotal);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  kern<<<ctas, kThreads, kSmemTotal, stream>>>(ta, tb, kp);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)ctas, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CG; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = CG > 1 ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, ta, tb, kp);
 }
 
-template <bool A_MN, bool B_MN>
+template <int CG, bool A_MN, bool B_MN>
 cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const KernelParams& kp, int ctas,
                            cudaStream_t stream) {
   switch (kp.epilogue) {
-    case kEpiStore: return launch_epi<A_MN, B_MN, kEpiStore>(ta, tb, kp, ctas, stream);
-    case kEpiBiasAct: return launch_epi<A_MN, B_MN, kEpiBiasAct>(ta, tb, kp, ctas, stream);
-    case kEpiDAct: return launch_epi<A_MN, B_MN, kEpiDAct>(ta, tb, kp, ctas, stream);
-    case kEpiPush: return launch_epi<A_MN, B_MN, kEpiPush>(ta, tb, kp, ctas, stream);
+    case kEpiStore: return launch_epi<CG, A_MN, B_MN, kEpiStore>(ta, tb, kp, ctas, stream);
+    case kEpiBiasAct: return launch_epi<CG, A_MN, B_MN, kEpiBiasAct>(ta, tb, kp, ctas, stream);
+    case kEpiDAct: return launch_epi<CG, A_MN, B_MN, kEpiDAct>(ta, tb, kp, ctas, stream);
+    case kEpiPush: return launch_epi<CG, A_MN, B_MN, kEpiPush>(ta, tb, kp, ctas, stream);
     default: return cudaErrorInvalidValue;
   }
 }
 
+template <int CG>
+cudaError_t launch_layout(const GemmArgs& a, const CUtensorMap& ta, const CUtensorMap& tb, const KernelParams& kp,
+                          int ctas, cudaStream_t stream) {
+  if (!a.A.mn_major && a.B.mn_major) return launch_variant<CG, false, true>(ta, tb, kp, ctas, stream);
+  if (!a.A.mn_major && !a.B.mn_major) return launch_variant<CG, false, false>(ta, tb, kp, ctas, stream);
+  if (a.A.mn_major && a.B.mn_major) return launch_variant<CG, true, true>(ta, tb, kp, ctas, stream);
+  return launch_variant<CG, true, false>(ta, tb, kp, ctas, stream);
+}
+
+// Largest number of two-CTA clusters of this kernel that can be resident at once.  A persistent grid
+// must not exceed it: CTAs that wait on flags fed by the copy warps of *every* CTA of the grid would
+// otherwise wait for CTAs that cannot start before they finish.
+int max_pair_units() {
+  static int units = 0;
+  if (units == 0) {
+    auto kern = grouped_gemm_kernel<2, false, true, kEpiStore>;
+    int n = 0;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = Geo<2>::kSmemTotal;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Geo<2>::kSmemTotal) != cudaSuccess ||
+        cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = 0;
+    }
+    units = n > 0 ? n : -1;
+  }
+  return units;
+}
+
+int sm_count_cached() {
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (sm_count <= 0) sm_count = 148;
+  }
+  return sm_count;
+}
+
 }  // namespace
+
+// CTA-group size of a launch: 2 (a two-CTA cluster per 256 x 256 tile) unless the problem has at most
+// 128 rows per group, where the second CTA of a pair would only compute padding, or the caller or the
+// environment variable PLANMOE_GEMM_CTA_GROUP asks for 1.
+int gemm_cta_group(int M, int requested) {
+  static int env = -1;
+  if (env < 0) {
+    const char* e = getenv("PLANMOE_GEMM_CTA_GROUP");
+    env = (e != nullptr && (e[0] == '1' || e[0] == '2')) ? e[0] - '0' : 0;
+  }
+  if (requested == 1 || requested == 2) return requested;
+  if (env != 0) return env;
+  return M > BM ? 2 : 1;
+}
+
+int gemm_grid_ctas(int groups, int M, int N, int max_ctas, int cta_group) {
+  const int cg = gemm_cta_group(M, cta_group);
+  const long long tiles = (long long)groups * ((M + BM * cg - 1) / (BM * cg)) * ((N + BN - 1) / BN);
+  long long units = (max_ctas > 0 ? max_ctas : sm_count_cached()) / cg;
+  if (cg == 2) {
+    const int cap = max_pair_units();
+    if (cap > 0 && units > cap) units = cap;
+  }
+  if (units < 1) units = 1;
+  if (units > tiles) units = tiles;
+  return (int)(units * cg);
+}
 
 int gemm_push_arrivals(int groups, int M, int N, int push_rows, int s) {
   const int nt = (N + BN - 1) / BN;
@@ -727,11 +898,12 @@ cudaError_t launch_grouped_gemm(const GemmArgs& a, cudaStream_t stream) {
       (reinterpret_cast<uintptr_t>(a.A.ptr) % 16) || (reinterpret_cast<uintptr_t>(a.B.ptr) % 16))
     return cudaErrorInvalidValue;
   if (a.A.chunks != a.B.chunks) return cudaErrorInvalidValue;
+  const int cg = gemm_cta_group(a.M, a.cta_group);
 
   CUtensorMap ta, tb;
   if (!make_map(&ta, a.A, a.groups, a.A.mn_major ? BK : BM)) return cudaErrorInvalidValue;
   const int b_groups = a.chunk_groups > 0 ? a.chunk_groups : a.groups;
-  if (!make_map(&tb, a.B, b_groups, a.B.mn_major ? BK : BN)) return cudaErrorInvalidValue;
+  if (!make_map(&tb, a.B, b_groups, a.B.mn_major ? BK : BN / cg)) return cudaErrorInvalidValue;
 
   KernelParams kp{};
   kp.groups = a.groups; kp.M = a.M; kp.N = a.N; kp.K = a.K;
@@ -756,28 +928,13 @@ cudaError_t launch_grouped_gemm(const GemmArgs& a, cudaStream_t stream) {
     kp.copy.ctas = 0;
   }
 
-  static int sm_count = 0;
-  if (sm_count == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-    if (sm_count <= 0) sm_count = 148;
-  }
-  const int tiles = a.groups * ((a.M + BM - 1) / BM) * ((a.N + BN - 1) / BN);
-  // Copy-role CTAs come first in the grid (they are dispatched first and never wait); together with
-  // the compute CTAs they fill the machine once, so all of them are resident at the same time.
-  int ctas = a.max_ctas > 0 ? a.max_ctas : sm_count;
-  if (kp.copy.ctas > 0) {
-    if (kp.copy.ctas > ctas - 1) kp.copy.ctas = ctas - 1;
-    ctas -= kp.copy.ctas;
-  }
-  if (ctas > tiles) ctas = tiles;
-  ctas += kp.copy.ctas;
+  const int ctas = gemm_grid_ctas(a.groups, a.M, a.N, a.max_ctas, cg);
+  // With a copy job every CTA of the grid adds one arrival per (chunk, destination) flag; the caller
+  // computed its expected count from gemm_grid_ctas() and passes it back as copy.ctas.
+  if (kp.copy.ctas > 0 && kp.copy.ctas != ctas) return cudaErrorInvalidValue;
 
-  if (!a.A.mn_major && a.B.mn_major) return launch_variant<false, true>(ta, tb, kp, ctas, stream);
-  if (!a.A.mn_major && !a.B.mn_major) return launch_variant<false, false>(ta, tb, kp, ctas, stream);
-  if (a.A.mn_major && a.B.mn_major) return launch_variant<true, true>(ta, tb, kp, ctas, stream);
-  return launch_variant<true, false>(ta, tb, kp, ctas, stream);
+  if (cg == 2) return launch_layout<2>(a, ta, tb, kp, ctas, stream);
+  return launch_layout<1>(a, ta, tb, kp, ctas, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

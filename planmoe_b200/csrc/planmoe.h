@@ -128,12 +128,14 @@ struct GemmArgs {
   int chunk_groups;
   unsigned long long budget_ns; int* status;
   int max_ctas;                    // 0 = one per SM
-  // Fused dispatch send ("copy role"): copy.ctas > 0 adds that many CTAs to the same launch.  They
-  // gather token rows of copy.x by slot map (optionally gate-weighted) and store them straight into
-  // the receive buffer of the rank that owns each expert, chunk by chunk, then release-add the
-  // (chunk, my_rank) flag on every destination (copy.ctas arrivals per flag).  The GEMM CTAs of the
-  // launch are the flag-gated consumers of the same exchange, so the transfer and the math overlap
-  // inside one kernel.  Uses heap_bases / W / my_rank above.
+  int cta_group;                   // 0 = automatic (gemm_cta_group), 1, or 2 (two-CTA clusters, 256 x 256 tiles)
+  // Fused dispatch send ("copy role"): with copy.ctas > 0 two extra warps of every CTA gather token
+  // rows of copy.x by slot map (optionally gate-weighted) and store them straight into the receive
+  // buffer of the rank that owns each expert, chunk by chunk, then release-add the (chunk, my_rank)
+  // flag on every destination: one arrival per CTA, and copy.ctas must equal the grid size
+  // (gemm_grid_ctas).  The producers of the same launch on every rank are the flag-gated consumers of
+  // this exchange, so the transfer and the math overlap inside one kernel.  Uses heap_bases / W /
+  // my_rank above.
   struct CopyJob {
     const void* x;                 // bf16 [S][M]
     const int* slot_map;           // [E_global * C] -> token * K + k, or -1
@@ -145,6 +147,9 @@ struct GemmArgs {
 
 // Returns cudaSuccess or the launch / tensor-map error.
 cudaError_t launch_grouped_gemm(const GemmArgs& args, cudaStream_t stream);
+// CTAs the launch of such a problem uses (= arrivals per flag of a fused copy job).
+int gemm_cta_group(int M, int requested);
+int gemm_grid_ctas(int groups, int M, int N, int max_ctas, int cta_group);
 // Number of flag arrivals rank s receives per push launch (host helper for the receiver).
 int gemm_push_arrivals(int groups, int M, int N, int push_rows, int s);
 

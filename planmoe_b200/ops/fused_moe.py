@@ -115,32 +115,31 @@ def _sm_count():
     return _SM_COUNT[dev]
 
 
-def _copy_ctas(world):
-    """CTAs of a flag-gated GEMM launch that run the dispatch send (copy role) instead of computing.
-    0 = no overlap: a separate copy kernel runs first on the whole machine, which is the faster choice
-    with one rank, where nothing crosses NVLink.  With peers the copy CTAs and the compute CTAs belong to
-    one launch, so they are resident together by construction and the transfer overlaps the math."""
-    env = os.environ.get('PLANMOE_COPY_CTAS')
+def _fuse_send(world):
+    """Whether the dispatch send runs inside the flag-gated GEMM launch (two copy warps in every CTA).
+    With peers it does: transfer and math then overlap in one kernel.  With one rank nothing crosses
+    NVLink and a separate copy kernel on the whole machine, run first, is the default; the environment
+    variable PLANMOE_FUSE_SEND=0/1 overrides either way."""
+    env = os.environ.get('PLANMOE_FUSE_SEND')
     if env is not None:
-        return max(0, min(int(env), _sm_count() - 1))
-    return 0 if world <= 1 else 20
+        return env not in ('0', '', 'false')
+    return world > 1
 
 
-def _send_and_gemm(lib, bs, phase, src, slot_map, gates, K, E, C, W, rank, d, gemm):
+def _send_and_gemm(lib, bs, phase, src, slot_map, gates, K, E, C, W, rank, d, grid, gemm):
     """Dispatch-style push of ``src`` plus the flag-gated GEMM that consumes it.  ``gemm(want, **copy)``
-    enqueues the GEMM gated on ``want`` arrivals per (chunk, source) flag."""
+    enqueues the GEMM gated on ``want`` arrivals per (chunk, source) flag; ``grid`` is its CTA count."""
     bases = bs.block.bases_ptr
-    n_copy = _copy_ctas(W)
-    if n_copy == 0:
+    if not _fuse_send(W):
         ctas = 4 * _sm_count()
         lib.scatter_push(src, slot_map, gates, K, E, C, bases, bs.off_of(phase), bs.flag_off(phase), W, rank, d,
                          ctas, 0, d)
         bs.arrived[phase] += ctas
         gemm(bs.arrived[phase])
     else:
-        bs.arrived[phase] += n_copy
+        bs.arrived[phase] += grid
         gemm(bs.arrived[phase], heap_bases_ptr=bases, copy_x=src, copy_slot_map=slot_map, copy_gates=gates,
-             copy_K=K, copy_E_local=E // W, copy_C=C, copy_chunks=d, copy_ctas=n_copy,
+             copy_K=K, copy_E_local=E // W, copy_C=C, copy_chunks=d, copy_ctas=grid,
              copy_data_off=bs.off_of(phase), copy_flag_off=bs.flag_off(phase))
 
 
@@ -211,7 +210,8 @@ class _FusedExperts(torch.autograd.Function):
             grouped_gemm(recv_x, False, w1, True, EPI_BIAS_ACT, act, bias=b1, aux=dact, out=h,
                          gate_flags_ptr=bs.flag_ptr(PH_DISPATCH, 0), gate_rows=Cc, gate_want=want,
                          chunk_groups=E_l, W=W, my_rank=rank, budget_ms=budget, status_ptr=status, **copy)
-        _send_and_gemm(lib, bs, PH_DISPATCH, x, slot_map, None if postscore else gates_f, K, E, C, W, rank, d, gemm1)
+        _send_and_gemm(lib, bs, PH_DISPATCH, x, slot_map, None if postscore else gates_f, K, E, C, W, rank, d,
+                       lib.gemm_grid_ctas(d * E_l, R, H), gemm1)
         push_arrivals = lib.gemm_push_arrivals(E_l, R, O, Cc, rank)
         # GEMM 2 over all chunks: the epilogue pushes rows to the token owners' combine buffers
         grouped_gemm(h, False, w2, True, EPI_PUSH, 0, bias=b2,
@@ -262,7 +262,7 @@ class _FusedExperts(torch.autograd.Function):
                          gate_flags_ptr=bs.flag_ptr(PH_COMBINE_BWD, 0), gate_rows=Cc, gate_want=want,
                          chunk_groups=E_l, W=W, my_rank=rank, budget_ms=budget, status_ptr=status, **copy)
         _send_and_gemm(lib, bs, PH_COMBINE_BWD, dout, slot_map, gates_f if postscore else None, K, E, C, W, rank, d,
-                       dgrad2)
+                       lib.gemm_grid_ctas(d * E_l, R, H), dgrad2)
         push_arrivals = lib.gemm_push_arrivals(E_l, R, M, Cc, rank)
         # dX slots = dH . W1^T, pushed back to the token owners
         grouped_gemm(dh, False, w1, False, EPI_PUSH, 0,

@@ -21,6 +21,10 @@ import os
 EPI_STORE, EPI_BIAS_ACT, EPI_DACT, EPI_PUSH = 0, 1, 2, 3
 ACT_CODES = {'identity': 0, 'relu': 1, 'gelu': 2, 'silu': 3}
 
+# CTA-group size used when a call does not name one: 0 lets the native launcher decide (two-CTA
+# clusters unless a group has at most 128 rows, or PLANMOE_GEMM_CTA_GROUP overrides).
+DEFAULT_CTA_GROUP = 0
+
 _STATUS = None
 
 
@@ -55,6 +59,7 @@ def grouped_gemm(A, a_mn, B, b_mn, epilogue=EPI_STORE, activation=0, bias=None, 
     o = lib.GemmOpts()
     o.epilogue, o.activation = int(epilogue), int(activation)
     o.bias, o.aux, o.out = bias, aux, out
+    o.cta_group = DEFAULT_CTA_GROUP
     for k, v in extra.items():
         setattr(o, k, v)
     if 'status_ptr' not in extra:

@@ -25,10 +25,10 @@ def _layer(E, M, H, k, cf, act='gelu', **kw):
 
 @pytest.mark.parametrize("degree", [1, 2])
 @pytest.mark.parametrize("postscore", [True, False])
-@pytest.mark.parametrize("copy_ctas", [0, 12])
-def test_fused_layer_matches_fp32_reference(degree, postscore, copy_ctas, monkeypatch):
-    """``copy_ctas`` > 0 runs the dispatch send inside the flag-gated GEMM launch (copy role)."""
-    monkeypatch.setenv('PLANMOE_COPY_CTAS', str(copy_ctas))
+@pytest.mark.parametrize("fuse_send", [0, 1])
+def test_fused_layer_matches_fp32_reference(degree, postscore, fuse_send, monkeypatch):
+    """``fuse_send`` = 1 runs the dispatch send inside the flag-gated GEMM launch (copy warps)."""
+    monkeypatch.setenv('PLANMOE_FUSE_SEND', str(fuse_send))
     E, M, H, k, cf = 4, 256, 512, 2, 1.0
     layer = _layer(E, M, H, k, cf, is_postscore=postscore, a2a_ffn_overlap_degree=degree)
     layer.gates[0].wg.float()

@@ -44,33 +44,49 @@ def test_gemm_single_tile(a_mn, b_mn):
     _check(out, _ref_gemm(A, a_mn, B, b_mn))
 
 
+@pytest.mark.parametrize("a_mn,b_mn", [(False, True), (False, False), (True, True), (True, False)])
+def test_gemm_single_pair_tile(a_mn, b_mn):
+    """One 256 x 256 tile on a two-CTA cluster (tcgen05 cta_group::2), two K steps."""
+    from planmoe_b200.ops import gemm
+    M, N, K = 256, 256, 128
+    A = _rand(1, K, M) if a_mn else _rand(1, M, K)
+    B = _rand(1, K, N) if b_mn else _rand(1, N, K)
+    out = gemm.grouped_gemm(A, a_mn, B, b_mn, cta_group=2)
+    gemm.check_status()
+    _check(out, _ref_gemm(A, a_mn, B, b_mn))
+
+
+@pytest.mark.parametrize("cg", [1, 2])
 @pytest.mark.parametrize("a_mn,b_mn", [(False, True), (False, False), (True, True)])
 @pytest.mark.parametrize("G,M,N,K", [(2, 256, 512, 256), (3, 200, 320, 96), (2, 1024, 768, 1024), (1, 64, 64, 2048)])
-def test_gemm_shapes(a_mn, b_mn, G, M, N, K):
+def test_gemm_shapes(a_mn, b_mn, G, M, N, K, cg):
     from planmoe_b200.ops import gemm
     A = _rand(G, K, M) if a_mn else _rand(G, M, K)
     B = _rand(G, K, N) if b_mn else _rand(G, N, K)
-    out = gemm.grouped_gemm(A, a_mn, B, b_mn)
+    out = gemm.grouped_gemm(A, a_mn, B, b_mn, cta_group=cg)
     gemm.check_status()
     assert out.shape == (G, M, N)
     _check(out, _ref_gemm(A, a_mn, B, b_mn))
 
 
-def test_gemm_many_tiles_persistent():
+@pytest.mark.parametrize("cg", [1, 2])
+def test_gemm_many_tiles_persistent(cg):
     """More tiles than SMs: exercises the ring / accumulator phase wrap-around."""
     from planmoe_b200.ops import gemm
-    G, M, N, K = 2, 2048, 2048, 512
+    G, M, N, K = 2, 4096, 2048, 512
     A, B = _rand(G, M, K), _rand(G, K, N)
-    out = gemm.grouped_gemm(A, False, B, True)
+    out = gemm.grouped_gemm(A, False, B, True, cta_group=cg)
     gemm.check_status()
     _check(out, _ref_gemm(A, False, B, True))
-    out2 = gemm.grouped_gemm(A, False, B, True)
+    out2 = gemm.grouped_gemm(A, False, B, True, cta_group=cg)
     assert torch.equal(out, out2)
 
 
+@pytest.mark.parametrize("cg", [1, 2])
 @pytest.mark.parametrize("act", ['relu', 'gelu', 'silu', 'identity'])
-def test_gemm_epilogues(act):
+def test_gemm_epilogues(act, cg, monkeypatch):
     from planmoe_b200.ops import gemm
+    monkeypatch.setattr(gemm, 'DEFAULT_CTA_GROUP', cg)
     G, M, N, K = 2, 384, 512, 256
     A, B = _rand(G, M, K), _rand(G, K, N, scale=0.1)
     bias = _rand(G, N)
@@ -90,11 +106,12 @@ def test_gemm_epilogues(act):
     _check(d, _ref_gemm(A, False, B, True) * dact.float())
 
 
-def test_gemm_split_k_chunks():
+@pytest.mark.parametrize("cg", [1, 2])
+def test_gemm_split_k_chunks(cg):
     from planmoe_b200.ops import gemm
     d, G, R, M, N = 3, 2, 192, 256, 320
     A, B = _rand(d, G, R, M), _rand(d, G, R, N)
-    out = gemm.grouped_gemm(A, True, B, True)
+    out = gemm.grouped_gemm(A, True, B, True, cta_group=cg)
     gemm.check_status()
     ref = torch.einsum('dgrm,dgrn->gmn', A.float(), B.float())
     _check(out, ref)
