@@ -40,6 +40,7 @@ def parse():
     ap.add_argument('--degree', default='1')
     ap.add_argument('--comm', default='naive')
     ap.add_argument('--compress', default='no')
+    ap.add_argument('--stages', action='store_true', help='also print per-stage device times (stderr)')
     return ap.parse_args()
 
 
@@ -286,6 +287,16 @@ def main():
     for _ in range(max(args.warmup, 3)):
         step(x_dev)
     barrier()
+    if args.stages and args.impl == 'ours':
+        # separate, untimed pass with per-stage CUDA events (the timed regions below run without them)
+        from planmoe_b200.utils import stage_timer
+        stage_timer.enable(True)
+        for _ in range(10):
+            step(x_dev)
+        barrier()
+        print('rank %d stages: %s' % (rank, json.dumps(stage_timer.summary(skip=2))), file=sys.stderr, flush=True)
+        stage_timer.enable(False)
+        stage_timer.reset()
     if args.impl == 'ours':
         # a bounded wait that expired during warm-up ends the run here instead of timing garbage
         from planmoe_b200.parallel import transport

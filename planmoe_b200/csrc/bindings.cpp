@@ -352,17 +352,25 @@ Tensor grouped_gemm_op(const Tensor& A, bool a_mn, const Tensor& B, bool b_mn, c
   return out;
 }
 
-Tensor colsum_op(const Tensor& x) {
+// fp32 column sums [groups / fold, N] of a bf16 [groups, rows, N] tensor; with `as_bf16` the result is
+// returned in bf16 (written by the same kernel).
+Tensor colsum_op(const Tensor& x, int64_t fold, bool as_bf16) {
   count_launch(2);
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 3 && x.stride(2) == 1);
   c10::cuda::CUDAGuard guard(x.device());
   const int groups = x.size(0), N = x.size(2);
   const int64_t rows = x.size(1);
+  TORCH_CHECK(fold >= 1 && groups % fold == 0, "colsum: groups must be a multiple of fold");
   TORCH_CHECK(N % 8 == 0 && x.stride(1) % 8 == 0 && x.stride(0) % 8 == 0, "colsum needs 16-byte aligned rows");
   const int64_t slabs = colsum_slabs(rows);
-  Tensor buf = torch::empty({(int64_t)groups * N * (1 + slabs)}, x.options().dtype(at::kFloat));
-  launch_colsum_bf16(x.data_ptr(), buf.data_ptr<float>(), groups, rows, N, x.stride(1), x.stride(0), cur_stream());
-  return buf.narrow(0, 0, (int64_t)groups * N).view({groups, N});
+  const int64_t out_groups = groups / fold;
+  Tensor buf = torch::empty({out_groups * N + (int64_t)groups * N * slabs}, x.options().dtype(at::kFloat));
+  Tensor ob;
+  if (as_bf16) ob = torch::empty({out_groups, (int64_t)N}, x.options());
+  launch_colsum_bf16(x.data_ptr(), buf.data_ptr<float>(), groups, rows, N, x.stride(1), x.stride(0), (int)fold,
+                     as_bf16 ? ob.data_ptr() : nullptr, cur_stream());
+  if (as_bf16) return ob;
+  return buf.narrow(0, 0, out_groups * N).view({out_groups, (int64_t)N});
 }
 
 // ---- push / wait wrappers for the fused MoE path ------------------------------------------------
@@ -548,7 +556,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("cumsum_sub_one", &cumsum_sub_one_op);
   m.def("int8_encode", &int8_encode_op);
   m.def("int8_decode", &int8_decode_op);
-  m.def("colsum", &colsum_op);
+  m.def("colsum", &colsum_op, py::arg("x"), py::arg("fold") = 1, py::arg("as_bf16") = false);
   m.def("scatter_push", &scatter_push_op);
   m.def("gather_wait", &gather_wait_op);
   m.def("zfp_encode", &zfp_encode_op);

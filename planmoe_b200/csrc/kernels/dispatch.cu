@@ -202,8 +202,11 @@ struct WaitGeom {
   int* status;
 };
 
-template <class T, bool DEQUANT>
-__global__ void __launch_bounds__(kRowThreads)
+// MAXK bounds the number of picks per token held in registers: 2 covers top-1 / top-2 gates and keeps
+// the kernel at 32 registers, so that eight CTAs (all 64 warps) fit on an SM and the whole token range
+// is resident in one wave; 8 is the general case.
+template <class T, bool DEQUANT, int MAXK>
+__global__ void __launch_bounds__(kRowThreads, MAXK <= 2 ? 8 : 4)
 gather_rows_kernel(const void* __restrict__ disp_, const float* __restrict__ scale_bias,
                    const int* __restrict__ idx, const int* __restrict__ loc,
                    const float* __restrict__ gates, T* __restrict__ out, int K, int S, int M,
@@ -221,7 +224,6 @@ gather_rows_kernel(const void* __restrict__ disp_, const float* __restrict__ sca
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int V = Vec16<T>::N;
   const int nvec = M / V;
-  constexpr int MAXK = 8;
   for (int t = blockIdx.x * kRowWarps + warp; t < S; t += gridDim.x * kRowWarps) {
     long long slot[MAXK];
     float gw[MAXK];
@@ -305,13 +307,15 @@ void launch_gather_rows(const void* disp, const float* scale_bias, const int* id
   if (ctas > 148 * 8) ctas = 148 * 8;
   if (ctas < 1) ctas = 1;
   if (scale_bias != nullptr)
-    gather_rows_kernel<T, true><<<ctas, kRowThreads, 0, stream>>>(disp, scale_bias, idx, loc, gates, out, K, S, M, C, w);
+    gather_rows_kernel<T, true, 8><<<ctas, kRowThreads, 0, stream>>>(disp, scale_bias, idx, loc, gates, out, K, S, M, C, w);
+  else if (K <= 2)
+    gather_rows_kernel<T, false, 2><<<ctas, kRowThreads, 0, stream>>>(disp, scale_bias, idx, loc, gates, out, K, S, M, C, w);
   else
-    gather_rows_kernel<T, false><<<ctas, kRowThreads, 0, stream>>>(disp, scale_bias, idx, loc, gates, out, K, S, M, C, w);
+    gather_rows_kernel<T, false, 8><<<ctas, kRowThreads, 0, stream>>>(disp, scale_bias, idx, loc, gates, out, K, S, M, C, w);
 }
 
 template <class T>
-__global__ void __launch_bounds__(kRowThreads)
+__global__ void __launch_bounds__(kRowThreads, 8)
 gate_grad_kernel(const T* __restrict__ disp, const T* __restrict__ dy, const int* __restrict__ idx,
                  const int* __restrict__ loc, float* __restrict__ dgates, int K, int S, int M, int C) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;

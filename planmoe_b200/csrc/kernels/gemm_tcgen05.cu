@@ -277,39 +277,49 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, Ctl* ct
   return true;
 }
 
-// Gaussian CDF and PDF at x with one exp and one reciprocal: erf by the Abramowitz-Stegun 7.1.26
-// rational approximation (|error| < 1.5e-7, far below bf16 resolution); exp(-x^2/2) serves both.
+__device__ __forceinline__ float rcp_approx(float x) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+
+// Gaussian CDF and PDF at x with one exp2 and one approximate reciprocal: erf by the Abramowitz-Stegun
+// 7.1.26 rational approximation (|error| < 1.5e-7, far below bf16 resolution); exp(-x^2/2) serves both.
 __device__ __forceinline__ void gauss_cdf_pdf(float x, float& cdf, float& pdf) {
   const float z = fabsf(x) * 0.70710678118654752f;
-  const float e = __expf(-z * z);
-  const float t = __frcp_rn(fmaf(0.3275911f, z, 1.f));
+  const float e = ex2_approx(-1.4426950408889634f * z * z);
+  const float t = rcp_approx(fmaf(0.3275911f, z, 1.f));
   float poly = fmaf(t, 1.061405429f, -1.453152027f);
   poly = fmaf(poly, t, 1.421413741f);
   poly = fmaf(poly, t, -0.284496736f);
   poly = fmaf(poly, t, 0.254829592f);
-  const float erf_abs = 1.f - poly * t * e;
-  cdf = 0.5f * (1.f + copysignf(erf_abs, x));
+  const float half_erf = 0.5f - 0.5f * poly * t * e;            // erf(|x| / sqrt 2) / 2
+  cdf = 0.5f + copysignf(half_erf, x);
   pdf = 0.3989422804014327f * e;
 }
 
-// Activation value and derivative in one go (they share the transcendental work).
-__device__ __forceinline__ void act_both(float x, int act, float& out, float& deriv) {
-  switch (act) {
-    case kActRelu: out = fmaxf(x, 0.f); deriv = x > 0.f ? 1.f : 0.f; break;
-    case kActGelu: {
-      float cdf, pdf;
-      gauss_cdf_pdf(x, cdf, pdf);
-      out = x * cdf;
-      deriv = fmaf(x, pdf, cdf);
-      break;
-    }
-    case kActSilu: {
-      const float sg = __frcp_rn(1.f + __expf(-x));
-      out = x * sg;
-      deriv = sg * (1.f + x * (1.f - sg));
-      break;
-    }
-    default: out = x; deriv = 1.f; break;
+// Activation value and derivative in one go (they share the transcendental work).  ACT is a
+// compile-time constant in the epilogue's inner loops.
+template <int ACT>
+__device__ __forceinline__ void act_both(float x, float& out, float& deriv) {
+  if constexpr (ACT == kActRelu) {
+    out = fmaxf(x, 0.f); deriv = x > 0.f ? 1.f : 0.f;
+  } else if constexpr (ACT == kActGelu) {
+    float cdf, pdf;
+    gauss_cdf_pdf(x, cdf, pdf);
+    out = x * cdf;
+    deriv = fmaf(x, pdf, cdf);
+  } else if constexpr (ACT == kActSilu) {
+    const float sg = rcp_approx(1.f + ex2_approx(-1.4426950408889634f * x));
+    out = x * sg;
+    deriv = sg * fmaf(x, 1.f - sg, 1.f);
+  } else {
+    out = x; deriv = 1.f;
   }
 }
 
@@ -404,6 +414,25 @@ __device__ __noinline__ void copy_role(const KernelParams& p, int cwarp) {
           reinterpret_cast<uint8_t*>(p.heap_bases[ctid]) + c.flag_off);
       red_release_sys_add(flags + (size_t)j * p.W + p.my_rank, 1ull);
     }
+  }
+}
+
+// Bias + activation on one thread's 64 accumulator values: the packed activation goes to `opk`, the
+// packed derivative into the thread's row of the (swizzled) staging tile.
+template <int ACT>
+__device__ __forceinline__ void slab_bias_act(const uint32_t* v, const float* bias, uint8_t* st_row, int lane,
+                                              uint4* opk) {
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const float4 b0 = *reinterpret_cast<const float4*>(bias + c * 8);
+    const float4 b1 = *reinterpret_cast<const float4*>(bias + c * 8 + 4);
+    const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+    float f[8], d[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) act_both<ACT>(__uint_as_float(v[c * 8 + i]) + bb[i], f[i], d[i]);
+    *reinterpret_cast<uint4*>(st_row + ((c ^ (lane & 7)) << 4)) =
+        make_uint4(pack_bf16(d[0], d[1]), pack_bf16(d[2], d[3]), pack_bf16(d[4], d[5]), pack_bf16(d[6], d[7]));
+    opk[c] = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
   }
 }
 
@@ -615,15 +644,25 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
       };
 
-#pragma unroll 1
+      // The accumulator is drained in two 64-column slabs.  The TMEM load of the second slab is issued
+      // as soon as the first slab's values have been consumed, so it runs under the first slab's stores.
+      // (The activation-backward epilogue also holds the saved derivatives in registers and issues each
+      // load at the top of its slab instead.)
+      constexpr bool kEarlyLd = EPI != kEpiDAct;
+      uint32_t v[64];
+      if (kEarlyLd && n0 + half * 128 < p.N) {
+        tmem_ld32(t_row, v);
+        tmem_ld32(t_row + 32, v + 32);
+      }
+#pragma unroll
       for (int s2 = 0; s2 < 2; ++s2) {
         const int c0 = half * 128 + s2 * 64;       // first accumulator column of this slab
         const int nb = n0 + c0;                    // first global column
         if (nb >= p.N) break;
-
-        uint32_t v[64];
-        tmem_ld32(t_row + s2 * 64, v);
-        tmem_ld32(t_row + s2 * 64 + 32, v + 32);
+        if constexpr (!kEarlyLd) {
+          tmem_ld32(t_row + s2 * 64, v);
+          tmem_ld32(t_row + s2 * 64 + 32, v + 32);
+        }
 
         uint4 dact[8];
         if constexpr (EPI == kEpiDAct) {
@@ -643,28 +682,40 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         tmem_ld_wait();
 
         uint4 opk[8];
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          float f[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[c * 8 + i]) + bias_s[c0 + c * 8 + i];
-          if constexpr (EPI == kEpiBiasAct) {
-            float d[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) act_both(f[i], p.activation, f[i], d[i]);
-            // derivative goes through the staging tile first; the activation waits in registers
-            *reinterpret_cast<uint4*>(st0 + lane * 128 + ((c ^ (lane & 7)) << 4)) =
-                make_uint4(pack_bf16(d[0], d[1]), pack_bf16(d[2], d[3]), pack_bf16(d[4], d[5]), pack_bf16(d[6], d[7]));
-          } else if constexpr (EPI == kEpiDAct) {
-            const __nv_bfloat162* ph = reinterpret_cast<const __nv_bfloat162*>(&dact[c]);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float2 df = __bfloat1622float2(ph[i]);
-              f[2 * i] *= df.x;
-              f[2 * i + 1] *= df.y;
-            }
+        if constexpr (EPI == kEpiBiasAct) {
+          // derivative goes through the staging tile first; the activation waits in registers
+          uint8_t* st_row = st0 + lane * 128;
+          switch (p.activation) {
+            case kActRelu: slab_bias_act<kActRelu>(v, bias_s + c0, st_row, lane, opk); break;
+            case kActGelu: slab_bias_act<kActGelu>(v, bias_s + c0, st_row, lane, opk); break;
+            case kActSilu: slab_bias_act<kActSilu>(v, bias_s + c0, st_row, lane, opk); break;
+            default: slab_bias_act<kActIdentity>(v, bias_s + c0, st_row, lane, opk); break;
           }
-          opk[c] = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+        } else {
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const float4 b0 = *reinterpret_cast<const float4*>(bias_s + c0 + c * 8);
+            const float4 b1 = *reinterpret_cast<const float4*>(bias_s + c0 + c * 8 + 4);
+            const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+            float f[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[c * 8 + i]) + bb[i];
+            if constexpr (EPI == kEpiDAct) {
+              const __nv_bfloat162* ph = reinterpret_cast<const __nv_bfloat162*>(&dact[c]);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float2 df = __bfloat1622float2(ph[i]);
+                f[2 * i] *= df.x;
+                f[2 * i + 1] *= df.y;
+              }
+            }
+            opk[c] = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+          }
+        }
+        // v is consumed: fetch the next slab while this one is written out
+        if (kEarlyLd && EPI != kEpiBiasAct && s2 == 0 && nb + 64 < p.N) {
+          tmem_ld32(t_row + 64, v);
+          tmem_ld32(t_row + 96, v + 32);
         }
         if constexpr (EPI == kEpiBiasAct) {
           __syncwarp();
@@ -675,6 +726,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         for (int c = 0; c < 8; ++c)
           *reinterpret_cast<uint4*>(st0 + lane * 128 + ((c ^ (lane & 7)) << 4)) = opk[c];
         __syncwarp();
+        if (EPI == kEpiBiasAct && s2 == 0 && nb + 64 < p.N) {     // both outputs are staged: registers are free
+          tmem_ld32(t_row + 64, v);
+          tmem_ld32(t_row + 96, v + 32);
+        }
 
         if constexpr (EPI == kEpiPush) {
 #pragma unroll
@@ -938,63 +993,102 @@ cudaError_t launch_grouped_gemm(const GemmArgs& a, cudaStream_t stream) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// Column sums (bias gradients): fp32 [groups][N] = sum over rows of bf16 [groups][rows][N].
-// Two-stage and deterministic: every CTA reduces a row slab, partials are added in slab order.
+// Column sums (bias gradients): fp32 [groups / fold][N] = sum over rows (and over `fold` leading
+// group blocks, the pipeline chunks) of bf16 [groups][rows][N].
+// Two-stage and deterministic.  Stage 1: a CTA of 8 row lanes x 32 column threads reduces a slab of
+// 128 rows x 256 columns with 16-byte loads (8 columns per thread), combines the row lanes through
+// shared memory and writes one fp32 partial row.  Stage 2 adds the partials in slab order.
 // ---------------------------------------------------------------------------------------------
 namespace {
-constexpr int kColsumSlab = 32;
+constexpr int kColsumSlab = 128;
+constexpr int kColsumCols = 256;
 
 __global__ void __launch_bounds__(256)
 colsum_partial_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ partial, long long rows, int N,
                       long long row_stride, long long group_stride, int slabs) {
-  // grid: (ceil(N / 2048), slabs, groups); each thread owns 8 adjacent columns (one 16-byte load per row)
-  const int col = (blockIdx.x * 256 + threadIdx.x) * 8;
-  if (col >= N) return;
+  __shared__ float red[8][kColsumCols + 8];
+  const int ct = threadIdx.x & 31, rl = threadIdx.x >> 5;
+  const int col0 = blockIdx.x * kColsumCols;
+  const int col = col0 + ct * 8;
   const int slab = blockIdx.y, g = blockIdx.z;
   const long long r0 = (long long)slab * kColsumSlab;
   const long long r1 = r0 + kColsumSlab < rows ? r0 + kColsumSlab : rows;
-  const __nv_bfloat16* base = x + (long long)g * group_stride + col;
   float a[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) a[i] = 0.f;
+  if (col < N) {
+    const __nv_bfloat16* base = x + (long long)g * group_stride + col;
 #pragma unroll 4
-  for (long long r = r0; r < r1; ++r) {
-    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(base + r * row_stride));
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    for (long long r = r0 + rl; r < r1; r += 8) {
+      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(base + r * row_stride));
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float2 f = __bfloat1622float2(h[i]);
-      a[2 * i] += f.x; a[2 * i + 1] += f.y;
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(h[i]);
+        a[2 * i] += f.x; a[2 * i + 1] += f.y;
+      }
     }
   }
-  float* dst = partial + ((long long)g * slabs + slab) * N + col;
-  *reinterpret_cast<float4*>(dst) = make_float4(a[0], a[1], a[2], a[3]);
-  *reinterpret_cast<float4*>(dst + 4) = make_float4(a[4], a[5], a[6], a[7]);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) red[rl][ct * 8 + i] = a[i];
+  __syncthreads();
+  const int c = threadIdx.x;
+  if (col0 + c < N) {
+    float acc = 0.f;
+#pragma unroll
+    for (int l = 0; l < 8; ++l) acc += red[l][c];
+    partial[((long long)g * slabs + slab) * N + col0 + c] = acc;
+  }
 }
 
-__global__ void colsum_final_kernel(const float* __restrict__ partial, float* __restrict__ out, int N, int slabs) {
-  const int col = blockIdx.x * blockDim.x + threadIdx.x;
-  const int g = blockIdx.y;
-  if (col >= N) return;
+__global__ void __launch_bounds__(256)
+colsum_final_kernel(const float* __restrict__ partial, float* __restrict__ out, __nv_bfloat16* __restrict__ out_bf16,
+                    int N, int slabs, int fold, int out_groups) {
+  // 32 columns x 8 slab lanes per CTA: lane l adds partials l, l + 8, ... (independent loads in flight),
+  // the eight lane sums are then added in lane order, so the result does not depend on timing.
+  __shared__ float red[8][33];
+  const int ct = threadIdx.x & 31, sl = threadIdx.x >> 5;
+  const int col = blockIdx.x * 32 + ct;
+  const int e = blockIdx.y;
   float acc = 0.f;
-  for (int s = 0; s < slabs; ++s) acc += partial[((long long)g * slabs + s) * N + col];
-  out[(long long)g * N + col] = acc;
+  if (col < N) {
+    const int total = fold * slabs;
+#pragma unroll 4
+    for (int i = sl; i < total; i += 8) {
+      const int j = i / slabs, s = i - j * slabs;
+      acc += partial[((long long)(j * out_groups + e) * slabs + s) * N + col];
+    }
+  }
+  red[sl][ct] = acc;
+  __syncthreads();
+  if (sl == 0 && col < N) {
+    float r = 0.f;
+#pragma unroll
+    for (int l = 0; l < 8; ++l) r += red[l][ct];
+    out[(long long)e * N + col] = r;
+    if (out_bf16 != nullptr) out_bf16[(long long)e * N + col] = __float2bfloat16_rn(r);
+  }
 }
 }  // namespace
 
 int colsum_slabs(long long rows) { return (int)((rows + kColsumSlab - 1) / kColsumSlab); }
 
-// `out` must have room for groups*N floats followed by groups*colsum_slabs(rows)*N floats of scratch.
-// N must be a multiple of 8 and rows of x 16-byte aligned.
+// `out` must have room for (groups / fold) * N floats followed by groups * colsum_slabs(rows) * N floats of
+// scratch.  N must be a multiple of 8 and rows of x 16-byte aligned.  groups = fold * (groups / fold):
+// group j * (groups / fold) + e is summed into output row e.  `out_bf16` (optional) receives the same sums
+// rounded to bf16.
 void launch_colsum_bf16(const void* x, float* out, int groups, long long rows, int N, long long row_stride,
-                        long long group_stride, cudaStream_t stream) {
+                        long long group_stride, int fold, void* out_bf16, cudaStream_t stream) {
+  if (fold < 1) fold = 1;
+  const int out_groups = groups / fold;
   const int slabs = colsum_slabs(rows);
-  float* partial = out + (long long)groups * N;
-  dim3 g1((N / 8 + 255) / 256, slabs, groups);
+  float* partial = out + (long long)out_groups * N;
+  dim3 g1((N + kColsumCols - 1) / kColsumCols, slabs, groups);
   colsum_partial_kernel<<<g1, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), partial, rows, N,
                                               row_stride, group_stride, slabs);
-  dim3 g2((N + 255) / 256, groups);
-  colsum_final_kernel<<<g2, 256, 0, stream>>>(partial, out, N, slabs);
+  dim3 g2((N + 31) / 32, out_groups);
+  colsum_final_kernel<<<g2, 256, 0, stream>>>(partial, out, reinterpret_cast<__nv_bfloat16*>(out_bf16), N, slabs, fold,
+                                            out_groups);
 }
 
 }  // namespace planmoe

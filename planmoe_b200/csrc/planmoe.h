@@ -153,9 +153,12 @@ int gemm_grid_ctas(int groups, int M, int N, int max_ctas, int cta_group);
 // Number of flag arrivals rank s receives per push launch (host helper for the receiver).
 int gemm_push_arrivals(int groups, int M, int N, int push_rows, int s);
 
-// Column sums of a bf16 [groups][rows][N] tensor -> fp32 [groups][N] (bias gradients).
+// Column sums of a bf16 [groups][rows][N] tensor -> fp32 [groups / fold][N] (bias gradients); the `fold`
+// leading blocks of groups (pipeline chunks) are added together.  `out` = (groups / fold) * N results
+// followed by groups * colsum_slabs(rows) * N floats of scratch; `out_bf16` optionally gets bf16 copies.
 int colsum_slabs(long long rows);
 void launch_colsum_bf16(const void* x, float* out, int groups, long long rows, int N,
-                        long long row_stride, long long group_stride, cudaStream_t stream);
+                        long long row_stride, long long group_stride, int fold, void* out_bf16,
+                        cudaStream_t stream);
 
 }  // namespace planmoe

@@ -36,6 +36,7 @@ import torch.nn.functional as F
 from . import native
 from .gemm import ACT_CODES, EPI_BIAS_ACT, EPI_DACT, EPI_PUSH, EPI_STORE, grouped_gemm
 from ..parallel import transport as T
+from ..utils.stage_timer import stage
 
 MAX_CHUNKS = 32
 PH_DISPATCH, PH_COMBINE, PH_COMBINE_BWD, PH_DISPATCH_BWD = 0, 1, 2, 3
@@ -210,22 +211,25 @@ class _FusedExperts(torch.autograd.Function):
             grouped_gemm(recv_x, False, w1, True, EPI_BIAS_ACT, act, bias=b1, aux=dact, out=h,
                          gate_flags_ptr=bs.flag_ptr(PH_DISPATCH, 0), gate_rows=Cc, gate_want=want,
                          chunk_groups=E_l, W=W, my_rank=rank, budget_ms=budget, status_ptr=status, **copy)
-        _send_and_gemm(lib, bs, PH_DISPATCH, x, slot_map, None if postscore else gates_f, K, E, C, W, rank, d,
-                       lib.gemm_grid_ctas(d * E_l, R, H), gemm1)
+        with stage('fwd.dispatch+gemm1'):
+            _send_and_gemm(lib, bs, PH_DISPATCH, x, slot_map, None if postscore else gates_f, K, E, C, W, rank, d,
+                           lib.gemm_grid_ctas(d * E_l, R, H), gemm1)
         push_arrivals = lib.gemm_push_arrivals(E_l, R, O, Cc, rank)
         # GEMM 2 over all chunks: the epilogue pushes rows to the token owners' combine buffers
-        grouped_gemm(h, False, w2, True, EPI_PUSH, 0, bias=b2,
-                     heap_bases_ptr=bases, push_data_off=bs.off_y,
-                     push_flag_off=bs.flag_off(PH_COMBINE), push_rows=Cc, push_C=C,
-                     chunk_groups=E_l, W=W, my_rank=rank, budget_ms=budget, status_ptr=status)
+        with stage('fwd.gemm2+combine_push'):
+            grouped_gemm(h, False, w2, True, EPI_PUSH, 0, bias=b2,
+                         heap_bases_ptr=bases, push_data_off=bs.off_y,
+                         push_flag_off=bs.flag_off(PH_COMBINE), push_rows=Cc, push_C=C,
+                         chunk_groups=E_l, W=W, my_rank=rank, budget_ms=budget, status_ptr=status)
         bs.arrived[PH_COMBINE] += push_arrivals
         want_y = bs.arrived[PH_COMBINE]
 
         # ---- combine: wait for every (chunk, expert rank) flag, gate-weighted sum over k ---------
         # flags of chunks 0..d-1 are consecutive: [d][W]
-        out = lib.gather_wait(bs.block.local_ptr + (bs.off_y - bs.block.offset), x.dtype, O, idx, loc,
-                              gates_f if postscore else None, C, bs.flag_ptr(PH_COMBINE, 0), d * W, want_y,
-                              budget, status)
+        with stage('fwd.combine_wait+decode'):
+            out = lib.gather_wait(bs.block.local_ptr + (bs.off_y - bs.block.offset), x.dtype, O, idx, loc,
+                                  gates_f if postscore else None, C, bs.flag_ptr(PH_COMBINE, 0), d * W, want_y,
+                                  budget, status)
 
         ctx.meta, ctx.bs = meta, bs
         ctx.save_for_backward(x, gates_f, w1, w2, dact, h)
@@ -249,7 +253,8 @@ class _FusedExperts(torch.autograd.Function):
         recv_y = bs.view(bs.off_y, (E * C, O))
         dgates = None
         if postscore and ctx.needs_input_grad[1]:
-            dgates = lib.dispatch_gate_grad(recv_y, dout, idx, loc, C)
+            with stage('bwd.gate_grad'):
+                dgates = lib.dispatch_gate_grad(recv_y, dout, idx, loc, C)
 
         # ---- combine backward: push dY (gate-weighted) + flag-gated dgrad 2 ---------------------------
         recv_dy = bs.view(bs.off_dy, (d * E_l, R, O))
@@ -261,27 +266,33 @@ class _FusedExperts(torch.autograd.Function):
             grouped_gemm(recv_dy, False, w2, False, EPI_DACT, act, aux=dact, out=dh,
                          gate_flags_ptr=bs.flag_ptr(PH_COMBINE_BWD, 0), gate_rows=Cc, gate_want=want,
                          chunk_groups=E_l, W=W, my_rank=rank, budget_ms=budget, status_ptr=status, **copy)
-        _send_and_gemm(lib, bs, PH_COMBINE_BWD, dout, slot_map, gates_f if postscore else None, K, E, C, W, rank, d,
-                       lib.gemm_grid_ctas(d * E_l, R, H), dgrad2)
+        with stage('bwd.combine_bwd_send+dgrad2'):
+            _send_and_gemm(lib, bs, PH_COMBINE_BWD, dout, slot_map, gates_f if postscore else None, K, E, C, W, rank,
+                           d, lib.gemm_grid_ctas(d * E_l, R, H), dgrad2)
         push_arrivals = lib.gemm_push_arrivals(E_l, R, M, Cc, rank)
         # dX slots = dH . W1^T, pushed back to the token owners
-        grouped_gemm(dh, False, w1, False, EPI_PUSH, 0,
-                     heap_bases_ptr=bases, push_data_off=bs.off_dx,
-                     push_flag_off=bs.flag_off(PH_DISPATCH_BWD), push_rows=Cc, push_C=C,
-                     chunk_groups=E_l, W=W, my_rank=rank, budget_ms=budget, status_ptr=status)
+        with stage('bwd.dgrad1+dispatch_bwd_push'):
+            grouped_gemm(dh, False, w1, False, EPI_PUSH, 0,
+                         heap_bases_ptr=bases, push_data_off=bs.off_dx,
+                         push_flag_off=bs.flag_off(PH_DISPATCH_BWD), push_rows=Cc, push_C=C,
+                         chunk_groups=E_l, W=W, my_rank=rank, budget_ms=budget, status_ptr=status)
         bs.arrived[PH_DISPATCH_BWD] += push_arrivals
         want_dx = bs.arrived[PH_DISPATCH_BWD]
 
         # ---- weight / bias gradients: contract over all chunks in one launch each ---------------
-        dw2 = grouped_gemm(h.view(d, E_l, R, H), True, recv_dy.view(d, E_l, R, O), True, EPI_STORE)
-        dw1 = grouped_gemm(recv_x.view(d, E_l, R, M), True, dh.view(d, E_l, R, H), True, EPI_STORE)
-        db2 = lib.colsum(recv_dy).view(d, E_l, O).sum(0).to(w2.dtype)
-        db1 = lib.colsum(dh).view(d, E_l, H).sum(0).to(w1.dtype)
+        with stage('bwd.wgrad2'):
+            dw2 = grouped_gemm(h.view(d, E_l, R, H), True, recv_dy.view(d, E_l, R, O), True, EPI_STORE)
+        with stage('bwd.wgrad1'):
+            dw1 = grouped_gemm(recv_x.view(d, E_l, R, M), True, dh.view(d, E_l, R, H), True, EPI_STORE)
+        with stage('bwd.bias_grads'):
+            db2 = lib.colsum(recv_dy, d, True)
+            db1 = lib.colsum(dh, d, True)
 
         # ---- dispatch backward: wait for the returned slots, gather (gate-weighted if pre-score)
-        dx = lib.gather_wait(bs.block.local_ptr + (bs.off_dx - bs.block.offset), dout.dtype, M, idx, loc,
-                             None if postscore else gates_f, C, bs.flag_ptr(PH_DISPATCH_BWD, 0), d * W,
-                             want_dx, budget, status)
+        with stage('bwd.dispatch_bwd_wait+gather'):
+            dx = lib.gather_wait(bs.block.local_ptr + (bs.off_dx - bs.block.offset), dout.dtype, M, idx, loc,
+                                 None if postscore else gates_f, C, bs.flag_ptr(PH_DISPATCH_BWD, 0), d * W,
+                                 want_dx, budget, status)
         if not postscore and ctx.needs_input_grad[1]:
             recv_dx = bs.view(bs.off_dx, (E * C, M))
             dgates = lib.dispatch_gate_grad(recv_dx, x, idx, loc, C)
@@ -297,7 +308,7 @@ def forward(layer, x, gctx, top_k, capacity_factor, degree):
     E = layer.num_global_experts
     top_k = min(int(top_k), E)
 
-    with torch.autocast('cuda', enabled=False):
+    with torch.autocast('cuda', enabled=False), stage('fwd.gate_linear'):
         logits = gctx(x)
         if layer.training and gctx.gate_noise > 0:
             logits = logits + gctx.gate_noise * torch.randn_like(logits) / E
@@ -306,7 +317,8 @@ def forward(layer, x, gctx, top_k, capacity_factor, degree):
     if capacity % align:
         capacity += align - capacity % align
 
-    gates, l_aux, idx, loc, slot_map = fused_gate(logits, top_k, capacity, layer.normalize_gate)
+    with stage('fwd.gate_topk_scan'):
+        gates, l_aux, idx, loc, slot_map = fused_gate(logits, top_k, capacity, layer.normalize_gate)
     ex = layer.experts
     meta = dict(state=st, idx=idx, loc=loc, slot_map=slot_map, E=E, C=capacity, degree=degree, K=top_k,
                 act=ACT_CODES[ex.act_name], postscore=layer.is_postscore)

@@ -121,6 +121,14 @@ def test_colsum():
     x = _rand(3, 1000, 256)
     out = _lib().colsum(x)
     assert torch.allclose(out, x.float().sum(1), atol=1e-2, rtol=1e-3)
+    # fold: chunk blocks of groups are added together; bf16 output comes from the same kernel
+    x = _rand(6, 517, 328)
+    ref = x.float().sum(1).view(3, 2, 328).sum(0)
+    out = _lib().colsum(x, 3)
+    assert out.shape == (2, 328) and torch.allclose(out, ref, atol=2e-2, rtol=1e-3)
+    ob = _lib().colsum(x, 3, True)
+    assert ob.dtype == torch.bfloat16 and torch.equal(ob, out.to(torch.bfloat16))
+    assert torch.equal(_lib().colsum(x, 3), out)            # fixed summation order
 
 
 def test_expert_ffn_forward_backward():
