@@ -37,7 +37,7 @@ def parse():
     ap.add_argument('--steps', type=int, default=20)
     ap.add_argument('--warmup', type=int, default=5)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference', 'ref-torch'])
-    ap.add_argument('--degree', default='1')
+    ap.add_argument('--degree', default='auto', help="pipeline degree: an integer, or 'auto' for the adaptive scheduler")
     ap.add_argument('--comm', default='naive')
     ap.add_argument('--compress', default='no')
     ap.add_argument('--stages', action='store_true', help='also print per-stage device times (stderr)')
@@ -286,6 +286,17 @@ def main():
 
     for _ in range(max(args.warmup, 3)):
         step(x_dev)
+    chosen = args.degree
+    if args.impl == 'ours' and args.degree == 'auto':
+        # the adaptive scheduler times every candidate degree over a few steps and then freezes one;
+        # keep warming up (untimed) until it has, so that the timed steps all run the frozen plan
+        for _ in range(64):
+            sched = getattr(layer, '_scheduler', None)
+            if sched is not None and sched.frozen is not None:
+                break
+            step(x_dev)
+        sched = getattr(layer, '_scheduler', None)
+        chosen = 'auto->%s' % (sched.frozen if sched is not None else '?')
     barrier()
     if args.stages and args.impl == 'ours':
         # separate, untimed pass with per-stage CUDA events (the timed regions below run without them)
@@ -310,29 +321,65 @@ def main():
     ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     l0 = launch_count()
     barrier()
+    host_t0 = time.perf_counter()
     for i in range(args.steps):
         flush.fill_(i & 0xff)
         starts[i].record()
         step(x_dev)
         ends[i].record()
+    host_ms = (time.perf_counter() - host_t0) * 1e3 / args.steps      # host time to enqueue one step
     barrier()
     launches = launch_count() - l0
     clocks = sampler.stop() if rank == 0 else None
     ms = sum(s.elapsed_time(e) for s, e in zip(starts, ends))
 
     # ---- end-to-end region: pinned H2D of the input + D2H of the loss, every step ---------------
+    # The way a training loop feeds a GPU: the input of step i + 1 is copied from pinned host memory on a
+    # copy stream while step i computes (two device buffers), and the loss of step i is copied to pinned
+    # host memory behind step i and read by the host one step later, so neither copy stalls the compute
+    # stream.  Every step's input is copied and every step's loss is read inside the timed region.
+    copy_stream = torch.cuda.Stream(device=device)
+    x_bufs = [torch.empty_like(x_dev) for _ in range(2)]
+    x_ready = [torch.cuda.Event() for _ in range(2)]
+    x_free = [torch.cuda.Event() for _ in range(2)]
+    loss_host = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(2)]
+    loss_done = [torch.cuda.Event() for _ in range(2)]
+    cur = torch.cuda.current_stream()
+    losses_read = 0
+
+    def prefetch(i):
+        b = i & 1
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(x_free[b])          # the step that last read this buffer has finished
+            x_bufs[b].copy_(host_x, non_blocking=True)
+            x_ready[b].record(copy_stream)
+
     e2e_s = torch.cuda.Event(enable_timing=True)
     e2e_e = torch.cuda.Event(enable_timing=True)
+    for b in range(2):
+        x_free[b].record(cur)
     barrier()
     e2e_s.record()
+    prefetch(0)
     for i in range(args.steps):
-        x_in = host_x.to(device, non_blocking=True)
-        loss = step(x_in)
-        host_loss.copy_(loss.detach().reshape(1), non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        _ = float(host_loss[0])
+        b = i & 1
+        if i + 1 < args.steps:
+            prefetch(i + 1)
+        cur.wait_event(x_ready[b])
+        loss = step(x_bufs[b])
+        x_free[b].record(cur)
+        loss_host[b].copy_(loss.detach().float().reshape(1), non_blocking=True)
+        loss_done[b].record(cur)
+        if i > 0:                                      # read the previous step's loss while this one runs
+            loss_done[b ^ 1].synchronize()
+            _ = float(loss_host[b ^ 1][0])
+            losses_read += 1
+    loss_done[(args.steps - 1) & 1].synchronize()
+    _ = float(loss_host[(args.steps - 1) & 1][0])
+    losses_read += 1
     e2e_e.record()
     barrier()
+    assert losses_read == args.steps
     e2e_ms = e2e_s.elapsed_time(e2e_e)
 
     if args.impl == 'ours':
@@ -360,13 +407,14 @@ def main():
                 'global_batch': CFG['batch'] * world, 'seq_len': CFG['tokens'],
                 'parallelism': 'ep%d' % world, 'step': 'forward + backward + SGD update',
                 'l2': 'flushed between timed steps (256 MiB write outside the event brackets)',
-                'degree': args.degree, 'comm': args.comm, 'compress': args.compress,
+                'degree': chosen, 'comm': args.comm, 'compress': args.compress,
             },
             'clocks': clocks,
             'e2e': {'value': tokens / (e2e_ms / 1e3), 'unit': 'tokens/s',
                     'h2d_bytes_per_step': host_x.numel() * host_x.element_size(),
                     'd2h_bytes_per_step': host_loss.numel() * host_loss.element_size()},
             'gpu_launches': int(launches),
+            'host_enqueue_ms_per_step': round(host_ms, 4),
         }
         print(json.dumps(out))
     if world > 1:

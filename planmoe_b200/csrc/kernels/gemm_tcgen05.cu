@@ -631,6 +631,21 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + half * 128;
 
+      // Push epilogue: where row (m0 + q * 32 + lane) of this tile lives in the combine buffer of the
+      // rank that owns the token (0 = row outside the problem).
+      unsigned long long push_row = 0ull;
+      if constexpr (EPI == kEpiPush) {
+        const int m = m0 + q * 32 + lane;
+        if (m < p.M) {
+          const int s = m / p.push_rows, cc = m - s * p.push_rows;
+          const int el = p.chunk_groups > 0 ? g % p.chunk_groups : g;
+          const int nel = p.chunk_groups > 0 ? p.chunk_groups : p.groups;
+          const int c_base = p.chunk_groups > 0 ? (g / p.chunk_groups) * p.push_rows : p.push_c0;
+          const long long drow = ((long long)p.my_rank * nel + el) * p.push_C + c_base + cc;
+          push_row = p.heap_bases[s] + p.push_data_off + (unsigned long long)drow * p.N * 2ull;
+        }
+      }
+
       // coalesced write-out of the staging tile: each instruction stores 4 rows x 128 bytes
       auto write_out = [&](__nv_bfloat16* dst, long long row_stride, long long group_stride, int nb) {
 #pragma unroll
@@ -735,17 +750,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
           for (int it = 0; it < 8; ++it) {
             const int r = it * 4 + (lane >> 3), c = lane & 7;
-            const int m = m0 + q * 32 + r;
-            if (m < p.M && nb + c * 8 < p.N) {
+            // destination row addresses were computed once per tile, one row per lane
+            const unsigned long long rp = __shfl_sync(0xffffffffu, push_row, r);
+            if (rp != 0ull && nb + c * 8 < p.N) {
               const uint4 val = *reinterpret_cast<const uint4*>(st0 + r * 128 + ((c ^ (r & 7)) << 4));
-              const int s = m / p.push_rows, cc = m - s * p.push_rows;
-              __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(
-                  reinterpret_cast<uint8_t*>(p.heap_bases[s]) + p.push_data_off);
-              const int el = p.chunk_groups > 0 ? g % p.chunk_groups : g;
-              const int nel = p.chunk_groups > 0 ? p.chunk_groups : p.groups;
-              const int c_base = p.chunk_groups > 0 ? (g / p.chunk_groups) * p.push_rows : p.push_c0;
-              const long long drow = ((long long)p.my_rank * nel + el) * p.push_C + c_base + cc;
-              *reinterpret_cast<uint4*>(base + drow * p.N + nb + c * 8) = val;
+              *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(rp) + nb + c * 8) = val;
             }
           }
         } else {

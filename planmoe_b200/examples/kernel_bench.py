@@ -3,7 +3,8 @@
 
     python -m planmoe_b200.examples.kernel_bench [--case NAME] [--iters N] [--small]
 
-Cases: gemm_fwd (K-major x MN-major, bias+GELU epilogue), gemm_dgrad (K x K, activation-backward
+Cases: gemm_fwd (K-major x MN-major, bias+GELU epilogue), gemm_push (same GEMM, rows stored into the
+symmetric heap with flags), gemm_dgrad (K x K, activation-backward
 epilogue), gemm_wgrad (MN x MN), cublas (torch.bmm of the forward shape, for comparison), scatter
 (dispatch), gather (combine), gate (fused gate), int8 (encode + decode), all.  Shapes are the
 per-rank shapes of the pre_test layer: 2 experts x 8192 rows, model_dim = hidden = 2048
@@ -92,6 +93,16 @@ def main():
     if want('gemm_plain'):
         ms, best = timed(lambda: gemm.grouped_gemm(x, False, w1, True, out=out), args.iters, flush)
         report('gemm_plain', ms, best, flops)
+    if want('gemm_push'):
+        # push epilogue with this rank's own heap as the destination (one rank: no NVLink traffic)
+        from planmoe_b200.parallel import transport
+        tr = transport.get_transport(None)
+        blk = tr.alloc(G * R * H * 2 + 4096)
+        ms, best = timed(lambda: gemm.grouped_gemm(
+            x, False, w1, True, gemm.EPI_PUSH, 0, bias=b1, heap_bases_ptr=blk.bases_ptr, push_data_off=blk.offset,
+            push_flag_off=blk.offset + G * R * H * 2, push_rows=R, push_C=R, W=1, my_rank=0,
+            budget_ms=tr.budget_ms, status_ptr=tr.status_ptr), args.iters, flush)
+        report('gemm_push_local', ms, best, flops)
     if want('gemm_dgrad'):
         ms, best = timed(lambda: gemm.grouped_gemm(dy, False, w1, False, gemm.EPI_DACT, 2, aux=pre, out=out),
                          args.iters, flush)

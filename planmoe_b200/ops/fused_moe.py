@@ -46,7 +46,7 @@ class _BufferSet:
     """Symmetric receive buffers + flags for one in-flight forward/backward of one layer."""
 
     def __init__(self, tr, key):
-        E_l, W, C, M, O = key
+        E_l, W, C, M, O = key[:5]
         self.tr = tr
         el = 2
         self.sz_x = E_l * W * C * M * el         # dispatch receive      [d][E_l][W][Cc][M]
@@ -194,7 +194,9 @@ class _FusedExperts(torch.autograd.Function):
         R = W * Cc                                  # rows per expert per chunk
         act = meta['act']
         postscore = meta['postscore']
-        bs = st.acquire((E_l, W, C, M, O))
+        # Buffer sets are keyed by the pipeline degree as well: the flags of a set are cumulative counters
+        # that advance together, chunk by chunk, only while every use has the same number of chunks.
+        bs = st.acquire((E_l, W, C, M, O, d))
         bases = bs.block.bases_ptr
         budget, status = tr.budget_ms, tr.status_ptr
         gates_f = gates.detach().contiguous()

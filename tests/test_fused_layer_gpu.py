@@ -78,6 +78,22 @@ def test_fused_layer_is_bit_reproducible_and_reuses_buffers():
     assert torch.equal(y, outs[0][0])
 
 
+def test_fused_layer_survives_degree_changes():
+    """The adaptive scheduler switches the pipeline degree between steps of one layer."""
+    layer = _layer(2, 256, 256, 2, 1.0)
+    x = torch.randn(1024, 256, device='cuda').to(torch.bfloat16)
+    outs = []
+    from planmoe_b200.parallel import transport
+    for d in (1, 2, 4, 1, 4, 2):
+        xi = x.clone().requires_grad_(True)
+        y = layer(xi, a2a_ffn_overlap_degree=d)
+        y.float().sum().backward()
+        transport.get_transport(layer.group).check()
+        outs.append(y.detach().clone())
+    for y in outs[1:]:
+        assert torch.equal(y, outs[0])
+
+
 def test_generic_cuda_path_matches_fused():
     """Same layer through the generic pipeline (torch.matmul experts) and through the fused path."""
     layer = _layer(4, 256, 256, 2, 2.0, act='relu')
