@@ -235,7 +235,8 @@ class MOELayer(torch.nn.Module):
             return False
         if self.experts_type != 'ffn' or self.sharded_count != 1:
             return False
-        if self.compress_name not in ('no', 'int8') or self.comm_name not in ('naive', 'pipe'):
+        # the fused kernels move raw bf16 rows; a codec takes the generic compress -> all-to-all -> decompress path
+        if self.compress_name != 'no' or self.comm_name not in ('naive', 'pipe'):
             return False
         if self.batch_prioritized_routing or not self.is_gshard_loss:
             return False
