@@ -153,9 +153,30 @@ Tensor dispatch_gate_grad_op(const Tensor& disp, const Tensor& dy, const Tensor&
   DISPATCH_FLOAT(disp, "dispatch_gate_grad", [&] {
     launch_gate_grad<scalar_t>(reinterpret_cast<const scalar_t*>(disp.data_ptr()),
                                reinterpret_cast<const scalar_t*>(dy.data_ptr()), idx.data_ptr<int>(),
-                               loc.data_ptr<int>(), out.data_ptr<float>(), K, S, M, C, cur_stream());
+                               loc.data_ptr<int>(), out.data_ptr<float>(), nullptr, nullptr, K, S, M, C, cur_stream());
   });
   return out;
+}
+
+// Gate gradient plus the gate-weighted copies of dy: returns (dgates [K, S] fp32, scaled [S * K, M]) with
+// scaled[t * K + k] = gates[k][t] * dy[t] for every pick that holds a slot (other rows are left unwritten).
+std::vector<Tensor> dispatch_gate_grad_scaled_op(const Tensor& disp, const Tensor& dy, const Tensor& idx,
+                                                 const Tensor& loc, const Tensor& gates, int64_t C) {
+  count_launch(1);
+  TORCH_CHECK(disp.is_cuda() && disp.is_contiguous() && dy.is_contiguous() && disp.scalar_type() == dy.scalar_type());
+  TORCH_CHECK(gates.is_cuda() && gates.scalar_type() == at::kFloat && gates.is_contiguous());
+  const int K = idx.size(0), S = idx.size(1), M = disp.size(1);
+  TORCH_CHECK(gates.numel() == (int64_t)K * S && dy.size(0) == S && dy.size(1) == M);
+  c10::cuda::CUDAGuard guard(disp.device());
+  Tensor out = torch::empty({K, S}, disp.options().dtype(at::kFloat));
+  Tensor scaled = torch::empty({(int64_t)S * K, (int64_t)M}, dy.options());
+  DISPATCH_FLOAT(disp, "dispatch_gate_grad_scaled", [&] {
+    launch_gate_grad<scalar_t>(reinterpret_cast<const scalar_t*>(disp.data_ptr()),
+                               reinterpret_cast<const scalar_t*>(dy.data_ptr()), idx.data_ptr<int>(),
+                               loc.data_ptr<int>(), out.data_ptr<float>(), gates.data_ptr<float>(),
+                               reinterpret_cast<scalar_t*>(scaled.data_ptr()), K, S, M, C, cur_stream());
+  });
+  return {out, scaled};
 }
 
 // ---- fused gate -------------------------------------------------------------------------------
@@ -551,6 +572,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("dispatch_scatter", &dispatch_scatter_op);
   m.def("dispatch_gather", &dispatch_gather_op);
   m.def("dispatch_gate_grad", &dispatch_gate_grad_op);
+  m.def("dispatch_gate_grad_scaled", &dispatch_gate_grad_scaled_op);
   m.def("gate_forward", &gate_forward_op);
   m.def("gate_backward", &gate_backward_op);
   m.def("cumsum_sub_one", &cumsum_sub_one_op);

@@ -314,10 +314,14 @@ void launch_gather_rows(const void* disp, const float* scale_bias, const int* id
     gather_rows_kernel<T, false, 8><<<ctas, kRowThreads, 0, stream>>>(disp, scale_bias, idx, loc, gates, out, K, S, M, C, w);
 }
 
+// dgates[k][t] = <disp[slot_k(t)], dy[t]>.  With `scaled` != null the same pass also writes the
+// gate-weighted rows scaled[t * K + k] = gates[k][t] * dy[t] (row index = the owner code of the slot
+// map), so that a following dispatch-style send can move them with plain bulk copies.
 template <class T>
 __global__ void __launch_bounds__(kRowThreads, 8)
 gate_grad_kernel(const T* __restrict__ disp, const T* __restrict__ dy, const int* __restrict__ idx,
-                 const int* __restrict__ loc, float* __restrict__ dgates, int K, int S, int M, int C) {
+                 const int* __restrict__ loc, float* __restrict__ dgates, const float* __restrict__ gates,
+                 T* __restrict__ scaled, int K, int S, int M, int C) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int V = Vec16<T>::N;
   const int nvec = M / V;
@@ -328,10 +332,25 @@ gate_grad_kernel(const T* __restrict__ disp, const T* __restrict__ dy, const int
       float acc = 0.f;
       if (e >= 0 && l >= 0 && l < C) {
         const T* a = disp + ((size_t)e * C + l) * M;
-        for (int v = lane; v < nvec; v += 32) {
-          Pack<T> pa = ld16(a + v * V), pb = ld16(b + v * V);
+        if (scaled != nullptr) {
+          const float gw = gates[(size_t)k * S + t];
+          T* o = scaled + ((size_t)t * K + k) * M;
+          for (int v = lane; v < nvec; v += 32) {
+            Pack<T> pa = ld16(a + v * V), pb = ld16(b + v * V), po;
 #pragma unroll
-          for (int i = 0; i < V; ++i) acc += to_f32(pa.v[i]) * to_f32(pb.v[i]);
+            for (int i = 0; i < V; ++i) {
+              const float fb = to_f32(pb.v[i]);
+              acc += to_f32(pa.v[i]) * fb;
+              po.v[i] = from_f32<T>(gw * fb);
+            }
+            st16(o + v * V, po);
+          }
+        } else {
+          for (int v = lane; v < nvec; v += 32) {
+            Pack<T> pa = ld16(a + v * V), pb = ld16(b + v * V);
+#pragma unroll
+            for (int i = 0; i < V; ++i) acc += to_f32(pa.v[i]) * to_f32(pb.v[i]);
+          }
         }
       }
       acc = warp_sum(acc);
@@ -342,11 +361,11 @@ gate_grad_kernel(const T* __restrict__ disp, const T* __restrict__ dy, const int
 
 template <class T>
 void launch_gate_grad(const T* disp, const T* dy, const int* idx, const int* loc, float* dgates,
-                      int K, int S, int M, int C, cudaStream_t stream) {
+                      const float* gates, T* scaled, int K, int S, int M, int C, cudaStream_t stream) {
   int ctas = (S + kRowWarps - 1) / kRowWarps;
   if (ctas > 148 * 8) ctas = 148 * 8;
   if (ctas < 1) ctas = 1;
-  gate_grad_kernel<T><<<ctas, kRowThreads, 0, stream>>>(disp, dy, idx, loc, dgates, K, S, M, C);
+  gate_grad_kernel<T><<<ctas, kRowThreads, 0, stream>>>(disp, dy, idx, loc, dgates, gates, scaled, K, S, M, C);
 }
 
 #define INSTANTIATE(T)                                                                             \
@@ -355,8 +374,8 @@ void launch_gate_grad(const T* disp, const T* dy, const int* idx, const int* loc
   template void launch_gather_rows<T>(const void*, const float*, const int*, const int*,           \
                                       const float*, T*, int, int, int, int, const WaitArgs*,       \
                                       cudaStream_t);                                               \
-  template void launch_gate_grad<T>(const T*, const T*, const int*, const int*, float*, int, int,  \
-                                    int, int, cudaStream_t);
+  template void launch_gate_grad<T>(const T*, const T*, const int*, const int*, float*, const float*, \
+                                    T*, int, int, int, int, cudaStream_t);
 INSTANTIATE(float)
 INSTANTIATE(__nv_bfloat16)
 INSTANTIATE(__half)

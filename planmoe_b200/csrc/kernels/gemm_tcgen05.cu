@@ -2,7 +2,7 @@
 //
 //   D[g] (M x N) = A[g] (M x K) . B[g] (K x N)          g = 0 .. groups-1, fp32 accumulate
 //
-// Hand-written tcgen05 pipeline, one persistent CTA per SM, 384 threads in four roles:
+// Hand-written tcgen05 pipeline, one persistent CTA per SM, 352 threads in four roles:
 //   warp 0      TMA producer: cp.async.bulk.tensor (4-D maps, 128-byte swizzle) into a 4-stage
 //               shared-memory ring, completion on mbarriers.  When the A operand is a receive
 //               buffer that peer GPUs fill, the producer first acquire-waits (bounded) on the
@@ -16,12 +16,16 @@
 //               derivative) / multiply by a saved derivative -> bf16 -> swizzled shared-memory staging -> full-line 16-byte stores,
 //               either to local memory or straight into the combine buffer of the rank that
 //               owns the token ("push"), followed by a release-add on that rank's flag.
-//   warps 10,11 dispatch send (optional): while the tensor cores work, these two warps of every CTA
-//               gather token rows by slot map and store them straight into the receive buffers of
-//               the ranks that own the experts, chunk by chunk, then release-add the (chunk, rank)
-//               flags there.  The same launch's producers on every rank are the flag-gated
+//   warp 10     dispatch send (optional): while the tensor cores work, this warp of every CTA moves
+//               token rows into the receive buffers of the ranks that own the experts with the
+//               bulk-copy engine: cp.async.bulk global -> shared (row picked by slot map), an
+//               optional gate scaling in shared memory, cp.async.bulk shared -> peer global; seven
+//               4 KiB slots are in flight per CTA, one per lane.  Chunks leave in order; after a
+//               chunk its stores are awaited and the (chunk, rank) flags on every destination get
+//               a release-add.  The producers of the same launch on every rank are the flag-gated
 //               consumers, so the all-to-all and the GEMM that follows it are one kernel and
-//               overlap tile by tile; the copy never waits, so no circular wait can form.
+//               overlap tile by tile; the copy never waits on another CTA or rank, so no circular
+//               wait can form.
 //
 // Operands may be K-major or MN-major (weights are stored input-major, and the weight-gradient
 // GEMMs contract over the token dimension), so all four FFN GEMM flavours — forward, dgrad,
@@ -51,28 +55,31 @@ namespace {
 constexpr int BM = 128, BN = 256, BK = 64;       // BM = accumulator rows per CTA (TMEM lanes)
 constexpr int UMMA_K = 16;
 constexpr int kAccStages = 2;
-constexpr int kThreads = 384;
-constexpr int kCopyWarps = 2;                     // warps 10 and 11
+constexpr int kThreads = 352;                     // TMA, MMA, 8 epilogue warps, copy warp
+constexpr uint32_t kCopySlot = 4096;              // bytes per bulk-copy slot (one bf16 row of 2048, or a piece of a longer row)
+constexpr int kCopyLanes = 7;                     // data slots = lanes of the copy warp that drive the bulk-copy engine
+constexpr uint32_t kSmemCopy = (kCopyLanes + 1) * kCopySlot;   // + one slot of zeros for empty expert slots
 constexpr int kEpiWarps = 8;
 constexpr uint32_t kABytes = BM * BK * 2;          // 16 KiB
 constexpr uint32_t kStagingPerWarp = 32 * 128;     // one 32-row x 128-byte tile
 constexpr uint32_t kSmemStaging = kEpiWarps * kStagingPerWarp;
 constexpr uint32_t kSmemBias = BN * 4;
-constexpr uint32_t kSmemBars = 256;
+constexpr uint32_t kSmemBars = 512;
 
 // Per-CTA geometry by CTA-group size CG.  CG = 1: one CTA computes a 128 x 256 tile from a 16 KiB A
 // block and a 32 KiB B block per 64-deep K step.  CG = 2: a cluster of two CTAs computes a 256 x 256
 // tile with one tcgen05.mma.cta_group::2 stream issued by the even CTA; each CTA stages its own 128
 // rows of A and its own 128 of the 256 B columns (16 KiB each), so a K step costs 32 KiB of shared
-// memory traffic per CTA instead of 48 and the ring is 6 deep instead of 4.
+// memory traffic per CTA instead of 48 and the ring is 5 deep instead of 3.
 template <int CG> struct Geo {
   static constexpr int kBRows = BN / CG;                        // B columns staged per CTA
   static constexpr uint32_t kBBytes = kBRows * BK * 2;
   static constexpr uint32_t kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = CG == 1 ? 4 : 6;
+  static constexpr int kStages = CG == 1 ? 3 : 5;
   static constexpr uint32_t kSmemRing = kStages * kStageBytes;
+  // ring | epilogue staging | bulk-copy slots of the dispatch send | bias | barriers.
   // No alignment slack: the dynamic shared array is declared 1024-byte aligned.
-  static constexpr uint32_t kSmemTotal = kSmemRing + kSmemStaging + kSmemBias + kSmemBars;
+  static constexpr uint32_t kSmemTotal = kSmemRing + kSmemStaging + kSmemCopy + kSmemBias + kSmemBars;
 };
 constexpr int kMaxStages = 6;
 constexpr uint32_t kTmemCols = 512;
@@ -253,6 +260,7 @@ struct Ctl {
   uint64_t empty[kMaxStages];
   uint64_t acc_full[kAccStages];
   uint64_t acc_empty[kAccStages];
+  uint64_t copy_full[kCopyLanes];   // a row has landed in bulk-copy slot i
   uint32_t tmem_base;
   volatile int abort;
   volatile int epi_abort[2];   // written by epilogue warps before a barrier, read after it
@@ -329,92 +337,127 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// Copy role (warps 10 and 11 of every CTA): the dispatch send.  Slot-major gather of token rows
-// (optionally gate-weighted), stored with full-line 16-byte stores straight into the receive buffer
-// [chunk][E_local][W_src][C/chunks][M] of the rank that owns the expert.  Chunks leave in order;
-// after a chunk has been stored for every destination the two warps meet on a named barrier, fence
-// once and add one arrival to the (chunk, my_rank) flag of every destination, so a flag is complete
-// after one arrival per CTA of the grid.  The role never waits on another CTA or rank.  Each warp
-// keeps two rows (16 x 16 bytes per lane) in flight to cover the load latency.
+// Copy role (warp 10 of every CTA): the dispatch send, driven by the bulk-copy engine.
+//
+// A unit is one token row (or a 4 KiB piece of a longer row) for one destination.  The CTA owns the
+// rows blockIdx.x, blockIdx.x + gridDim.x, ... of every (chunk, destination).  Units are handled in
+// batches of seven, one per lane: the lane looks up the slot map, starts a bulk load of the token row
+// into its shared-memory slot (or, for an empty expert slot, a bulk store of the zero slot), waits
+// (bounded) for the row, the warp scales gate-weighted rows in shared memory, and the lane starts the
+// bulk store into the receive buffer [chunk][E_local][W_src][C/chunks][M] of the destination rank.
+// After a chunk every lane waits for its stores to complete, then the warp fences and adds one
+// arrival to the (chunk, my_rank) flag of every destination: one arrival per CTA of the grid.
 // ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint4 scale_bf16x8(uint4 v, float g) {
-  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float2 f = __bfloat1622float2(h[i]);
-    h[i] = __floats2bfloat162_rn(f.x * g, f.y * g);
-  }
-  return v;
+__device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
+__device__ __forceinline__ void bulk_store(void* dst, uint32_t src_smem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src_smem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
-__device__ __noinline__ void copy_role(const KernelParams& p, int cwarp) {
+__device__ __forceinline__ void copy_role(const KernelParams& p, uint8_t* cring, Ctl* ctl) {
   const GemmArgs::CopyJob& c = p.copy;
-  constexpr int U = 8;                               // 16-byte vectors per lane per row and pass
-  const int Cc = c.C / c.chunks;
-  const int rows = c.E_local * Cc;
   const int lane = threadIdx.x & 31;
-  const int ctid = cwarp * 32 + lane;                // 0 .. 63 inside the copy group
-  const int nvec = c.M >> 3;
-  const int wid = (int)blockIdx.x * kCopyWarps + cwarp, nw = (int)gridDim.x * kCopyWarps;
-  const uint4* x = reinterpret_cast<const uint4*>(c.x);
+  const int Cc = c.C / c.chunks;
+  const int rows = c.E_local * Cc;                               // rows per (chunk, destination)
+  const uint32_t row_bytes = (uint32_t)c.M * 2u;
+  const int pieces = (int)((row_bytes + kCopySlot - 1) / kCopySlot);
+  const int my_rows = ((int)blockIdx.x < rows) ? (rows - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+  const int units = p.W * my_rows * pieces;                      // per chunk, for this CTA
+  const uint8_t* x = reinterpret_cast<const uint8_t*>(c.x);
+  uint8_t* my_slot = cring + lane * kCopySlot;
+  const uint32_t my_slot_s = smem_u32(my_slot);
+  const uint32_t zero_s = smem_u32(cring + kCopyLanes * kCopySlot);
+  const uint32_t my_bar = smem_u32(&ctl->copy_full[lane < kCopyLanes ? lane : 0]);
+  uint32_t phase = 0;                                            // parity of my slot's barrier
+  bool ok = true;
 
-  for (int j = 0; j < c.chunks; ++j) {
-    for (int rr = 0; rr < p.W; ++rr) {
-      // destinations start at my right-hand neighbour, staggered by CTA so that all links are busy
-      const int r = (p.my_rank + 1 + rr + (int)blockIdx.x) % p.W;
-      uint4* dst_base = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.heap_bases[r]) + c.data_off);
-      for (int row0 = wid; row0 < rows; row0 += 2 * nw) {
-        const uint4* src[2];
-        uint4* dst[2];
-        float gw[2];
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int row = row0 + h * nw;
-          src[h] = nullptr; dst[h] = nullptr; gw[h] = 1.f;
-          if (row < rows) {
-            const int el = row / Cc, cc = row - el * Cc;
-            const int owner = c.slot_map[(size_t)(r * c.E_local + el) * c.C + j * Cc + cc];
-            dst[h] = dst_base + ((((size_t)j * c.E_local + el) * p.W + p.my_rank) * Cc + cc) * nvec;
-            if (owner >= 0) {
-              const int t = owner / c.K, k = owner - t * c.K;
-              src[h] = x + (size_t)t * nvec;
-              if (c.gates != nullptr) gw[h] = c.gates[(size_t)k * c.S + t];
-            }
-          }
-        }
-        for (int v0 = 0; v0 < nvec; v0 += 32 * U) {
-          uint4 buf[2][U];
-#pragma unroll
-          for (int h = 0; h < 2; ++h)
-#pragma unroll
-            for (int i = 0; i < U; ++i) {
-              const int v = v0 + i * 32 + lane;
-              buf[h][i] = make_uint4(0, 0, 0, 0);
-              if (src[h] != nullptr && v < nvec) buf[h][i] = __ldg(src[h] + v);
-            }
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            if (dst[h] == nullptr) continue;
-            const bool scaled = gw[h] != 1.f;
-#pragma unroll
-            for (int i = 0; i < U; ++i) {
-              const int v = v0 + i * 32 + lane;
-              if (v < nvec) dst[h][v] = scaled ? scale_bf16x8(buf[h][i], gw[h]) : buf[h][i];
-            }
-          }
+  for (uint32_t i = lane; i < kCopySlot / 16; i += 32)
+    reinterpret_cast<uint4*>(cring + kCopyLanes * kCopySlot)[i] = make_uint4(0, 0, 0, 0);
+  fence_proxy_async();                                           // zeros visible to the bulk-copy engine
+  __syncwarp();
+
+  for (int j = 0; j < c.chunks && ok; ++j) {
+    for (int base = 0; base < units; base += kCopyLanes) {
+      const int u = base + lane;
+      const bool mine = lane < kCopyLanes && u < units;
+      bool loaded = false;
+      float gw = 1.f;
+      uint8_t* dst = nullptr;
+      uint32_t bytes = 0;
+      if (mine) {
+        const int piece = u % pieces;
+        const int k = (u / pieces) % my_rows;
+        const int rr = u / (pieces * my_rows);
+        // destinations start at my right-hand neighbour, staggered by CTA so that all links are busy
+        const int r = (p.my_rank + 1 + rr + (int)blockIdx.x) % p.W;
+        const int row = (int)blockIdx.x + k * (int)gridDim.x;
+        const int el = row / Cc, cc = row - el * Cc;
+        const int owner = c.slot_map[(size_t)(r * c.E_local + el) * c.C + j * Cc + cc];
+        bytes = min(kCopySlot, row_bytes - (uint32_t)piece * kCopySlot);
+        dst = reinterpret_cast<uint8_t*>(p.heap_bases[r]) + c.data_off +
+              ((((size_t)j * c.E_local + el) * p.W + p.my_rank) * Cc + cc) * row_bytes + (size_t)piece * kCopySlot;
+        bulk_wait_read_all();                                    // my previous store has left the slot
+        if (owner >= 0) {
+          const int t = owner / c.K, kk = owner - t * c.K;
+          if (c.gates != nullptr) gw = c.gates[(size_t)kk * c.S + t];
+          mbar_expect_tx(my_bar, bytes);
+          bulk_load(my_slot_s, x + (size_t)t * row_bytes + (size_t)piece * kCopySlot, bytes, my_bar);
+          loaded = true;
+        } else {
+          bulk_store(dst, zero_s, bytes);                        // empty expert slot: a row of zeros
+          bulk_commit();
         }
       }
+      if (loaded) {
+        ok = mbar_wait(my_bar, phase, ctl, p.budget_ns, p.status, 3, lane);
+        phase ^= 1u;
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      // gate-weighted rows (pre-score dispatch, gate-weighted dY): scale in shared memory, the whole
+      // warp on one slot at a time
+      unsigned scaled = __ballot_sync(0xffffffffu, loaded && gw != 1.f);
+      while (scaled) {
+        const int sl = __ffs(scaled) - 1;
+        scaled &= scaled - 1;
+        const float g = __shfl_sync(0xffffffffu, gw, sl);
+        const uint32_t nb = __shfl_sync(0xffffffffu, bytes, sl);
+        uint4* q = reinterpret_cast<uint4*>(cring + sl * kCopySlot);
+        for (uint32_t i = lane; i < nb / 16; i += 32) {
+          uint4 v = q[i];
+          __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(h[e]);
+            h[e] = __floats2bfloat162_rn(f.x * g, f.y * g);
+          }
+          q[i] = v;
+        }
+        fence_proxy_async();                                     // my writes -> the bulk store below
+      }
+      __syncwarp();
+      if (loaded) {
+        bulk_store(dst, my_slot_s, bytes);
+        bulk_commit();
+      }
     }
-    // chunk j stored everywhere by this CTA: publish it
-    asm volatile("bar.sync 2, 64;" ::: "memory");
-    if (ctid == 0) __threadfence_system();
-    asm volatile("bar.sync 2, 64;" ::: "memory");
-    if (ctid < p.W) {
+    // chunk j handed to the copy engine everywhere: wait for the stores, then publish it
+    bulk_wait_all();
+    __syncwarp();
+    if (lane == 0) __threadfence_system();
+    __syncwarp();
+    if (lane < p.W) {
       unsigned long long* flags = reinterpret_cast<unsigned long long*>(
-          reinterpret_cast<uint8_t*>(p.heap_bases[ctid]) + c.flag_off);
+          reinterpret_cast<uint8_t*>(p.heap_bases[lane]) + c.flag_off);
       red_release_sys_add(flags + (size_t)j * p.W + p.my_rank, 1ull);
     }
   }
+  bulk_wait_all();                                               // nothing of mine is in flight at teardown
 }
 
 // Bias + activation on one thread's 64 accumulator values: the packed activation goes to `opk`, the
@@ -455,8 +498,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int unit = (int)blockIdx.x / CG, nunits = (int)gridDim.x / CG;
   uint8_t* ring = smem;
   uint8_t* staging = smem + G::kSmemRing;
-  float* bias_s = reinterpret_cast<float*>(smem + G::kSmemRing + kSmemStaging);
-  Ctl* ctl = reinterpret_cast<Ctl*>(smem + G::kSmemRing + kSmemStaging + kSmemBias);
+  uint8_t* cring = smem + G::kSmemRing + kSmemStaging;
+  float* bias_s = reinterpret_cast<float*>(smem + G::kSmemRing + kSmemStaging + kSmemCopy);
+  Ctl* ctl = reinterpret_cast<Ctl*>(smem + G::kSmemRing + kSmemStaging + kSmemCopy + kSmemBias);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -472,6 +516,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       mbar_init(smem_u32(&ctl->acc_full[a]), 1);
       mbar_init(smem_u32(&ctl->acc_empty[a]), kEpiWarps * CG);     // the epilogue warps of every CTA of the group
     }
+    for (int i = 0; i < kCopyLanes; ++i) mbar_init(smem_u32(&ctl->copy_full[i]), 1);
     ctl->abort = 0;
     ctl->epi_abort[0] = ctl->epi_abort[1] = 0;
     fence_barrier_init();
@@ -576,8 +621,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     __syncwarp();
   } else if (warp >= 2 + kEpiWarps) {
-    // ------------------------------------------------------------------ dispatch send (2 warps)
-    if (p.copy.ctas > 0) copy_role(p, warp - (2 + kEpiWarps));
+    // ------------------------------------------------------------------ dispatch send (copy warp)
+    if (p.copy.ctas > 0) copy_role(p, cring, ctl);
   } else {
     // ------------------------------------------------------------------ epilogue warps (8)
     // Warp pairs share a TMEM lane quarter (warp % 4); each warp of a pair drains one 128-column

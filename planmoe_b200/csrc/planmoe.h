@@ -50,9 +50,10 @@ template <class T>
 void launch_gather_rows(const void* disp, const float* scale_bias, const int* idx, const int* loc,
                         const float* gates, T* out, int K, int S, int M, int C, const WaitArgs* wait,
                         cudaStream_t stream);
+// `gates` / `scaled` optional: also write scaled[t * K + k] = gates[k][t] * dy[t]
 template <class T>
 void launch_gate_grad(const T* disp, const T* dy, const int* idx, const int* loc, float* dgates,
-                      int K, int S, int M, int C, cudaStream_t stream);
+                      const float* gates, T* scaled, int K, int S, int M, int C, cudaStream_t stream);
 
 // ---- kernels/gate.cu -------------------------------------------------------------------------
 int gate_workspace_blocks(int S);

@@ -254,7 +254,15 @@ class _FusedExperts(torch.autograd.Function):
 
         recv_y = bs.view(bs.off_y, (E * C, O))
         dgates = None
-        if postscore and ctx.needs_input_grad[1]:
+        send_src, send_gates, send_K = dout, (gates_f if postscore else None), K
+        if postscore and _fuse_send(W):
+            # The fused send moves rows with the bulk-copy engine, which cannot scale them: the gate-gradient
+            # pass, which reads every dY row anyway, also writes the gate-weighted copies (row = token * K + k,
+            # the owner code of the slot map), and the send then moves those as they are.
+            with stage('bwd.gate_grad'):
+                dgates, send_src = lib.dispatch_gate_grad_scaled(recv_y, dout, idx, loc, gates_f, C)
+            send_gates, send_K = None, 1
+        elif postscore and ctx.needs_input_grad[1]:
             with stage('bwd.gate_grad'):
                 dgates = lib.dispatch_gate_grad(recv_y, dout, idx, loc, C)
 
@@ -269,7 +277,7 @@ class _FusedExperts(torch.autograd.Function):
                          gate_flags_ptr=bs.flag_ptr(PH_COMBINE_BWD, 0), gate_rows=Cc, gate_want=want,
                          chunk_groups=E_l, W=W, my_rank=rank, budget_ms=budget, status_ptr=status, **copy)
         with stage('bwd.combine_bwd_send+dgrad2'):
-            _send_and_gemm(lib, bs, PH_COMBINE_BWD, dout, slot_map, gates_f if postscore else None, K, E, C, W, rank,
+            _send_and_gemm(lib, bs, PH_COMBINE_BWD, send_src, slot_map, send_gates, send_K, E, C, W, rank,
                            d, lib.gemm_grid_ctas(d * E_l, R, H), dgrad2)
         push_arrivals = lib.gemm_push_arrivals(E_l, R, M, Cc, rank)
         # dX slots = dH . W1^T, pushed back to the token owners

@@ -49,15 +49,17 @@ class A2AChannel:
         self.L = _local_size(self.W)
         self.calls = 0
         self.bufs = {}          # (algo, parity) -> dict(name -> HeapBlock), sized for `cap` bytes per pair
-        self.flags = None       # HeapBlock: [parity 2][phase 4][W] u64
-        self.arrived = {}       # (parity, phase) -> cumulative arrivals expected per flag
+        self.flags = {}         # algo -> HeapBlock: [parity 2][phase 4][W] u64
+        self.arrived = {}       # (algo, parity, phase) -> cumulative arrivals expected per flag
         self.tables = {}
         self.side = None
 
     # -- resources ----------------------------------------------------------------------------
     def _ensure(self, algo, parity, n):
-        if self.flags is None:
-            self.flags = self.tr.alloc(2 * self.N_PHASES * self.W * 8)
+        # Flags are cumulative counters, and which flags a call advances depends on the algorithm (in the
+        # hierarchical ones only group leaders receive some phases), so every algorithm owns its flags.
+        if algo not in self.flags:
+            self.flags[algo] = self.tr.alloc(2 * self.N_PHASES * self.W * 8)
         key = (algo, parity)
         cur = self.bufs.get(key)
         if cur is not None and cur['cap'] >= n:
@@ -76,11 +78,11 @@ class A2AChannel:
         self.tables = {k: v for k, v in self.tables.items() if k[:2] != key}
         return cur
 
-    def _flag_off(self, parity, phase):
-        return self.flags.offset + ((parity * self.N_PHASES + phase) * self.W) * 8
+    def _flag_off(self, algo, parity, phase):
+        return self.flags[algo].offset + ((parity * self.N_PHASES + phase) * self.W) * 8
 
-    def _flag_ptr(self, parity, phase):
-        return self.flags.local_ptr + ((parity * self.N_PHASES + phase) * self.W) * 8
+    def _flag_ptr(self, algo, parity, phase):
+        return self.flags[algo].local_ptr + ((parity * self.N_PHASES + phase) * self.W) * 8
 
     # -- message tables ---------------------------------------------------------------------------
     def _plan(self, algo, parity, n, bufs):
@@ -175,7 +177,7 @@ class A2AChannel:
 
         # cumulative arrivals every flag of every pushing phase will have reached after this call
         for logical, per_call in arrivals.items():
-            key = (parity, logical)
+            key = (algo, parity, logical)
             self.arrived[key] = self.arrived.get(key, 0) + per_call * self._ctas(algo, logical, n)
 
         cur = torch.cuda.current_stream(tr.device)
@@ -186,14 +188,14 @@ class A2AChannel:
             src_ptr = t.data_ptr() if ph.src == 'in' else bufs[ph.src].local_ptr
             want, wait_ptr = 0, 0
             if ph.wait_phase is not None:
-                want = self.arrived[(parity, ph.wait_phase)]
-                wait_ptr = self._flag_ptr(parity, ph.wait_phase)
+                want = self.arrived[(algo, parity, ph.wait_phase)]
+                wait_ptr = self._flag_ptr(algo, parity, ph.wait_phase)
             if ph.logical is None:
                 ctas = max(1, min(592 // max(msgs.size(0), 1), max(1, n >> 16)))
                 flag_off = 0
             else:
                 ctas = self._ctas(algo, ph.logical, n)
-                flag_off = self._flag_off(parity, ph.logical)
+                flag_off = self._flag_off(algo, parity, ph.logical)
             if ph.stream == 0:
                 for ev in side_events:
                     cur.wait_event(ev)
