@@ -545,7 +545,7 @@ void xfer_op(int64_t src_ptr, const Tensor& msgs, int64_t ctas_per_msg, int64_t 
              int64_t status_ptr, int64_t local_dst_ptr) {
   count_launch(1);
   TORCH_CHECK(msgs.is_cuda() && msgs.scalar_type() == at::kLong && msgs.is_contiguous() && msgs.dim() == 2 &&
-              msgs.size(1) == 5, "msgs must be a contiguous CUDA int64 [n, 5] tensor");
+              msgs.size(1) == 6, "msgs must be a contiguous CUDA int64 [n, 6] tensor");
   c10::cuda::CUDAGuard guard(msgs.device());
   const int n_wait = (wait_idx.has_value() && wait_idx->defined()) ? wait_idx->numel() : 0;
   launch_xfer(reinterpret_cast<const void*>(src_ptr), reinterpret_cast<const long long*>(msgs.data_ptr<int64_t>()),

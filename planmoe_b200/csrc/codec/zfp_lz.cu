@@ -2,7 +2,7 @@
 //
 // ZFP: one thread per 4x4 block; a thread reads four 4-element row segments (neighbouring threads
 // read neighbouring segments, so rows are read coalesced) and writes its 2*rate-byte code word with
-// 16-byte stores.  LZ: one thread per 2 KiB block for both directions, then a per-slice scan and a
+// 16-byte stores.  LZ: one warp per 2 KiB block for both directions, then a per-slice scan and a
 // compaction copy pack the blocks back to back.  Both reuse the host/device block coders of
 // codec_core.h, so the CUDA streams are bit-identical to the CPU oracle.
 //
@@ -133,13 +133,130 @@ __host__ __device__ inline void lz_decode_one(const uint8_t* packed, uint8_t* ra
 }
 
 // scratch layout: [slices][nb] slots of kLzSlotBytes, then int sizes [slices][nb]
-__global__ void __launch_bounds__(64)
-lz_encode_blocks_kernel(const uint8_t* raw, uint8_t* slots, int* blk_sizes, long long slices, long long raw_bytes, int sym) {
+//
+// Warp-parallel block coder.  One warp codes one 2 KiB block and produces exactly the bytes of the
+// serial coder lz_encode_block (the CPU twin, which the tests compare against):
+//   1. every lane finds, for its positions p = lane, lane + 32, ..., the longest match in the 32-symbol
+//      window (first candidate of maximal length), as the serial coder would if a token started at p;
+//   2. the token starts are the positions reachable from 0 by next(p) = p + (match ? length : 1); they are
+//      marked with ten rounds of pointer doubling (2^10 >= symbols per block);
+//   3. token ordinals and data offsets come from a warp scan over contiguous 32-position segments;
+//   4. flags and data are assembled in shared memory and copied to the block's slot.
+constexpr int kLzWarps = 4;                       // blocks coded per CTA
+constexpr int kLzMaxSym = kLzBlockBytes / 2;      // symbols per block with 16-bit symbols
+
+template <class Sym>
+struct LzEncSmem {
+  Sym in[kLzBlockBytes / sizeof(Sym)];
+  uint8_t best[kLzMaxSym];                        // match length at p (0 = literal)
+  uint8_t dist[kLzMaxSym];                        // p - candidate
+  uint16_t jump[2][kLzMaxSym];                    // pointer doubling, double buffered
+  uint8_t mark[kLzMaxSym];                        // p starts a token
+  uint32_t flagw[kLzMaxSym / 32];                 // one bit per token: 1 = match
+  uint8_t data[kLzBlockBytes];                    // token payload
+};
+
+template <class Sym>
+__device__ __forceinline__ void lz_encode_block_warp(const Sym* __restrict__ g_in, int nsym, uint8_t* __restrict__ out,
+                                                     int* __restrict__ out_size, LzEncSmem<Sym>& sm, int lane) {
+  constexpr int min_match = sizeof(Sym) == 2 ? 2 : 1;
+  for (int i = lane; i < nsym; i += 32) sm.in[i] = g_in[i];
+  for (int i = lane; i < kLzMaxSym / 32; i += 32) sm.flagw[i] = 0u;
+  __syncwarp();
+
+  // 1. longest match per position
+  for (int p = lane; p < nsym; p += 32) {
+    int best = 0, bestc = 0;
+    const int w0 = p - kLzWindow < 0 ? 0 : p - kLzWindow;
+    const int lim = nsym - p < kLzMaxMatch ? nsym - p : kLzMaxMatch;
+    const Sym first = sm.in[p];
+    for (int c = w0; c < p; ++c) {
+      if (sm.in[c] != first) continue;
+      int len = 1;
+      while (len < lim && sm.in[c + len] == sm.in[p + len]) ++len;
+      if (len > best) { best = len; bestc = c; }
+    }
+    const bool match = best >= min_match && best > 0;
+    sm.best[p] = (uint8_t)(match ? best : 0);
+    sm.dist[p] = (uint8_t)(p - bestc);
+    const int nx = p + (match ? best : 1);
+    sm.jump[0][p] = (uint16_t)(nx < nsym ? nx : nsym);
+    sm.mark[p] = p == 0 ? 1 : 0;
+  }
+  __syncwarp();
+
+  // 2. token starts = positions reachable from 0
+  int cur = 0;
+  for (int hop = 1; hop < nsym; hop <<= 1) {
+    for (int p = lane; p < nsym; p += 32) {
+      const int j = sm.jump[cur][p];
+      if (sm.mark[p] && j < nsym) sm.mark[j] = 1;
+      sm.jump[cur ^ 1][p] = (uint16_t)(j < nsym ? sm.jump[cur][j] : nsym);
+    }
+    __syncwarp();
+    cur ^= 1;
+  }
+
+  // 3. ordinals and data offsets: lane owns positions [lane * seg, lane * seg + seg)
+  const int seg = (nsym + 31) / 32;
+  const int p0 = lane * seg, p1 = p0 + seg < nsym ? p0 + seg : nsym;
+  int ntok_l = 0, bytes_l = 0;
+  for (int p = p0; p < p1; ++p) {
+    if (sm.mark[p]) { ++ntok_l; bytes_l += sm.best[p] ? 2 : (int)sizeof(Sym); }
+  }
+  int tok_incl = ntok_l, byt_incl = bytes_l;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, tok_incl, o);
+    const int b = __shfl_up_sync(0xffffffffu, byt_incl, o);
+    if (lane >= o) { tok_incl += t; byt_incl += b; }
+  }
+  const int ntok = __shfl_sync(0xffffffffu, tok_incl, 31);
+  const int dbytes = __shfl_sync(0xffffffffu, byt_incl, 31);
+  int t = tok_incl - ntok_l, dpos = byt_incl - bytes_l;
+
+  // 4. flags + data
+  for (int p = p0; p < p1; ++p) {
+    if (!sm.mark[p]) continue;
+    if (sm.best[p]) {
+      atomicOr(&sm.flagw[t >> 5], 1u << (t & 31));
+      sm.data[dpos++] = sm.best[p];
+      sm.data[dpos++] = sm.dist[p];
+    } else {
+      const uint32_t v = (uint32_t)sm.in[p];
+#pragma unroll
+      for (unsigned b = 0; b < sizeof(Sym); ++b) sm.data[dpos++] = (uint8_t)(v >> (8 * b));
+    }
+    ++t;
+  }
+  __syncwarp();
+  const int flag_bytes = (ntok + 7) >> 3;
+  if (lane == 0) {
+    out[0] = (uint8_t)(ntok & 0xff);
+    out[1] = (uint8_t)(ntok >> 8);
+    *out_size = 2 + flag_bytes + dbytes;
+  }
+  const uint8_t* fb = reinterpret_cast<const uint8_t*>(sm.flagw);
+  for (int i = lane; i < flag_bytes; i += 32) out[2 + i] = fb[i];
+  uint8_t* od = out + 2 + flag_bytes;
+  for (int i = lane; i < dbytes; i += 32) od[i] = sm.data[i];
+  __syncwarp();
+}
+
+template <class Sym>
+__global__ void __launch_bounds__(kLzWarps * 32)
+lz_encode_blocks_kernel(const uint8_t* raw, uint8_t* slots, int* blk_sizes, long long slices, long long raw_bytes) {
+  extern __shared__ __align__(16) uint8_t lz_smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  LzEncSmem<Sym>& sm = reinterpret_cast<LzEncSmem<Sym>*>(lz_smem)[warp];
   const long long nb = lz_blocks(raw_bytes);
-  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long i = (long long)blockIdx.x * kLzWarps + warp;
   if (i >= slices * nb) return;
   const long long s = i / nb, b = i - s * nb;
-  blk_sizes[i] = lz_encode_one(raw + s * raw_bytes, raw_bytes, b, sym, slots + i * kLzSlotBytes);
+  const long long off = b * kLzBlockBytes;
+  const int bytes = (int)(raw_bytes - off < kLzBlockBytes ? raw_bytes - off : kLzBlockBytes);
+  lz_encode_block_warp<Sym>(reinterpret_cast<const Sym*>(raw + s * raw_bytes + off), bytes / (int)sizeof(Sym),
+                            slots + i * kLzSlotBytes, blk_sizes + i, sm, lane);
 }
 
 // one CTA per slice: exclusive scan of the block sizes -> header of the slice payload
@@ -192,16 +309,96 @@ lz_compact_kernel(const uint8_t* slots, const int* blk_sizes, uint8_t* payload, 
   for (int k = threadIdx.x & 31; k < n; k += 32) dst[k] = src[k];
 }
 
-__global__ void __launch_bounds__(64)
-lz_decode_blocks_kernel(const uint8_t* payload, uint8_t* raw, long long slices, long long raw_bytes, long long payload_stride,
-                        int sym) {
+// Warp-parallel block decoder (same output as lz_decode_block).  Tokens are expanded to a source map
+// (a literal is its own source; symbol i of a match sources position p - distance) from a warp scan of
+// token lengths; sources are resolved to literals with ten rounds of pointer doubling, because a match
+// may copy symbols that an earlier (or the same, overlapping) match produced.
+template <class Sym>
+struct LzDecSmem {
+  uint8_t code[kLzSlotBytes + 2];                 // the block's code bytes
+  Sym val[kLzBlockBytes / sizeof(Sym)];           // literal value at p (defined where src[p] == p)
+  uint16_t src[2][kLzMaxSym];
+};
+
+template <class Sym>
+__device__ __forceinline__ void lz_decode_block_warp(const uint8_t* __restrict__ g_code, int code_bytes,
+                                                     Sym* __restrict__ g_out, int nsym, LzDecSmem<Sym>& sm, int lane) {
+  for (int i = lane; i < code_bytes; i += 32) sm.code[i] = g_code[i];
+  for (int q = lane; q < nsym; q += 32) { sm.src[0][q] = (uint16_t)q; sm.val[q] = (Sym)0; }   // defined even for a short code
+  __syncwarp();
+  const int ntok = (int)sm.code[0] | ((int)sm.code[1] << 8);
+  const uint8_t* flags = sm.code + 2;
+  const uint8_t* data = flags + ((ntok + 7) >> 3);
+
+  // lane owns tokens [t0, t1): first their data bytes, then (needs the lengths) their output symbols
+  const int seg = (ntok + 31) / 32;
+  const int t0 = lane * seg < ntok ? lane * seg : ntok, t1 = t0 + seg < ntok ? t0 + seg : ntok;
+  int byt_l = 0;
+  for (int t = t0; t < t1; ++t) byt_l += ((flags[t >> 3] >> (t & 7)) & 1u) ? 2 : (int)sizeof(Sym);
+  int byt_incl = byt_l;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int b = __shfl_up_sync(0xffffffffu, byt_incl, o);
+    if (lane >= o) byt_incl += b;
+  }
+  int dpos = byt_incl - byt_l;
+  int sym_l = 0;
+  {
+    int d = dpos;
+    for (int t = t0; t < t1; ++t) {
+      if ((flags[t >> 3] >> (t & 7)) & 1u) { sym_l += data[d]; d += 2; }
+      else { sym_l += 1; d += (int)sizeof(Sym); }
+    }
+  }
+  int sym_incl = sym_l;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int b = __shfl_up_sync(0xffffffffu, sym_incl, o);
+    if (lane >= o) sym_incl += b;
+  }
+  int p = sym_incl - sym_l;
+  for (int t = t0; t < t1; ++t) {
+    if ((flags[t >> 3] >> (t & 7)) & 1u) {
+      const int len = data[dpos], dist = data[dpos + 1];
+      dpos += 2;
+      for (int i = 0; i < len && p < nsym; ++i, ++p) sm.src[0][p] = (uint16_t)(p - dist > 0 ? p - dist : 0);
+    } else {
+      uint32_t v = 0;
+#pragma unroll
+      for (unsigned b = 0; b < sizeof(Sym); ++b) v |= (uint32_t)data[dpos++] << (8 * b);
+      if (p < nsym) { sm.val[p] = (Sym)v; sm.src[0][p] = (uint16_t)p; }
+      ++p;
+    }
+  }
+  __syncwarp();
+  int cur = 0;
+  for (int hop = 1; hop < nsym; hop <<= 1) {
+    for (int q = lane; q < nsym; q += 32) sm.src[cur ^ 1][q] = sm.src[cur][sm.src[cur][q]];
+    __syncwarp();
+    cur ^= 1;
+  }
+  for (int q = lane; q < nsym; q += 32) g_out[q] = sm.val[sm.src[cur][q]];
+  __syncwarp();
+}
+
+template <class Sym>
+__global__ void __launch_bounds__(kLzWarps * 32)
+lz_decode_blocks_kernel(const uint8_t* payload, uint8_t* raw, long long slices, long long raw_bytes, long long payload_stride) {
+  extern __shared__ __align__(16) uint8_t lz_smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  LzDecSmem<Sym>& sm = reinterpret_cast<LzDecSmem<Sym>*>(lz_smem)[warp];
   const long long nb = lz_blocks(raw_bytes);
-  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long i = (long long)blockIdx.x * kLzWarps + warp;
   if (i >= slices * nb) return;
   const long long s = i / nb, b = i - s * nb;
   const uint8_t* base = payload + s * payload_stride;
   const uint32_t* hdr = reinterpret_cast<const uint32_t*>(base);
-  lz_decode_one(base + lz_header_bytes(nb) + hdr[1 + b], raw + s * raw_bytes, raw_bytes, b, sym);
+  const long long off = b * kLzBlockBytes;
+  const int bytes = (int)(raw_bytes - off < kLzBlockBytes ? raw_bytes - off : kLzBlockBytes);
+  const int code_bytes = (int)(hdr[2 + b] - hdr[1 + b]);
+  if (code_bytes < 2 || code_bytes > kLzSlotBytes) return;       // corrupt header: leave the block untouched
+  lz_decode_block_warp<Sym>(base + lz_header_bytes(nb) + hdr[1 + b], code_bytes,
+                            reinterpret_cast<Sym*>(raw + s * raw_bytes + off), bytes / (int)sizeof(Sym), sm, lane);
 }
 
 }  // namespace
@@ -253,7 +450,18 @@ void launch_lz_encode(const uint8_t* raw, uint8_t* payload, int* sizes, uint8_t*
   if (total <= 0) return;
   uint8_t* slots = scratch;
   int* blk_sizes = reinterpret_cast<int*>(scratch + (total * kLzSlotBytes + 15) / 16 * 16);
-  lz_encode_blocks_kernel<<<(unsigned)((total + 63) / 64), 64, 0, stream>>>(raw, slots, blk_sizes, slices, raw_bytes, sym);
+  const unsigned ctas = (unsigned)((total + kLzWarps - 1) / kLzWarps);
+  if (sym == 2) {
+    constexpr int smem = kLzWarps * (int)sizeof(LzEncSmem<uint16_t>);
+    static bool once = false;
+    if (!once) { cudaFuncSetAttribute(lz_encode_blocks_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); once = true; }
+    lz_encode_blocks_kernel<uint16_t><<<ctas, kLzWarps * 32, smem, stream>>>(raw, slots, blk_sizes, slices, raw_bytes);
+  } else {
+    constexpr int smem = kLzWarps * (int)sizeof(LzEncSmem<uint32_t>);
+    static bool once = false;
+    if (!once) { cudaFuncSetAttribute(lz_encode_blocks_kernel<uint32_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); once = true; }
+    lz_encode_blocks_kernel<uint32_t><<<ctas, kLzWarps * 32, smem, stream>>>(raw, slots, blk_sizes, slices, raw_bytes);
+  }
   lz_scan_kernel<<<(unsigned)slices, 256, 0, stream>>>(blk_sizes, payload, sizes, raw_bytes, payload_stride);
   dim3 grid((unsigned)((nb + 3) / 4), (unsigned)slices);
   lz_compact_kernel<<<grid, 128, 0, stream>>>(slots, blk_sizes, payload, raw_bytes, payload_stride);
@@ -262,7 +470,18 @@ void launch_lz_decode(const uint8_t* payload, uint8_t* raw, long long slices, lo
                       long long payload_stride, int sym, cudaStream_t stream) {
   const long long total = slices * lz_blocks(raw_bytes);
   if (total <= 0) return;
-  lz_decode_blocks_kernel<<<(unsigned)((total + 63) / 64), 64, 0, stream>>>(payload, raw, slices, raw_bytes, payload_stride, sym);
+  const unsigned ctas = (unsigned)((total + kLzWarps - 1) / kLzWarps);
+  if (sym == 2) {
+    constexpr int smem = kLzWarps * (int)sizeof(LzDecSmem<uint16_t>);
+    static bool once = false;
+    if (!once) { cudaFuncSetAttribute(lz_decode_blocks_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); once = true; }
+    lz_decode_blocks_kernel<uint16_t><<<ctas, kLzWarps * 32, smem, stream>>>(payload, raw, slices, raw_bytes, payload_stride);
+  } else {
+    constexpr int smem = kLzWarps * (int)sizeof(LzDecSmem<uint32_t>);
+    static bool once = false;
+    if (!once) { cudaFuncSetAttribute(lz_decode_blocks_kernel<uint32_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); once = true; }
+    lz_decode_blocks_kernel<uint32_t><<<ctas, kLzWarps * 32, smem, stream>>>(payload, raw, slices, raw_bytes, payload_stride);
+  }
 }
 
 }  // namespace planmoe

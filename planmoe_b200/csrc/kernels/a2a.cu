@@ -1,8 +1,9 @@
 // Generic "wait, copy to peers, signal" kernel: the building block of every stand-alone
 // all-to-all algorithm (flat, Pipe-A2A, HeTu-hierarchical, 2DH) of the symmetric-heap transport.
 //
-// One launch executes a table of messages.  CTA (i, m) first acquire-waits (bounded) on the listed
-// local flags, then copies slice i of message m with 16-byte loads/stores from local memory to
+// One launch executes a table of messages.  CTA (i, m) first acquire-waits (bounded) on the local flags
+// message m depends on, then moves slice i of message m through the bulk-copy engine (cp.async.bulk
+// global -> shared -> global, four 16 KiB units in flight, no thread touches the data) from local memory to
 //   heap_bases[dest] + dst_off     (a peer's or this rank's heap), or
 //   local_dst + dst_off            (dest < 0: plain local output tensor),
 // and finally, if the message carries a flag index, issues a system-scope fence and a release-add
@@ -17,45 +18,77 @@
 
 namespace planmoe {
 
-__global__ void __launch_bounds__(256)
+constexpr int kXferSlots = 4;                  // bulk-copy slots per CTA, one per lane of the single warp
+constexpr unsigned kXferSlotBytes = 16384;
+
+// msgs: int64 [n_msgs][6] = (dest rank or -1, flag index to signal or -1, src_off, dst_off, bytes,
+// index into wait_flags this message alone depends on, or -1: every listed flag).
+__global__ void __launch_bounds__(32)
 xfer_kernel(const unsigned char* __restrict__ src_base, const long long* __restrict__ msgs, int n_msgs,
             const unsigned long long* __restrict__ heap_bases, unsigned long long flag_off,
             const unsigned long long* __restrict__ wait_flags, const int* __restrict__ wait_idx, int n_wait,
             unsigned long long want, unsigned long long budget_ns, int* status, unsigned char* local_dst) {
-  __shared__ int ok_s;
-  if (n_wait > 0) {
-    if (threadIdx.x == 0) ok_s = 1;
-    __syncthreads();
-    for (int f = threadIdx.x; f < n_wait; f += blockDim.x) {
-      if (!wait_flag_ge(wait_flags + wait_idx[f], want, budget_ns, status, wait_idx[f])) ok_s = 0;
-    }
-    __syncthreads();
-    if (!ok_s) return;
-  }
+  extern __shared__ __align__(128) unsigned char xs[];
+  __shared__ unsigned long long bars[kXferSlots];
+  const int lane = threadIdx.x;
   const int m = blockIdx.y;
   if (m >= n_msgs) return;
-  const long long dest = msgs[m * 5 + 0];
-  const long long flag_idx = msgs[m * 5 + 1];
-  const unsigned long long src_off = (unsigned long long)msgs[m * 5 + 2];
-  const unsigned long long dst_off = (unsigned long long)msgs[m * 5 + 3];
-  const unsigned long long bytes = (unsigned long long)msgs[m * 5 + 4];
+  const long long dest = msgs[m * 6 + 0];
+  const long long flag_idx = msgs[m * 6 + 1];
+  const unsigned long long src_off = (unsigned long long)msgs[m * 6 + 2];
+  const unsigned long long dst_off = (unsigned long long)msgs[m * 6 + 3];
+  const unsigned long long bytes = (unsigned long long)msgs[m * 6 + 4];
+  const long long wait_one = msgs[m * 6 + 5];
 
-  const uint4* src = reinterpret_cast<const uint4*>(src_base + src_off);
-  unsigned char* dbase = dest >= 0 ? reinterpret_cast<unsigned char*>(heap_bases[dest]) : local_dst;
-  uint4* dst = reinterpret_cast<uint4*>(dbase + dst_off);
-  const unsigned long long nvec = bytes >> 4;
-  const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
-  unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
-  // 4 independent 16-byte transfers in flight per thread
-  for (; i + 3 * stride < nvec; i += 4 * stride) {
-    const uint4 a = src[i], b = src[i + stride], c = src[i + 2 * stride], d = src[i + 3 * stride];
-    dst[i] = a; dst[i + stride] = b; dst[i + 2 * stride] = c; dst[i + 3 * stride] = d;
+  // ---- what this message reads must have arrived (bounded) --------------------------------------
+  bool ok = true;
+  if (n_wait > 0) {
+    if (wait_one >= 0) {
+      if (lane == 0) ok = wait_flag_ge(wait_flags + wait_one, want, budget_ns, status, (int)wait_one);
+    } else {
+      for (int f = lane; f < n_wait; f += 32)
+        if (!wait_flag_ge(wait_flags + wait_idx[f], want, budget_ns, status, wait_idx[f])) ok = false;
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) return;
+    fence_proxy_async();                           // what peers wrote -> this CTA's bulk loads
   }
-  for (; i < nvec; i += stride) dst[i] = src[i];
+  if (lane < kXferSlots) mbar_init(smem_u32(&bars[lane]), 1);
+  fence_barrier_init();
+  __syncwarp();
 
-  if (flag_idx >= 0 && dest >= 0) {
-    __syncthreads();
-    if (threadIdx.x == 0) {
+  // ---- my slice of the message, in 16 KiB units, through the bulk-copy engine --------------------
+  // Lane l owns slot l: load a unit into it, wait for the bytes, store it to the destination, and reuse
+  // the slot once the store has read it.  Four units are in flight per CTA and no thread touches data.
+  const unsigned long long units = (bytes + kXferSlotBytes - 1) / kXferSlotBytes;
+  const unsigned long long per = (units + gridDim.x - 1) / gridDim.x;
+  const unsigned long long u0 = (unsigned long long)blockIdx.x * per;
+  const unsigned long long u1 = u0 + per < units ? u0 + per : units;
+  const unsigned char* src = src_base + src_off;
+  unsigned char* dst = (dest >= 0 ? reinterpret_cast<unsigned char*>(heap_bases[dest]) : local_dst) + dst_off;
+  if (lane < kXferSlots) {
+    const unsigned slot_s = smem_u32(xs + lane * kXferSlotBytes);
+    const unsigned bar = smem_u32(&bars[lane]);
+    unsigned phase = 0;
+    for (unsigned long long u = u0 + lane; u < u1 && ok; u += kXferSlots) {
+      const unsigned long long off = u * kXferSlotBytes;
+      const unsigned n = (unsigned)(bytes - off < kXferSlotBytes ? bytes - off : kXferSlotBytes);
+      bulk_wait_read_all();
+      mbar_expect_tx(bar, n);
+      bulk_load(slot_s, src + off, n, bar);
+      ok = mbar_wait_bounded(bar, phase, budget_ns, status, 4, lane);
+      phase ^= 1u;
+      if (ok) {
+        bulk_store(dst + off, slot_s, n);
+        bulk_commit();
+      }
+    }
+    bulk_wait_all();                               // my stores have been performed
+  }
+  ok = __all_sync(0xffffffffu, ok);
+
+  if (ok && flag_idx >= 0 && dest >= 0) {
+    if (lane == 0) {
       __threadfence_system();
       unsigned long long* flags = reinterpret_cast<unsigned long long*>(
           reinterpret_cast<unsigned char*>(heap_bases[dest]) + flag_off);
@@ -70,10 +103,16 @@ void launch_xfer(const void* src_base, const long long* msgs, int n_msgs, int ct
                  unsigned long long budget_ns, int* status, void* local_dst, cudaStream_t stream) {
   if (n_msgs <= 0) return;
   if (ctas_per_msg < 1) ctas_per_msg = 1;
+  constexpr int smem = kXferSlots * kXferSlotBytes;
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(xfer_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    configured = true;
+  }
   dim3 grid(ctas_per_msg, n_msgs);
-  xfer_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const unsigned char*>(src_base), msgs, n_msgs, heap_bases,
-                                      flag_off, wait_flags, wait_idx, n_wait, want, budget_ns, status,
-                                      reinterpret_cast<unsigned char*>(local_dst));
+  xfer_kernel<<<grid, 32, smem, stream>>>(reinterpret_cast<const unsigned char*>(src_base), msgs, n_msgs, heap_bases,
+                                        flag_off, wait_flags, wait_idx, n_wait, want, budget_ns, status,
+                                        reinterpret_cast<unsigned char*>(local_dst));
 }
 
 // A kernel that only waits (used by tests of the bounded-wait path and by host code that needs a

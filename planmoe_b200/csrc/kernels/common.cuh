@@ -1,5 +1,5 @@
-// Device-side helpers shared by the SIMT kernels: 16-byte vector access, dtype conversion,
-// warp reductions, system-scope flag access with bounded waits.
+// Device-side helpers shared by the kernels: 16-byte vector access, dtype conversion, warp
+// reductions, system-scope flag access with bounded waits, mbarrier and bulk-copy wrappers.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -109,6 +109,66 @@ __device__ __forceinline__ bool wait_flag_ge(const unsigned long long* flag, uns
     __nanosleep(ns);
     if (ns < 1024) ns <<= 1;
   }
+}
+
+// ---- shared-memory barriers and the bulk-copy engine (cp.async.bulk, no tensor map) ----
+// Bulk copies move 16-byte-aligned byte ranges between global and shared memory without occupying
+// threads: a load completes on an mbarrier (complete_tx), stores are tracked in per-thread bulk groups.
+// None of these uses cluster multicast.
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ void fence_barrier_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async;" ::: "memory");
+}
+
+__device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* dst, uint32_t src_smem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src_smem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+
+// Bounded wait on an mbarrier phase: false once budget_ns have passed (the status word records it).
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, unsigned long long budget_ns,
+                                                  int* status, int role, int detail) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 63u) == 0u && global_timer_ns() - t0 > budget_ns) {
+      report_status(status, kStatusMbarTimeout, role, detail, (int)parity);
+      return false;
+    }
+  }
+  return true;
 }
 
 }  // namespace planmoe

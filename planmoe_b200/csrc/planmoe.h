@@ -78,7 +78,8 @@ void launch_int8_decode(const unsigned char* q, const float* scale, const float*
                         int M, cudaStream_t stream);
 
 // ---- kernels/a2a.cu --------------------------------------------------------------------------
-// msgs: device int64 [n_msgs][5] = (dest rank or -1, flag index or -1, src_off, dst_off, bytes).
+// msgs: device int64 [n_msgs][6] = (dest rank or -1, flag index to signal or -1, src_off, dst_off, bytes,
+// position in wait_flags this message alone waits for, or -1 = all of wait_idx).
 void launch_xfer(const void* src_base, const long long* msgs, int n_msgs, int ctas_per_msg,
                  const unsigned long long* heap_bases, unsigned long long flag_off,
                  const unsigned long long* wait_flags, const int* wait_idx, int n_wait, unsigned long long want,

@@ -49,21 +49,24 @@ class A2AChannel:
         self.L = _local_size(self.W)
         self.calls = 0
         self.bufs = {}          # (algo, parity) -> dict(name -> HeapBlock), sized for `cap` bytes per pair
-        self.flags = {}         # algo -> HeapBlock: [parity 2][phase 4][W] u64
         self.arrived = {}       # (algo, parity, phase) -> cumulative arrivals expected per flag
         self.tables = {}
         self.side = None
 
     # -- resources ----------------------------------------------------------------------------
     def _ensure(self, algo, parity, n):
-        # Flags are cumulative counters, and which flags a call advances depends on the algorithm (in the
-        # hierarchical ones only group leaders receive some phases), so every algorithm owns its flags.
-        if algo not in self.flags:
-            self.flags[algo] = self.tr.alloc(2 * self.N_PHASES * self.W * 8)
+        """Staging buffers and flags of one (algorithm, call parity), sized for ``n`` bytes per pair.
+
+        Buffers and their flags are carved out of ONE heap block: a kernel addresses both through the
+        same table of peer base addresses, and a block never spans heap segments.  Flags are cumulative
+        counters, and which flags a call advances depends on the algorithm (in the hierarchical ones
+        only group leaders receive some phases), so every (algorithm, parity) owns its flags; a larger
+        reallocation starts from fresh (zeroed) flags and zeroed counters."""
         key = (algo, parity)
         cur = self.bufs.get(key)
         if cur is not None and cur['cap'] >= n:
             return cur
+        from .transport import HeapBlock
         W, L = self.W, self.L
         cap = max(n, 1 << 20)
         if algo == 'hetu':
@@ -72,21 +75,29 @@ class A2AChannel:
             sizes = dict(a=W * cap, b=W * cap)
         else:
             sizes = dict(a=W * cap)
-        cur = {k: self.tr.alloc(v) for k, v in sizes.items()}
+        sizes['flags'] = self.N_PHASES * W * 8
+        total = sum((v + 1023) // 1024 * 1024 for v in sizes.values())
+        blk = self.tr.alloc(total)
+        cur, off = {}, blk.offset
+        for k, v in sizes.items():
+            cur[k] = HeapBlock(self.tr, blk.segment, off, v)
+            off += (v + 1023) // 1024 * 1024
         cur['cap'] = cap
         self.bufs[key] = cur
         self.tables = {k: v for k, v in self.tables.items() if k[:2] != key}
+        self.arrived = {k: v for k, v in self.arrived.items() if k[:2] != key}
         return cur
 
     def _flag_off(self, algo, parity, phase):
-        return self.flags[algo].offset + ((parity * self.N_PHASES + phase) * self.W) * 8
+        return self.bufs[(algo, parity)]['flags'].offset + phase * self.W * 8
 
     def _flag_ptr(self, algo, parity, phase):
-        return self.flags[algo].local_ptr + ((parity * self.N_PHASES + phase) * self.W) * 8
+        return self.bufs[(algo, parity)]['flags'].local_ptr + phase * self.W * 8
 
     # -- message tables ---------------------------------------------------------------------------
     def _plan(self, algo, parity, n, bufs):
-        """List of phases; a message is (dest, flag_idx, src_off, dst_off, bytes).  ``src`` names the
+        """List of phases; a message is (dest, flag_idx, src_off, dst_off, bytes, wait_one): ``wait_one`` is the
+        one flag of the waited phase this message's source bytes depend on (-1: all listed).  ``src`` names the
         buffer the offsets are relative to: 'in' (the caller's tensor) or a staging block."""
         W, L, me = self.W, self.L, self.me
         N = W // L
@@ -95,7 +106,7 @@ class A2AChannel:
         phases = []
         if algo in ('flat', 'pipe'):
             def push(peers, stream):
-                return _Phase([(d, me, d * n, a.offset + me * n, n) for d in peers], None, 'in', None, stream, 0)
+                return _Phase([(d, me, d * n, a.offset + me * n, n, -1) for d in peers], None, 'in', None, stream, 0)
             if algo == 'flat' or L == W or L == 1:
                 phases.append(push(range(W), 0))
             else:
@@ -103,34 +114,37 @@ class A2AChannel:
                 inter = [d for d in range(W) if d // L != mn]
                 phases.append(push(intra, 1))
                 phases.append(push(inter, 2))
-            phases.append(_Phase([(-1, -1, s * n, s * n, n) for s in range(W)], list(range(W)), 'a', 0))
+            # copy-out: the slice from source s only needs flag s, so it starts while others are in flight
+            phases.append(_Phase([(-1, -1, s * n, s * n, n, s) for s in range(W)], list(range(W)), 'a', 0))
             arrivals = {0: 1}
         elif algo == 'dd':
             b = bufs['b']
             # phase 0: to local peer l' everything I send to local index l' of any group -> a[sl][dn]
-            phases.append(_Phase([(mn * L + lp, ml, (dn * L + lp) * n, a.offset + (ml * N + dn) * n, n)
+            phases.append(_Phase([(mn * L + lp, ml, (dn * L + lp) * n, a.offset + (ml * N + dn) * n, n, -1)
                                   for lp in range(L) for dn in range(N)], None, 'in', logical=0))
-            # phase 1: a[sl][dn] -> rank (dn, ml), b[sn = mn][sl]
-            phases.append(_Phase([(dn * L + ml, mn, (sl * N + dn) * n, b.offset + (mn * L + sl) * n, n)
+            # phase 1: a[sl][dn] (filled by local peer sl: flag sl) -> rank (dn, ml), b[sn = mn][sl]
+            phases.append(_Phase([(dn * L + ml, mn, (sl * N + dn) * n, b.offset + (mn * L + sl) * n, n, sl)
                                   for dn in range(N) for sl in range(L)], list(range(L)), 'a', 0, logical=1))
-            phases.append(_Phase([(-1, -1, s * n, s * n, n) for s in range(W)], list(range(N)), 'b', 1))
+            # copy-out of b[sn][sl], filled by rank (sn, ml): flag sn
+            phases.append(_Phase([(-1, -1, s * n, s * n, n, s // L) for s in range(W)], list(range(N)), 'b', 1))
             arrivals = {0: N, 1: L}
         elif algo == 'hetu':
             b, c = bufs['b'], bufs['c']
             leader = mn * L
             # phase 0: whole buffer to my leader: a[sl][d]
-            phases.append(_Phase([(leader, ml, d * n, a.offset + (ml * W + d) * n, n) for d in range(W)], None, 'in', logical=0))
+            phases.append(_Phase([(leader, ml, d * n, a.offset + (ml * W + d) * n, n, -1) for d in range(W)], None, 'in',
+                                 logical=0))
             if ml == 0:
                 # phase 1 (leaders): a[sl][dn][dl] -> leader of dn, b[sn = mn][dl][sl]
                 phases.append(_Phase([(dn * L, mn, (sl * W + dn * L + dl) * n,
-                                       b.offset + ((mn * L + dl) * L + sl) * n, n)
+                                       b.offset + ((mn * L + dl) * L + sl) * n, n, sl)
                                       for dn in range(N) for dl in range(L) for sl in range(L)],
                                      list(range(L)), 'a', 0, logical=1))
                 # phase 2 (leaders): b[sn][dl][sl] -> local rank dl, c[sn][sl]
-                phases.append(_Phase([(leader + dl, 0, ((sn * L + dl) * L + sl) * n, c.offset + (sn * L + sl) * n, n)
+                phases.append(_Phase([(leader + dl, 0, ((sn * L + dl) * L + sl) * n, c.offset + (sn * L + sl) * n, n, sn)
                                       for dl in range(L) for sn in range(N) for sl in range(L)],
                                      list(range(N)), 'b', 1, logical=2))
-            phases.append(_Phase([(-1, -1, s * n, s * n, n) for s in range(W)], [0], 'c', 2))
+            phases.append(_Phase([(-1, -1, s * n, s * n, n, 0) for s in range(W)], [0], 'c', 2))
             arrivals = {0: W, 1: L * L, 2: N * L}
         else:
             raise ValueError('unknown all-to-all algorithm: %s' % algo)
@@ -143,7 +157,7 @@ class A2AChannel:
             dev = self.tr.device
             built = []
             for ph in phases:
-                msgs = torch.tensor(ph.msgs, dtype=torch.int64, device=dev).view(-1, 5)
+                msgs = torch.tensor(ph.msgs, dtype=torch.int64, device=dev).view(-1, 6)
                 wait = torch.tensor(ph.wait_idx, dtype=torch.int32, device=dev) if ph.wait_idx else None
                 built.append((ph, msgs, wait))
             self.tables[key] = (built, arrivals)
