@@ -2,20 +2,26 @@
 //
 //   D[g] (M x N) = A[g] (M x K) . B[g] (K x N)          g = 0 .. groups-1, fp32 accumulate
 //
-// Hand-written tcgen05 pipeline, one persistent CTA per SM, 352 threads in four roles:
-//   warp 0      TMA producer: cp.async.bulk.tensor (4-D maps, 128-byte swizzle) into a 4-stage
-//               shared-memory ring, completion on mbarriers.  When the A operand is a receive
-//               buffer that peer GPUs fill, the producer first acquire-waits (bounded) on the
-//               flag of every source rank whose rows the tile touches: the GEMM starts on a
-//               tile as soon as its rows have landed ("flag-gated A").
-//   warp 1      MMA issuer: one thread issues tcgen05.mma.cta_group::1.kind::f16, 128 x 256 x 16
-//               per instruction, accumulating in TMEM (2 x 256 columns, double buffered so the
+// Hand-written tcgen05 pipeline, one persistent CTA per SM, 352 threads in four roles.  By default two
+// CTAs form a cluster and compute one 256 x 256 tile with tcgen05.mma.cta_group::2 (each CTA stages
+// its own 128 rows of A and 128 of the 256 B columns; the even CTA issues the MMAs for both);
+// problems with at most 128 rows per group run the one-CTA variant (128 x 256 tiles).
+//   warp 0      TMA producer: cp.async.bulk.tensor (4-D maps, 128-byte swizzle) into a 5-stage
+//               shared-memory ring (3-stage in the one-CTA variant), completion on the mbarrier of
+//               the MMA-issuing CTA.  When the A operand is a receive buffer that peer GPUs fill,
+//               the producer first acquire-waits (bounded) on the flag of every source rank whose
+//               rows the tile touches: the GEMM starts on a tile as soon as its rows have landed
+//               ("flag-gated A").
+//   warp 1      MMA issuer: one thread issues tcgen05.mma.kind::f16, (128 or 256) x 256 x 16 per
+//               instruction, accumulating in TMEM (2 x 256 columns, double buffered so the
 //               epilogue of tile i overlaps the main loop of tile i+1); tcgen05.commit releases
-//               ring stages and publishes the accumulator.
+//               ring stages and publishes the accumulator in every CTA of the group.
 //   warps 2..9  epilogue: tcgen05.ld 32x32b -> registers -> bias / activation (saving its
-//               derivative) / multiply by a saved derivative -> bf16 -> swizzled shared-memory staging -> full-line 16-byte stores,
-//               either to local memory or straight into the combine buffer of the rank that
-//               owns the token ("push"), followed by a release-add on that rank's flag.
+//               derivative) / multiply by a saved derivative -> bf16 -> swizzled shared-memory
+//               staging -> full-line 16-byte stores, either to local memory or straight into the
+//               combine buffer of the rank that owns the token ("push"), followed by a release-add
+//               on that rank's flag.  The TMEM load of the second half of a warp's columns is
+//               issued under the stores of the first half.
 //   warp 10     dispatch send (optional): while the tensor cores work, this warp of every CTA moves
 //               token rows into the receive buffers of the ranks that own the experts with the
 //               bulk-copy engine: cp.async.bulk global -> shared (row picked by slot map), an
@@ -32,9 +38,10 @@
 // wgrad — run on this one kernel without transposed copies.  A split-K "chunk" dimension lets a
 // weight-gradient GEMM contract over all pipeline chunks of a receive buffer in one launch.
 //
-// TMA loads here never use cluster multicast, and peer memory is only ever written with plain
-// stores and read with plain flag loads.  Every wait (mbarrier or flag) is bounded: on expiry the
-// CTA records a code in the status word, drains, frees its TMEM and returns.
+// TMA loads here never use cluster multicast and never read another GPU's memory: peer memory is
+// only written (epilogue stores, bulk stores of the dispatch send) and signalled (flag adds); what
+// a GPU computes on has landed in its own memory first.  Every wait (mbarrier or flag) is bounded:
+// on expiry the CTA records a code in the status word, drains, frees its TMEM and returns.
 //
 // Takes the place of the reference's torch.matmul -> cuBLAS calls and separate bias / activation
 // kernels (PlanMoE/experts/ffn.py:76-78) and of the permute copies around them

@@ -3,10 +3,12 @@
 Forward, per pipeline chunk j of the capacity dimension (``degree`` chunks):
 
     fused gate kernel      softmax + top-k + slot scan + slot map + GShard loss
-    dispatch  (scatter)    slot-major gather of token rows, stored straight into the receive
-                           buffer of the rank that owns the expert, + release-add on its flag
-    expert GEMM 1          tcgen05; A tiles are read from the receive buffer as soon as the flags
-                           of the source ranks they touch have arrived; bias + activation epilogue
+    dispatch + GEMM 1      ONE launch.  A copy warp in every CTA moves token rows (picked by slot
+                           map) with the bulk-copy engine straight into the receive buffer of the
+                           rank that owns the expert and release-adds its flag; the tcgen05 GEMM of
+                           the same launch reads A tiles from its own receive buffer as soon as the
+                           flags of the source ranks they touch have arrived; bias + activation
+                           epilogue.  (With one rank a separate slot-major copy kernel runs first.)
     expert GEMM 2          tcgen05; the epilogue stores rows straight into the combine buffer of
                            the rank that owns the token, + release-add on its flag
     combine   (gather)     waits for the flags, gate-weighted sum over the k picks
