@@ -41,6 +41,7 @@ def parse():
     ap.add_argument('--comm', default='naive')
     ap.add_argument('--compress', default='no')
     ap.add_argument('--stages', action='store_true', help='also print per-stage device times (stderr)')
+    ap.add_argument('--no-graph', action='store_true', help='time the eager loop instead of CUDA-graph replays')
     return ap.parse_args()
 
 
@@ -313,25 +314,66 @@ def main():
         from planmoe_b200.parallel import transport
         transport.get_transport(None).check()
 
+    # ---- CUDA-graph capture of the step (two steps per graph: the layer alternates buffer sets) ------
+    graphed, x_static, launches_per_step = None, None, 0
+    if args.impl == 'ours' and not args.no_graph:
+        try:
+            from planmoe_b200.utils.graphs import GraphedSteps
+            layer.l_aux = None                  # last reference to the autograd graph of the eager warm-up steps
+            x_static = [x_dev.clone(), x_dev.clone()]
+            turn = [0]
+
+            def graph_step():
+                loss = step(x_static[turn[0] & 1])
+                turn[0] += 1
+                return loss.detach().float().reshape(1)
+            lc0 = launch_count()
+            graphed = GraphedSteps(graph_step, unroll=2, warmup=2)
+            launches_per_step = (launch_count() - lc0) // (2 * 2 + 2)      # warm-up steps + the captured pair
+            graphed.replay()
+            barrier()
+        except Exception as exc:                                            # capture not possible: eager loop
+            print('bench.py: CUDA-graph capture failed (%s); timing the eager loop' % (exc,), file=sys.stderr)
+            graphed = None
+            torch.cuda.synchronize()
+
     # ---- device-timed region -------------------------------------------------------------
     sampler = ClockSampler(local_rank, getattr(torch.cuda.get_device_properties(device), 'uuid', None))
     if rank == 0:
         sampler.start()
-    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-    ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     l0 = launch_count()
     barrier()
     host_t0 = time.perf_counter()
-    for i in range(args.steps):
-        flush.fill_(i & 0xff)
-        starts[i].record()
-        step(x_dev)
-        ends[i].record()
-    host_ms = (time.perf_counter() - host_t0) * 1e3 / args.steps      # host time to enqueue one step
-    barrier()
-    launches = launch_count() - l0
+    if graphed is not None:
+        # K steps = K // 2 replays of the two-step graph (+ one eager step if K is odd), one event bracket
+        # around all of them.  The working set of a step (about 0.6 GB of activations, receive buffers and
+        # weights) is several times the 126 MB L2, so no step finds its inputs cached.
+        t_s, t_e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t_s.record()
+        for _ in range(args.steps // 2):
+            graphed.replay()
+        if args.steps & 1:
+            step(x_dev)
+        t_e.record()
+        host_ms = (time.perf_counter() - host_t0) * 1e3 / args.steps
+        barrier()
+        launches = launches_per_step * args.steps
+        ms = t_s.elapsed_time(t_e)
+        l2_note = 'working set per step (~0.6 GB) exceeds L2; K steps timed as one bracket of CUDA-graph replays'
+    else:
+        starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+        ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+        for i in range(args.steps):
+            flush.fill_(i & 0xff)
+            starts[i].record()
+            step(x_dev)
+            ends[i].record()
+        host_ms = (time.perf_counter() - host_t0) * 1e3 / args.steps      # host time to enqueue one step
+        barrier()
+        launches = launch_count() - l0
+        ms = sum(s.elapsed_time(e) for s, e in zip(starts, ends))
+        l2_note = 'flushed between timed steps (256 MiB write outside the event brackets)'
     clocks = sampler.stop() if rank == 0 else None
-    ms = sum(s.elapsed_time(e) for s, e in zip(starts, ends))
 
     # ---- end-to-end region: pinned H2D of the input + D2H of the loss, every step ---------------
     # The way a training loop feeds a GPU: the input of step i + 1 is copied from pinned host memory on a
@@ -358,29 +400,82 @@ def main():
     e2e_e = torch.cuda.Event(enable_timing=True)
     for b in range(2):
         x_free[b].record(cur)
-    barrier()
-    e2e_s.record()
-    prefetch(0)
-    for i in range(args.steps):
-        b = i & 1
-        if i + 1 < args.steps:
-            prefetch(i + 1)
-        cur.wait_event(x_ready[b])
-        loss = step(x_bufs[b])
-        x_free[b].record(cur)
-        loss_host[b].copy_(loss.detach().float().reshape(1), non_blocking=True)
-        loss_done[b].record(cur)
-        if i > 0:                                      # read the previous step's loss while this one runs
-            loss_done[b ^ 1].synchronize()
-            _ = float(loss_host[b ^ 1][0])
+    if graphed is not None:
+        # Graph mode: a replay runs two steps on two static inputs.  The inputs of the next replay are copied
+        # host -> device into staging buffers on the copy stream while this replay computes, moved into the
+        # static inputs by two device copies right before the replay, and the two losses of a replay are copied
+        # to pinned host memory behind it and read one replay later.
+        pair_ready, pair_free = torch.cuda.Event(), torch.cuda.Event()
+        loss_pair = [torch.zeros(2, dtype=torch.float32).pin_memory() for _ in range(2)]
+        pair_done = [torch.cuda.Event() for _ in range(2)]
+
+        def prefetch_pair():
+            with torch.cuda.stream(copy_stream):
+                copy_stream.wait_event(pair_free)
+                x_bufs[0].copy_(host_x, non_blocking=True)
+                x_bufs[1].copy_(host_x, non_blocking=True)
+                pair_ready.record(copy_stream)
+
+        n_rep = args.steps // 2
+        pair_free.record(cur)
+        barrier()
+        e2e_s.record()
+        if n_rep:
+            prefetch_pair()
+        for r in range(n_rep):
+            cur.wait_event(pair_ready)
+            x_static[0].copy_(x_bufs[0], non_blocking=True)
+            x_static[1].copy_(x_bufs[1], non_blocking=True)
+            pair_free.record(cur)
+            if r + 1 < n_rep:
+                prefetch_pair()
+            outs = graphed.replay()
+            loss_pair[r & 1][0:1].copy_(outs[0], non_blocking=True)
+            loss_pair[r & 1][1:2].copy_(outs[1], non_blocking=True)
+            pair_done[r & 1].record(cur)
+            if r > 0:
+                pair_done[(r - 1) & 1].synchronize()
+                _ = float(loss_pair[(r - 1) & 1][0]) + float(loss_pair[(r - 1) & 1][1])
+                losses_read += 2
+        if n_rep:
+            pair_done[(n_rep - 1) & 1].synchronize()
+            _ = float(loss_pair[(n_rep - 1) & 1][0]) + float(loss_pair[(n_rep - 1) & 1][1])
+            losses_read += 2
+        if args.steps & 1:                             # odd K: one more step, eagerly
+            x_in = host_x.to(device, non_blocking=True)
+            loss = step(x_in)
+            host_loss.copy_(loss.detach().float().reshape(1), non_blocking=True)
+            cur.synchronize()
+            _ = float(host_loss[0])
             losses_read += 1
-    loss_done[(args.steps - 1) & 1].synchronize()
-    _ = float(loss_host[(args.steps - 1) & 1][0])
-    losses_read += 1
-    e2e_e.record()
-    barrier()
-    assert losses_read == args.steps
-    e2e_ms = e2e_s.elapsed_time(e2e_e)
+        e2e_e.record()
+        barrier()
+        assert losses_read == args.steps
+        e2e_ms = e2e_s.elapsed_time(e2e_e)
+    else:
+      barrier()
+      e2e_s.record()
+      prefetch(0)
+      for i in range(args.steps):
+          b = i & 1
+          if i + 1 < args.steps:
+              prefetch(i + 1)
+          cur.wait_event(x_ready[b])
+          loss = step(x_bufs[b])
+          x_free[b].record(cur)
+          loss_host[b].copy_(loss.detach().float().reshape(1), non_blocking=True)
+          loss_done[b].record(cur)
+          if i > 0:                                      # read the previous step's loss while this one runs
+              loss_done[b ^ 1].synchronize()
+              _ = float(loss_host[b ^ 1][0])
+              losses_read += 1
+      loss_done[(args.steps - 1) & 1].synchronize()
+      _ = float(loss_host[(args.steps - 1) & 1][0])
+      losses_read += 1
+      e2e_e.record()
+      barrier()
+      assert losses_read == args.steps
+      e2e_ms = e2e_s.elapsed_time(e2e_e)
 
     if args.impl == 'ours':
         from planmoe_b200.parallel import transport
@@ -406,7 +501,7 @@ def main():
                 'model': 'pre_test MoE layer: model_dim 2048, hidden 2048, 2 local experts/GPU, top-2, cf 1.0, GELU',
                 'global_batch': CFG['batch'] * world, 'seq_len': CFG['tokens'],
                 'parallelism': 'ep%d' % world, 'step': 'forward + backward + SGD update',
-                'l2': 'flushed between timed steps (256 MiB write outside the event brackets)',
+                'l2': l2_note, 'cuda_graph': graphed is not None,
                 'degree': chosen, 'comm': args.comm, 'compress': args.compress,
             },
             'clocks': clocks,

@@ -270,11 +270,12 @@ struct GemmOpts {
   int64_t epilogue = 0, activation = 0;
   c10::optional<Tensor> bias, aux, out;
   // flag gate
-  int64_t gate_flags_ptr = 0, gate_rows = 0, gate_want = 0;
+  int64_t gate_flags_ptr = 0, gate_rows = 0, gate_want = 0, gate_want_ptr = 0;
   // push
   int64_t heap_bases_ptr = 0, push_data_off = 0, push_flag_off = 0, push_rows = 0, push_C = 0, push_c0 = 0,
           push_chunk = 0, W = 1, my_rank = 0, chunk_groups = 0;
   int64_t budget_ms = 0, status_ptr = 0, max_ctas = 0, cta_group = 0;
+  std::vector<int64_t> heap_bases_host;      // peers' mapped base addresses (push epilogue with bulk stores)
   // dispatch send fused into the launch (copy role)
   c10::optional<Tensor> copy_x, copy_slot_map, copy_gates;
   int64_t copy_K = 0, copy_E_local = 0, copy_C = 0, copy_chunks = 0, copy_ctas = 0, copy_data_off = 0,
@@ -339,10 +340,13 @@ Tensor grouped_gemm_op(const Tensor& A, bool a_mn, const Tensor& B, bool b_mn, c
   }
   g.gate_flags = reinterpret_cast<const unsigned long long*>(o.gate_flags_ptr);
   g.gate_rows = o.gate_rows; g.gate_want = o.gate_want;
+  g.gate_want_ptr = reinterpret_cast<const unsigned long long*>(o.gate_want_ptr);
   g.heap_bases = reinterpret_cast<const unsigned long long*>(o.heap_bases_ptr);
   g.push_data_off = o.push_data_off; g.push_flag_off = o.push_flag_off; g.push_rows = o.push_rows;
   g.push_C = o.push_C; g.push_c0 = o.push_c0; g.push_chunk = o.push_chunk; g.W = o.W; g.my_rank = o.my_rank;
   g.chunk_groups = o.chunk_groups;
+  std::vector<unsigned long long> bases_host(o.heap_bases_host.begin(), o.heap_bases_host.end());
+  if (!bases_host.empty() && (int64_t)bases_host.size() == o.W) g.heap_bases_host = bases_host.data();
   g.budget_ns = (unsigned long long)o.budget_ms * 1000000ull;
   g.status = reinterpret_cast<int*>(o.status_ptr);
   g.max_ctas = o.max_ctas;
@@ -416,7 +420,7 @@ void scatter_push_op(const Tensor& x, const Tensor& slot_map, const c10::optiona
 
 Tensor gather_wait_op(int64_t disp_ptr, at::ScalarType dtype, int64_t M, const Tensor& idx, const Tensor& loc,
                       const c10::optional<Tensor>& gates, int64_t C, int64_t flags_ptr, int64_t n_flags, int64_t want,
-                      int64_t budget_ms, int64_t status_ptr) {
+                      int64_t budget_ms, int64_t status_ptr, int64_t want_ptr) {
   count_launch(1);
   c10::cuda::CUDAGuard guard(idx.device());
   const int K = idx.size(0), S = idx.size(1);
@@ -424,6 +428,7 @@ Tensor gather_wait_op(int64_t disp_ptr, at::ScalarType dtype, int64_t M, const T
   WaitArgs wa{};
   wa.flags = reinterpret_cast<const unsigned long long*>(flags_ptr);
   wa.n_flags = n_flags; wa.want = want; wa.budget_ns = (unsigned long long)budget_ms * 1000000ull;
+  wa.want_ptr = reinterpret_cast<const unsigned long long*>(want_ptr);
   wa.status = reinterpret_cast<int*>(status_ptr);
   DISPATCH_FLOAT(out, "gather_wait", [&] {
     launch_gather_rows<scalar_t>(reinterpret_cast<const void*>(disp_ptr), nullptr, idx.data_ptr<int>(),
@@ -580,7 +585,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("int8_decode", &int8_decode_op);
   m.def("colsum", &colsum_op, py::arg("x"), py::arg("fold") = 1, py::arg("as_bf16") = false);
   m.def("scatter_push", &scatter_push_op);
-  m.def("gather_wait", &gather_wait_op);
+  m.def("gather_wait", &gather_wait_op, py::arg("disp_ptr"), py::arg("dtype"), py::arg("M"), py::arg("idx"), py::arg("loc"),
+        py::arg("gates"), py::arg("C"), py::arg("flags_ptr"), py::arg("n_flags"), py::arg("want"), py::arg("budget_ms"),
+        py::arg("status_ptr"), py::arg("want_ptr") = 0);
   m.def("zfp_encode", &zfp_encode_op);
   m.def("zfp_decode", &zfp_decode_op);
   m.def("lz_encode", &lz_encode_op);
@@ -604,6 +611,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_readwrite("gate_flags_ptr", &GemmOpts::gate_flags_ptr)
       .def_readwrite("gate_rows", &GemmOpts::gate_rows)
       .def_readwrite("gate_want", &GemmOpts::gate_want)
+      .def_readwrite("gate_want_ptr", &GemmOpts::gate_want_ptr)
       .def_readwrite("heap_bases_ptr", &GemmOpts::heap_bases_ptr)
       .def_readwrite("push_data_off", &GemmOpts::push_data_off)
       .def_readwrite("push_flag_off", &GemmOpts::push_flag_off)
@@ -618,6 +626,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_readwrite("status_ptr", &GemmOpts::status_ptr)
       .def_readwrite("max_ctas", &GemmOpts::max_ctas)
       .def_readwrite("cta_group", &GemmOpts::cta_group)
+      .def_readwrite("heap_bases_host", &GemmOpts::heap_bases_host)
       .def_readwrite("copy_x", &GemmOpts::copy_x)
       .def_readwrite("copy_slot_map", &GemmOpts::copy_slot_map)
       .def_readwrite("copy_gates", &GemmOpts::copy_gates)

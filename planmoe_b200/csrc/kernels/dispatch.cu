@@ -198,6 +198,7 @@ struct WaitGeom {
   const unsigned long long* flags;  // local u64 flags [n_flags], or null (no wait)
   int n_flags;
   unsigned long long want;
+  const unsigned long long* want_ptr;   // overrides `want` when set
   unsigned long long budget_ns;
   int* status;
 };
@@ -215,8 +216,9 @@ gather_rows_kernel(const void* __restrict__ disp_, const float* __restrict__ sca
   if (w.flags != nullptr) {
     if (threadIdx.x == 0) ok_s = 1;
     __syncthreads();
+    const unsigned long long want = w.want_ptr != nullptr ? *w.want_ptr : w.want;
     for (int f = threadIdx.x; f < w.n_flags; f += blockDim.x) {
-      if (!wait_flag_ge(w.flags + f, w.want, w.budget_ns, w.status, f)) ok_s = 0;
+      if (!wait_flag_ge(w.flags + f, want, w.budget_ns, w.status, f)) ok_s = 0;
     }
     __syncthreads();
     if (!ok_s) return;
@@ -300,7 +302,7 @@ void launch_gather_rows(const void* disp, const float* scale_bias, const int* id
                         const WaitArgs* wait, cudaStream_t stream) {
   WaitGeom w{};
   if (wait != nullptr) {
-    w.flags = wait->flags; w.n_flags = wait->n_flags; w.want = wait->want;
+    w.flags = wait->flags; w.n_flags = wait->n_flags; w.want = wait->want; w.want_ptr = wait->want_ptr;
     w.budget_ns = wait->budget_ns; w.status = wait->status;
   }
   int ctas = (S + kRowWarps - 1) / kRowWarps;

@@ -53,6 +53,7 @@
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
+#include <cstring>
 #include <mutex>
 
 namespace planmoe {
@@ -226,14 +227,28 @@ struct KernelParams {
   __nv_bfloat16* aux; long long aux_row_stride, aux_group_stride;
   const __nv_bfloat16* bias; long long bias_group_stride;
   const unsigned long long* gate_flags; int gate_rows; unsigned long long gate_want;
+  const unsigned long long* gate_want_ptr;
   const unsigned long long* heap_bases; unsigned long long push_data_off, push_flag_off;
   int push_rows, push_C, push_c0, push_chunk, W, my_rank;
   // chunk_groups > 0: groups are [chunk][expert] with chunk_groups experts; weights / bias are indexed
   // by the expert, flags and push offsets by the chunk.
   int chunk_groups;
   unsigned long long budget_ns; int* status;
-  GemmArgs::CopyJob copy;        // copy.ctas > 0: the first copy.ctas CTAs run the dispatch send
+  GemmArgs::CopyJob copy;        // copy.ctas > 0: the copy warp of every CTA runs the dispatch send
+  int tma_out;                   // epilogue writes its staging tiles with bulk tensor stores (OutMaps valid)
 };
+
+// Tensor maps of the outputs, for the bulk tensor stores of the epilogue (box = 64 columns x 32 rows,
+// 128-byte swizzle: exactly one epilogue warp's staging tile).  Plain-store epilogues: m[0] = D,
+// m[1] = aux (the saved derivative).  Push epilogue: m[s] = the combine buffer of rank s.
+struct OutMaps {
+  CUtensorMap m[8];
+};
+
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src_smem, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(map), "r"(src_smem), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
 
 struct Ctl {
   uint64_t full[kMaxStages];
@@ -451,7 +466,7 @@ __device__ __forceinline__ void slab_bias_act(const uint32_t* v, const float* bi
 template <int CG, bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    const KernelParams p) {
+                    const __grid_constant__ OutMaps om, const KernelParams p) {
   using G = Geo<CG>;
   constexpr int kStages = G::kStages;
   constexpr uint32_t kStageBytes = G::kStageBytes;
@@ -505,6 +520,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
+      const unsigned long long gate_want = p.gate_want_ptr != nullptr ? *p.gate_want_ptr : p.gate_want;
       for (int tile = unit; tile < tiles && ok; tile += nunits) {
         const int nt = tile % nt_count;
         const int mt = (tile / nt_count) % mt_count;
@@ -516,7 +532,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           const int last_row = min(m0 + BM, p.M) - 1;
           const int s_lo = m0 / p.gate_rows, s_hi = last_row / p.gate_rows;
           for (int s = s_lo; s <= s_hi && ok; ++s)
-            ok = wait_flag_ge(p.gate_flags + (p.chunk_groups > 0 ? (g / p.chunk_groups) * p.W : 0) + s, p.gate_want,
+            ok = wait_flag_ge(p.gate_flags + (p.chunk_groups > 0 ? (g / p.chunk_groups) * p.W : 0) + s, gate_want,
                               p.budget_ns, p.status, s);
           if (!ok) { ctl->abort = 1; break; }
           fence_proxy_async();   // peers' generic-proxy stores -> this thread's async-proxy loads
@@ -648,7 +664,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       // Push epilogue: where row (m0 + q * 32 + lane) of this tile lives in the combine buffer of the
       // rank that owns the token (0 = row outside the problem).
       unsigned long long push_row = 0ull;
+      int push_s = 0, push_drow = 0;               // bulk-store form: rank and row of the slice's first row
       if constexpr (EPI == kEpiPush) {
+        {
+          const int mf = m0 + q * 32;
+          const int s = mf / p.push_rows, cc = mf - s * p.push_rows;
+          const int el = p.chunk_groups > 0 ? g % p.chunk_groups : g;
+          const int nel = p.chunk_groups > 0 ? p.chunk_groups : p.groups;
+          const int c_base = p.chunk_groups > 0 ? (g / p.chunk_groups) * p.push_rows : p.push_c0;
+          push_s = s < p.W ? s : 0;
+          push_drow = (int)(((long long)p.my_rank * nel + el) * p.push_C + c_base + cc);
+        }
         const int m = m0 + q * 32 + lane;
         if (m < p.M) {
           const int s = m / p.push_rows, cc = m - s * p.push_rows;
@@ -660,7 +686,26 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
       }
 
-      // coalesced write-out of the staging tile: each instruction stores 4 rows x 128 bytes
+      // Output of a staging tile.  With tensor maps: one bulk tensor store per tile, issued by lane 0 and
+      // tracked in its bulk group (rows and columns outside the tensor are clipped by the copy engine);
+      // the tile may be overwritten once the store has read it (stage_free).  Otherwise: coalesced
+      // 16-byte stores, each instruction 4 rows x 128 bytes.
+      const uint32_t st0_s = smem_u32(st0);
+      const int tile_row = m0 + q * 32;            // first row of this warp's 32-row slice
+      auto stage_free = [&]() {
+        if (p.tma_out) {
+          if (lane == 0) bulk_wait_read_all();
+          __syncwarp();
+        }
+      };
+      auto tma_out = [&](const CUtensorMap* map, int col, int row, int grp) {
+        fence_proxy_async();                       // the warp's staging writes -> the copy engine
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_3d(map, st0_s, col, row, grp);
+          bulk_commit();
+        }
+      };
       auto write_out = [&](__nv_bfloat16* dst, long long row_stride, long long group_stride, int nb) {
 #pragma unroll
         for (int it = 0; it < 8; ++it) {
@@ -692,6 +737,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           tmem_ld32(t_row + s2 * 64, v);
           tmem_ld32(t_row + s2 * 64 + 32, v + 32);
         }
+        stage_free();                              // the previous slab's store has left the staging tile
 
         uint4 dact[8];
         if constexpr (EPI == kEpiDAct) {
@@ -748,7 +794,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
         if constexpr (EPI == kEpiBiasAct) {
           __syncwarp();
-          if (p.aux != nullptr) write_out(p.aux, p.aux_row_stride, p.aux_group_stride, nb);
+          if (p.aux != nullptr) {
+            if (p.tma_out) {
+              if (tile_row < p.M) tma_out(&om.m[1], nb, tile_row, g);
+              stage_free();
+            } else {
+              write_out(p.aux, p.aux_row_stride, p.aux_group_stride, nb);
+            }
+          }
           __syncwarp();
         }
 #pragma unroll
@@ -761,18 +814,27 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
 
         if constexpr (EPI == kEpiPush) {
+          if (p.tma_out) {
+            // the 32 rows of the slice belong to one source rank and are contiguous in its combine buffer
+            if (tile_row < p.M) tma_out(&om.m[push_s], nb, push_drow, 0);
+          } else {
 #pragma unroll
-          for (int it = 0; it < 8; ++it) {
-            const int r = it * 4 + (lane >> 3), c = lane & 7;
-            // destination row addresses were computed once per tile, one row per lane
-            const unsigned long long rp = __shfl_sync(0xffffffffu, push_row, r);
-            if (rp != 0ull && nb + c * 8 < p.N) {
-              const uint4 val = *reinterpret_cast<const uint4*>(st0 + r * 128 + ((c ^ (r & 7)) << 4));
-              *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(rp) + nb + c * 8) = val;
+            for (int it = 0; it < 8; ++it) {
+              const int r = it * 4 + (lane >> 3), c = lane & 7;
+              // destination row addresses were computed once per tile, one row per lane
+              const unsigned long long rp = __shfl_sync(0xffffffffu, push_row, r);
+              if (rp != 0ull && nb + c * 8 < p.N) {
+                const uint4 val = *reinterpret_cast<const uint4*>(st0 + r * 128 + ((c ^ (r & 7)) << 4));
+                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(rp) + nb + c * 8) = val;
+              }
             }
           }
         } else {
-          write_out(p.D, p.d_row_stride, p.d_group_stride, nb);
+          if (p.tma_out) {
+            if (tile_row < p.M) tma_out(&om.m[0], nb, tile_row, g);
+          } else {
+            write_out(p.D, p.d_row_stride, p.d_group_stride, nb);
+          }
         }
         __syncwarp();
       }
@@ -787,6 +849,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       if (++acc == kAccStages) { acc = 0; acc_phase ^= 1u; }
 
       if constexpr (EPI == kEpiPush) {
+        if (p.tma_out && lane == 0) bulk_wait_all();   // my bulk stores have been performed
         epi_bar_sync();                            // every row of the tile has been stored
         if (etid == 0) {
           __threadfence_system();
@@ -801,6 +864,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
       }
     }
+    if (p.tma_out && lane == 0) bulk_wait_all();   // no bulk store of mine is in flight at teardown
   }
 
   // ---------------------------------------------------------------------- teardown
@@ -833,25 +897,67 @@ EncodeFn get_encode_fn() {
   return fn;
 }
 
-// 4-D map over (cols, rows, groups, chunks) with a (64, box_rows, 1, 1) box and 128-byte swizzle.
-bool make_map(CUtensorMap* map, const GemmOperand& op, int groups, int box_rows) {
+// Encoded tensor maps are cached: a training step encodes the same handful of (address, shape) pairs
+// over and over, and an encode costs microseconds of host time.
+struct MapKey {
+  const void* ptr; unsigned long long d[4]; unsigned long long st[3]; unsigned box[4]; int rank;
+  bool operator==(const MapKey& o) const { return std::memcmp(this, &o, sizeof(MapKey)) == 0; }
+};
+struct MapCache {
+  static constexpr int kSlots = 128;
+  MapKey key[kSlots]; CUtensorMap map[kSlots]; int used = 0, next = 0;
+  std::mutex mu;
+};
+MapCache& map_cache() { static MapCache c; return c; }
+
+bool encode_cached(CUtensorMap* out, int rank, const void* ptr, const cuuint64_t* dims, const cuuint64_t* strides,
+                   const cuuint32_t* box) {
   EncodeFn enc = get_encode_fn();
   if (enc == nullptr) return false;
+  MapKey k;
+  std::memset(&k, 0, sizeof(k));
+  k.ptr = ptr; k.rank = rank;
+  for (int i = 0; i < rank; ++i) { k.d[i] = dims[i]; k.box[i] = box[i]; }
+  for (int i = 0; i + 1 < rank; ++i) k.st[i] = strides[i];
+  MapCache& c = map_cache();
+  std::lock_guard<std::mutex> lock(c.mu);
+  for (int i = 0; i < c.used; ++i)
+    if (c.key[i] == k) { *out = c.map[i]; return true; }
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(ptr), dims, strides, box,
+                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  const int slot = c.used < MapCache::kSlots ? c.used++ : (c.next = (c.next + 1) % MapCache::kSlots);
+  c.key[slot] = k; c.map[slot] = *out;
+  return true;
+}
+
+// 3-D output map over (cols, rows, groups) with a (64, 32, 1) box: one epilogue warp's staging tile.
+bool make_out_map(CUtensorMap* map, const void* ptr, long long cols, long long rows, long long groups,
+                  long long row_stride, long long group_stride) {
+  if ((reinterpret_cast<uintptr_t>(ptr) % 16) || (row_stride % 8) || (groups > 1 && (group_stride % 8))) return false;
+  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)(groups > 0 ? groups : 1)};
+  cuuint64_t strides[2] = {(cuuint64_t)row_stride * 2,
+                           (cuuint64_t)(groups > 1 ? group_stride : rows * row_stride) * 2};
+  cuuint32_t box[3] = {64, 32, 1};
+  return encode_cached(map, 3, ptr, dims, strides, box);
+}
+
+// 4-D map over (cols, rows, groups, chunks) with a (64, box_rows, 1, 1) box and 128-byte swizzle.
+bool make_map(CUtensorMap* map, const GemmOperand& op, int groups, int box_rows) {
+  if (get_encode_fn() == nullptr) return false;
   const cuuint64_t chunks = op.chunks > 0 ? op.chunks : 1;
   cuuint64_t dims[4] = {(cuuint64_t)op.cols, (cuuint64_t)op.rows, (cuuint64_t)groups, chunks};
   long long gs = op.group_stride > 0 ? op.group_stride : op.rows * op.row_stride;
   long long cs = op.chunk_stride > 0 ? op.chunk_stride : gs * groups;
   cuuint64_t strides[3] = {(cuuint64_t)op.row_stride * 2, (cuuint64_t)gs * 2, (cuuint64_t)cs * 2};
   cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
-  cuuint32_t estr[4] = {1, 1, 1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(op.ptr), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS;
+  return encode_cached(map, 4, op.ptr, dims, strides, box);
 }
 
 template <int CG, bool A_MN, bool B_MN, int EPI>
-cudaError_t launch_epi(const CUtensorMap& ta, const CUtensorMap& tb, const KernelParams& kp, int ctas,
+cudaError_t launch_epi(const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& om, const KernelParams& kp, int ctas,
                        cudaStream_t stream) {
   auto kern = grouped_gemm_kernel<CG, A_MN, B_MN, EPI>;
   constexpr int smem = (int)Geo<CG>::kSmemTotal;
@@ -871,28 +977,28 @@ cudaError_t launch_epi(const CUtensorMap& ta, const CUtensorMap& tb, const Kerne
   attr[0].val.clusterDim.x = CG; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = CG > 1 ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, kern, ta, tb, kp);
+  return cudaLaunchKernelEx(&cfg, kern, ta, tb, om, kp);
 }
 
 template <int CG, bool A_MN, bool B_MN>
-cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const KernelParams& kp, int ctas,
-                           cudaStream_t stream) {
+cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& om, const KernelParams& kp,
+                           int ctas, cudaStream_t stream) {
   switch (kp.epilogue) {
-    case kEpiStore: return launch_epi<CG, A_MN, B_MN, kEpiStore>(ta, tb, kp, ctas, stream);
-    case kEpiBiasAct: return launch_epi<CG, A_MN, B_MN, kEpiBiasAct>(ta, tb, kp, ctas, stream);
-    case kEpiDAct: return launch_epi<CG, A_MN, B_MN, kEpiDAct>(ta, tb, kp, ctas, stream);
-    case kEpiPush: return launch_epi<CG, A_MN, B_MN, kEpiPush>(ta, tb, kp, ctas, stream);
+    case kEpiStore: return launch_epi<CG, A_MN, B_MN, kEpiStore>(ta, tb, om, kp, ctas, stream);
+    case kEpiBiasAct: return launch_epi<CG, A_MN, B_MN, kEpiBiasAct>(ta, tb, om, kp, ctas, stream);
+    case kEpiDAct: return launch_epi<CG, A_MN, B_MN, kEpiDAct>(ta, tb, om, kp, ctas, stream);
+    case kEpiPush: return launch_epi<CG, A_MN, B_MN, kEpiPush>(ta, tb, om, kp, ctas, stream);
     default: return cudaErrorInvalidValue;
   }
 }
 
 template <int CG>
-cudaError_t launch_layout(const GemmArgs& a, const CUtensorMap& ta, const CUtensorMap& tb, const KernelParams& kp,
-                          int ctas, cudaStream_t stream) {
-  if (!a.A.mn_major && a.B.mn_major) return launch_variant<CG, false, true>(ta, tb, kp, ctas, stream);
-  if (!a.A.mn_major && !a.B.mn_major) return launch_variant<CG, false, false>(ta, tb, kp, ctas, stream);
-  if (a.A.mn_major && a.B.mn_major) return launch_variant<CG, true, true>(ta, tb, kp, ctas, stream);
-  return launch_variant<CG, true, false>(ta, tb, kp, ctas, stream);
+cudaError_t launch_layout(const GemmArgs& a, const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& om,
+                          const KernelParams& kp, int ctas, cudaStream_t stream) {
+  if (!a.A.mn_major && a.B.mn_major) return launch_variant<CG, false, true>(ta, tb, om, kp, ctas, stream);
+  if (!a.A.mn_major && !a.B.mn_major) return launch_variant<CG, false, false>(ta, tb, om, kp, ctas, stream);
+  if (a.A.mn_major && a.B.mn_major) return launch_variant<CG, true, true>(ta, tb, om, kp, ctas, stream);
+  return launch_variant<CG, true, false>(ta, tb, om, kp, ctas, stream);
 }
 
 // Largest number of two-CTA clusters of this kernel that can be resident at once.  A persistent grid
@@ -991,6 +1097,7 @@ cudaError_t launch_grouped_gemm(const GemmArgs& a, cudaStream_t stream) {
   kp.aux = reinterpret_cast<__nv_bfloat16*>(a.aux); kp.aux_row_stride = a.aux_row_stride; kp.aux_group_stride = a.aux_group_stride;
   kp.bias = reinterpret_cast<const __nv_bfloat16*>(a.bias); kp.bias_group_stride = a.bias_group_stride;
   kp.gate_flags = a.gate_flags; kp.gate_rows = a.gate_rows > 0 ? a.gate_rows : a.M; kp.gate_want = a.gate_want;
+  kp.gate_want_ptr = a.gate_want_ptr;
   kp.heap_bases = a.heap_bases; kp.push_data_off = a.push_data_off; kp.push_flag_off = a.push_flag_off;
   kp.push_rows = a.push_rows > 0 ? a.push_rows : a.M; kp.push_C = a.push_C; kp.push_c0 = a.push_c0;
   kp.push_chunk = a.push_chunk; kp.W = a.W; kp.my_rank = a.my_rank;
@@ -1011,8 +1118,37 @@ cudaError_t launch_grouped_gemm(const GemmArgs& a, cudaStream_t stream) {
   // computed its expected count from gemm_grid_ctas() and passes it back as copy.ctas.
   if (kp.copy.ctas > 0 && kp.copy.ctas != ctas) return cudaErrorInvalidValue;
 
-  if (cg == 2) return launch_layout<2>(a, ta, tb, kp, ctas, stream);
-  return launch_layout<1>(a, ta, tb, kp, ctas, stream);
+  // ---- output tensor maps for the bulk-store epilogue ------------------------------------------
+  // Used whenever every 32-row slice of a tile maps to 32 consecutive destination rows: always for
+  // plain outputs; for the push epilogue when the rows per source rank are a multiple of 32 and the
+  // caller supplied the peers' base addresses.  PLANMOE_GEMM_TMA_STORE=0 keeps the 16-byte store path.
+  static int tma_env = -1;
+  if (tma_env < 0) {
+    const char* e = getenv("PLANMOE_GEMM_TMA_STORE");
+    tma_env = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  static OutMaps om;                       // filled per launch; copied into the kernel's parameters at launch
+  static std::mutex om_mu;
+  std::lock_guard<std::mutex> om_lock(om_mu);
+  kp.tma_out = 0;
+  if (tma_env) {
+    bool okm = true;
+    if (a.epilogue == kEpiPush) {
+      okm = a.heap_bases_host != nullptr && a.W >= 1 && a.W <= 8 && kp.push_rows % 32 == 0 && a.M % 32 == 0;
+      const int nel = a.chunk_groups > 0 ? a.chunk_groups : a.groups;
+      for (int r = 0; okm && r < a.W; ++r)
+        okm = make_out_map(&om.m[r], reinterpret_cast<const void*>(a.heap_bases_host[r] + a.push_data_off), a.N,
+                           (long long)a.W * nel * a.push_C, 1, a.N, 0);
+    } else {
+      okm = make_out_map(&om.m[0], a.D, a.N, a.M, a.groups, a.d_row_stride, a.d_group_stride);
+      if (okm && a.epilogue == kEpiBiasAct && a.aux != nullptr)
+        okm = make_out_map(&om.m[1], a.aux, a.N, a.M, a.groups, a.aux_row_stride, a.aux_group_stride);
+    }
+    kp.tma_out = okm ? 1 : 0;
+  }
+
+  if (cg == 2) return launch_layout<2>(a, ta, tb, om, kp, ctas, stream);
+  return launch_layout<1>(a, ta, tb, om, kp, ctas, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

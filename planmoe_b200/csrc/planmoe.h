@@ -35,6 +35,7 @@ struct WaitArgs {
   const unsigned long long* flags;  // local device pointer, n_flags consecutive u64
   int n_flags;
   unsigned long long want;          // proceed when every flag >= want
+  const unsigned long long* want_ptr;  // if set: `want` is read from this device word instead (CUDA-graph replays)
   unsigned long long budget_ns;     // give up (status word, kernel returns) after this long
   int* status;                      // host-mapped int32[8]
 };
@@ -118,11 +119,14 @@ struct GemmArgs {
   // flag-gated A rows (A is a receive buffer filled by peers): rows [s*gate_rows, (s+1)*gate_rows)
   // of every group become readable when gate_flags[s] >= gate_want.
   const unsigned long long* gate_flags; int gate_rows; unsigned long long gate_want;
+  const unsigned long long* gate_want_ptr;   // if set: gate_want is read from this device word at kernel start
   // push epilogue: row m of group g belongs to rank s = m / push_rows; it is stored at
   // heap_bases[s] + push_data_off + ((my_rank*groups + g) * push_C + push_c0 + m % push_rows) * N
   // and flag (push_flag_off)[push_chunk * W + my_rank] on rank s is incremented once per tile.
   const unsigned long long* heap_bases; unsigned long long push_data_off, push_flag_off;
   int push_rows, push_C, push_c0, push_chunk, W, my_rank;
+  // host copy of heap_bases (optional): lets the push epilogue use bulk tensor stores into the peers' buffers
+  const unsigned long long* heap_bases_host;
   // chunk_groups > 0: the `groups` of A / D / aux are [chunk][expert] with chunk_groups experts per
   // chunk; B and bias are indexed by the expert (group % chunk_groups); gate flags are
   // gate_flags[chunk * W + s]; pushed rows land at column offset chunk * push_rows and signal

@@ -99,7 +99,8 @@ def main():
         tr = transport.get_transport(None)
         blk = tr.alloc(G * R * H * 2 + 4096)
         ms, best = timed(lambda: gemm.grouped_gemm(
-            x, False, w1, True, gemm.EPI_PUSH, 0, bias=b1, heap_bases_ptr=blk.bases_ptr, push_data_off=blk.offset,
+            x, False, w1, True, gemm.EPI_PUSH, 0, bias=b1, heap_bases_ptr=blk.bases_ptr, heap_bases_host=blk.bases_host,
+            push_data_off=blk.offset,
             push_flag_off=blk.offset + G * R * H * 2, push_rows=R, push_C=R, W=1, my_rank=0,
             budget_ms=tr.budget_ms, status_ptr=tr.status_ptr), args.iters, flush)
         report('gemm_push_local', ms, best, flops)

@@ -62,12 +62,24 @@ class _BufferSet:
         self.off_dx = self.off_dy + self.sz_y
         self.off_flags = self.off_dx + self.sz_x
         self.W = W
-        self.arrived = [0, 0, 0, 0]               # cumulative arrivals expected per flag, per phase
+        # Cumulative arrivals expected on every flag of a phase.  The count lives in device memory and is
+        # advanced by a tiny add kernel in stream order before each use, and the waiting kernels read it
+        # from there: nothing about the step's history is baked into kernel arguments, so a captured
+        # CUDA graph of a step can be replayed.
+        self.want_dev = torch.zeros(4, dtype=torch.int64, device=tr.device)
+        self.want_views = [self.want_dev[i:i + 1] for i in range(4)]
+        self.bases_host = self.block.bases_host   # peers' base addresses, for tensor maps over their buffers
         self.held = False
 
     def off_of(self, phase):
         """Heap offset of the receive buffer the given phase writes."""
         return (self.off_x, self.off_y, self.off_dy, self.off_dx)[phase]
+
+    def expect(self, phase, arrivals):
+        """Every flag of ``phase`` will receive ``arrivals`` more; returns the device address of the new
+        cumulative count (a u64)."""
+        self.want_views[phase].add_(int(arrivals))
+        return self.want_dev.data_ptr() + 8 * phase
 
     def flag_off(self, phase):
         return self.off_flags + phase * MAX_CHUNKS * self.W * 8
@@ -130,18 +142,16 @@ def _fuse_send(world):
 
 
 def _send_and_gemm(lib, bs, phase, src, slot_map, gates, K, E, C, W, rank, d, grid, gemm):
-    """Dispatch-style push of ``src`` plus the flag-gated GEMM that consumes it.  ``gemm(want, **copy)``
-    enqueues the GEMM gated on ``want`` arrivals per (chunk, source) flag; ``grid`` is its CTA count."""
+    """Dispatch-style push of ``src`` plus the flag-gated GEMM that consumes it.  ``gemm(want_ptr, **copy)``
+    enqueues the GEMM gated on the arrival count stored at ``want_ptr``; ``grid`` is its CTA count."""
     bases = bs.block.bases_ptr
     if not _fuse_send(W):
         ctas = 4 * _sm_count()
         lib.scatter_push(src, slot_map, gates, K, E, C, bases, bs.off_of(phase), bs.flag_off(phase), W, rank, d,
                          ctas, 0, d)
-        bs.arrived[phase] += ctas
-        gemm(bs.arrived[phase])
+        gemm(bs.expect(phase, ctas))
     else:
-        bs.arrived[phase] += grid
-        gemm(bs.arrived[phase], heap_bases_ptr=bases, copy_x=src, copy_slot_map=slot_map, copy_gates=gates,
+        gemm(bs.expect(phase, grid), heap_bases_ptr=bases, copy_x=src, copy_slot_map=slot_map, copy_gates=gates,
              copy_K=K, copy_E_local=E // W, copy_C=C, copy_chunks=d, copy_ctas=grid,
              copy_data_off=bs.off_of(phase), copy_flag_off=bs.flag_off(phase))
 
@@ -211,9 +221,9 @@ class _FusedExperts(torch.autograd.Function):
         dact = torch.empty((d * E_l, R, H), dtype=x.dtype, device=x.device)
         h = torch.empty_like(dact)
 
-        def gemm1(want, **copy):
+        def gemm1(want_ptr, **copy):
             grouped_gemm(recv_x, False, w1, True, EPI_BIAS_ACT, act, bias=b1, aux=dact, out=h,
-                         gate_flags_ptr=bs.flag_ptr(PH_DISPATCH, 0), gate_rows=Cc, gate_want=want,
+                         gate_flags_ptr=bs.flag_ptr(PH_DISPATCH, 0), gate_rows=Cc, gate_want_ptr=want_ptr,
                          chunk_groups=E_l, W=W, my_rank=rank, budget_ms=budget, status_ptr=status, **copy)
         with stage('fwd.dispatch+gemm1'):
             _send_and_gemm(lib, bs, PH_DISPATCH, x, slot_map, None if postscore else gates_f, K, E, C, W, rank, d,
@@ -222,18 +232,17 @@ class _FusedExperts(torch.autograd.Function):
         # GEMM 2 over all chunks: the epilogue pushes rows to the token owners' combine buffers
         with stage('fwd.gemm2+combine_push'):
             grouped_gemm(h, False, w2, True, EPI_PUSH, 0, bias=b2,
-                         heap_bases_ptr=bases, push_data_off=bs.off_y,
+                         heap_bases_ptr=bases, heap_bases_host=bs.bases_host, push_data_off=bs.off_y,
                          push_flag_off=bs.flag_off(PH_COMBINE), push_rows=Cc, push_C=C,
                          chunk_groups=E_l, W=W, my_rank=rank, budget_ms=budget, status_ptr=status)
-        bs.arrived[PH_COMBINE] += push_arrivals
-        want_y = bs.arrived[PH_COMBINE]
+        want_y = bs.expect(PH_COMBINE, push_arrivals)
 
         # ---- combine: wait for every (chunk, expert rank) flag, gate-weighted sum over k ---------
         # flags of chunks 0..d-1 are consecutive: [d][W]
         with stage('fwd.combine_wait+decode'):
             out = lib.gather_wait(bs.block.local_ptr + (bs.off_y - bs.block.offset), x.dtype, O, idx, loc,
-                                  gates_f if postscore else None, C, bs.flag_ptr(PH_COMBINE, 0), d * W, want_y,
-                                  budget, status)
+                                  gates_f if postscore else None, C, bs.flag_ptr(PH_COMBINE, 0), d * W, 0,
+                                  budget, status, want_y)
 
         ctx.meta, ctx.bs = meta, bs
         ctx.save_for_backward(x, gates_f, w1, w2, dact, h)
@@ -273,10 +282,10 @@ class _FusedExperts(torch.autograd.Function):
         recv_x = bs.view(bs.off_x, (d * E_l, R, M))
         dh = torch.empty_like(dact)
 
-        def dgrad2(want, **copy):
+        def dgrad2(want_ptr, **copy):
             # dH = (dY . W2^T) * act'
             grouped_gemm(recv_dy, False, w2, False, EPI_DACT, act, aux=dact, out=dh,
-                         gate_flags_ptr=bs.flag_ptr(PH_COMBINE_BWD, 0), gate_rows=Cc, gate_want=want,
+                         gate_flags_ptr=bs.flag_ptr(PH_COMBINE_BWD, 0), gate_rows=Cc, gate_want_ptr=want_ptr,
                          chunk_groups=E_l, W=W, my_rank=rank, budget_ms=budget, status_ptr=status, **copy)
         with stage('bwd.combine_bwd_send+dgrad2'):
             _send_and_gemm(lib, bs, PH_COMBINE_BWD, send_src, slot_map, send_gates, send_K, E, C, W, rank,
@@ -285,11 +294,10 @@ class _FusedExperts(torch.autograd.Function):
         # dX slots = dH . W1^T, pushed back to the token owners
         with stage('bwd.dgrad1+dispatch_bwd_push'):
             grouped_gemm(dh, False, w1, False, EPI_PUSH, 0,
-                         heap_bases_ptr=bases, push_data_off=bs.off_dx,
+                         heap_bases_ptr=bases, heap_bases_host=bs.bases_host, push_data_off=bs.off_dx,
                          push_flag_off=bs.flag_off(PH_DISPATCH_BWD), push_rows=Cc, push_C=C,
                          chunk_groups=E_l, W=W, my_rank=rank, budget_ms=budget, status_ptr=status)
-        bs.arrived[PH_DISPATCH_BWD] += push_arrivals
-        want_dx = bs.arrived[PH_DISPATCH_BWD]
+        want_dx = bs.expect(PH_DISPATCH_BWD, push_arrivals)
 
         # ---- weight / bias gradients: contract over all chunks in one launch each ---------------
         with stage('bwd.wgrad2'):
@@ -304,7 +312,7 @@ class _FusedExperts(torch.autograd.Function):
         with stage('bwd.dispatch_bwd_wait+gather'):
             dx = lib.gather_wait(bs.block.local_ptr + (bs.off_dx - bs.block.offset), dout.dtype, M, idx, loc,
                                  None if postscore else gates_f, C, bs.flag_ptr(PH_DISPATCH_BWD, 0), d * W,
-                                 want_dx, budget, status)
+                                 0, budget, status, want_dx)
         if not postscore and ctx.needs_input_grad[1]:
             recv_dx = bs.view(bs.off_dx, (E * C, M))
             dgates = lib.dispatch_gate_grad(recv_dx, x, idx, loc, C)

@@ -58,6 +58,12 @@ class HeapBlock:
     def bases_ptr(self):
         return self.transport.segments[self.segment].bases_device_ptr()
 
+    @property
+    def bases_host(self):
+        """Base address of this block's heap segment on every rank, as mapped into this process."""
+        seg = self.transport.segments[self.segment]
+        return [int(seg.base(r)) for r in range(self.transport.world)]
+
     def tensor(self, dtype, shape, byte_offset=0):
         """Torch view of this rank's copy of (part of) the block."""
         n = 1

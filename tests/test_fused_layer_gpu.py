@@ -94,6 +94,43 @@ def test_fused_layer_survives_degree_changes():
         assert torch.equal(y, outs[0])
 
 
+def test_fused_layer_replays_under_cuda_graph():
+    """Two training steps (forward + backward + SGD) captured in one CUDA graph and replayed give the same
+    parameters as the same number of eager steps."""
+    from planmoe_b200.parallel import transport
+    from planmoe_b200.utils.graphs import GraphedSteps
+
+    def make():
+        layer = _layer(2, 256, 256, 2, 1.0)
+        opt = torch.optim.SGD(layer.parameters(), lr=1e-2)
+        return layer, opt
+
+    torch.manual_seed(0)
+    x = torch.randn(1024, 256, device='cuda').to(torch.bfloat16)
+
+    def one_step(layer, opt):
+        opt.zero_grad(set_to_none=True)
+        y = layer(x)
+        loss = y.float().pow(2).mean() + 0.01 * y.l_aux.float()
+        loss.backward()
+        opt.step()
+        return loss.detach().reshape(1)
+
+    warm, unroll, replays = 2, 2, 3
+    layer_e, opt_e = make()
+    for _ in range(warm * unroll + replays * unroll):     # the capture pass itself executes nothing
+        one_step(layer_e, opt_e)
+    layer_g, opt_g = make()
+    g = GraphedSteps(lambda: one_step(layer_g, opt_g), unroll=unroll, warmup=warm)     # warm-up + the captured pair
+    for _ in range(replays):
+        outs = g.replay()
+    torch.cuda.synchronize()
+    transport.get_transport(layer_g.group).check()
+    assert torch.isfinite(outs[-1]).all()
+    for pe, pg in zip(layer_e.parameters(), layer_g.parameters()):
+        assert torch.equal(pe, pg), pe.shape
+
+
 def test_generic_cuda_path_matches_fused():
     """Same layer through the generic pipeline (torch.matmul experts) and through the fused path."""
     layer = _layer(4, 256, 256, 2, 2.0, act='relu')
