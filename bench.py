@@ -9,9 +9,13 @@ capacity_factor 1.0, GELU, bf16, synthetic N(0,1) input, random-init weights, se
 
 For N > 1 launch one process per GPU with ``python -m torch.distributed.run --nproc-per-node N``.
 Rank 0 prints ONE JSON line.  ``value`` is whole-job tokens/s from CUDA-event timing of exactly
-K steps (max over ranks), with an L2 flush (256 MiB write) between timed steps that is outside the
-event brackets.  ``e2e`` repeats the measurement through the public API including, every step,
-the pinned-host -> device copy of the step's input and a device -> host read of the loss.
+K steps (max over ranks).  By default the step (forward + backward + SGD) is captured once as a
+two-step CUDA graph and the K steps are K/2 replays inside one event bracket; a step touches about
+0.6 GB, several times the L2, so no step finds its inputs cached.  ``--no-graph`` (and any run in
+which capture fails) times the eager loop instead, one event pair per step with a 256 MiB L2 flush
+between steps outside the brackets.  ``e2e`` repeats the measurement through the public API
+including, every step, the pinned-host -> device copy of the step's input (on a copy stream, one
+step or graph replay ahead) and a device -> host read of the loss.
 """
 
 import argparse
@@ -330,12 +334,19 @@ def main():
             lc0 = launch_count()
             graphed = GraphedSteps(graph_step, unroll=2, warmup=2)
             launches_per_step = (launch_count() - lc0) // (2 * 2 + 2)      # warm-up steps + the captured pair
-            graphed.replay()
-            barrier()
         except Exception as exc:                                            # capture not possible: eager loop
             print('bench.py: CUDA-graph capture failed (%s); timing the eager loop' % (exc,), file=sys.stderr)
             graphed = None
             torch.cuda.synchronize()
+        # every rank must take the same path from here on (the ranks' kernels wait for one another)
+        agreed = torch.tensor([1 if graphed is not None else 0], device=device, dtype=torch.int32)
+        if world > 1:
+            dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+        if int(agreed.item()) == 0:
+            graphed = None
+        else:
+            graphed.replay()
+        barrier()
 
     # ---- device-timed region -------------------------------------------------------------
     sampler = ClockSampler(local_rank, getattr(torch.cuda.get_device_properties(device), 'uuid', None))
