@@ -16,6 +16,18 @@ def _free_port():
 
 
 def run_workers(fn, world, backend='gloo', timeout=180, env=None, args=()):
+    """Run the workers; a failed attempt is repeated once on a fresh port (a rendezvous on a shared host can
+    lose its port between the probe and the bind), and only a second failure fails the test."""
+    try:
+        return _run_workers_once(fn, world, backend, timeout, env, args)
+    except AssertionError as first:
+        try:
+            return _run_workers_once(fn, world, backend, timeout, env, args)
+        except AssertionError as second:
+            raise AssertionError('%s\n==== first attempt ====\n%s' % (second, first))
+
+
+def _run_workers_once(fn, world, backend, timeout, env, args):
     port = _free_port()
     procs = []
     for rank in range(world):
