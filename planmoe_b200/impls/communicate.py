@@ -259,6 +259,183 @@ class RestoreBackward(torch.autograd.Function):
         return (None, simple_all_to_all(grad_output, group=ctx.group), None)
 
 
+# ---------------------------------------------------------------------------------------
+# Stream hand-over and chunked asynchronous all-to-all (autograd Functions)
+# ---------------------------------------------------------------------------------------
+# The reference declares these Functions on top of native entry points that its extension does not
+# bind (communicate.py:243-370; the four stream calls it does bind return their input unchanged,
+# custom_kernel.cpp:178-192).  Here they work: a per-device communication stream, one event per
+# hand-over index, chunked exchanges that run on that stream and are joined on use.
+
+class _CommStreams:
+    streams, events = {}, {}
+
+    @classmethod
+    def stream(cls, device):
+        key = (device.type, device.index)
+        if key not in cls.streams:
+            cls.streams[key] = torch.cuda.Stream(device=device)
+        return cls.streams[key]
+
+    @classmethod
+    def event(cls, device, idx):
+        key = (device.type, device.index, int(idx))
+        if key not in cls.events:
+            cls.events[key] = torch.cuda.Event()
+        return cls.events[key]
+
+
+def _hand_over(t, idx, to_comm):
+    """Order the two streams through event ``idx``: work that follows on the receiving stream sees
+    everything queued so far on the releasing one.  CPU tensors pass through."""
+    if not t.is_cuda:
+        return t
+    comm, cur = _CommStreams.stream(t.device), torch.cuda.current_stream(t.device)
+    ev = _CommStreams.event(t.device, idx)
+    src, dst = (cur, comm) if to_comm else (comm, cur)
+    ev.record(src)
+    dst.wait_event(ev)
+    t.record_stream(dst)
+    return t
+
+
+class CurrentStreamRelease(torch.autograd.Function):
+    """The compute stream hands ``input`` to the communication stream (backward: takes the gradient back)."""
+    @staticmethod
+    def forward(ctx, input, idx):
+        ctx.idx = idx
+        return _hand_over(input.contiguous(), idx, True)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        return _hand_over(grad_output, ctx.idx, False), None
+
+
+class CurrentStreamAcquire(torch.autograd.Function):
+    """The compute stream waits for what the communication stream produced under index ``idx``."""
+    @staticmethod
+    def forward(ctx, input, idx):
+        ctx.idx = idx
+        return _hand_over(input, idx, False)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        return _hand_over(grad_output.contiguous(), ctx.idx, True), None
+
+
+class NcclStreamRelease(torch.autograd.Function):
+    """The communication stream publishes ``input`` under index ``idx`` (the compute stream may acquire it)."""
+    @staticmethod
+    def forward(ctx, input, idx):
+        ctx.idx = idx
+        return _hand_over(input, idx, False)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        return _hand_over(grad_output, ctx.idx, True), None
+
+
+class NcclStreamAcquire(torch.autograd.Function):
+    """The communication stream waits for what the compute stream released under index ``idx``."""
+    @staticmethod
+    def forward(ctx, input, idx):
+        ctx.idx = idx
+        return _hand_over(input, idx, True)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        return _hand_over(grad_output, ctx.idx, False), None
+
+
+def _a2a_chunks(chunks, group, is_compress):
+    """All-to-all every chunk (dim 0 split over the ranks); CUDA chunks run back to back on the
+    communication stream and the caller's stream joins at the end.  ``is_compress``: ZFP fixed-rate
+    8 bits per value around each exchange, as the reference's *_zfp_async entry points intend."""
+    if get_world_size(group) == 1:
+        return [c.contiguous() for c in chunks]
+    codec = None
+    if is_compress:
+        from ..parallel import codecs
+        codec = codecs.get_compressor('zfp')
+    world = get_world_size(group)
+
+    def one(c):
+        if codec is None:
+            return simple_all_to_all(c, group=group)
+        packed = codec.compress(c.contiguous(), world)
+        wires = [simple_all_to_all(w.view(world, -1), group=group).view(w.shape) for w in packed.wires]
+        return codec.decompress(type(packed)(wires, packed.meta))
+
+    if not chunks[0].is_cuda:
+        return [one(c) for c in chunks]
+    dev = chunks[0].device
+    comm, cur = _CommStreams.stream(dev), torch.cuda.current_stream(dev)
+    comm.wait_stream(cur)
+    with torch.cuda.stream(comm):
+        outs = [one(c) for c in chunks]
+    cur.wait_stream(comm)
+    for t in list(chunks) + outs:
+        t.record_stream(comm)
+    return outs
+
+
+def _a2a_two_level(t, group):
+    """Equal-split all-to-all along dim 0 through the two-level (2DH) algorithm: on a CUDA world the
+    symmetric-heap 'dd' exchange (inside LOCAL_SIZE groups, then between them); elsewhere the flat
+    exchange, which delivers the same result."""
+    if get_world_size(group) == 1:
+        return t
+    t = t.contiguous()
+    if t.is_cuda and dist.get_backend(group) == 'nccl':
+        from ..parallel import transport
+        return transport.get_transport(group).all_to_all(t, 'dd')
+    return simple_all_to_all(t, group)
+
+
+class AllToAll2DAsync(torch.autograd.Function):
+    """Two-level all-to-all of ``input`` along dim 0; its own adjoint."""
+    @staticmethod
+    def forward(ctx, input, group=None):
+        ctx.group = group
+        return _a2a_two_level(input, group)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        return _a2a_two_level(grad_output, ctx.group), None
+
+
+class AllToAllScatterAsync(torch.autograd.Function):
+    """Split ``input`` into ``AllToAllStatus.num_split`` chunks along ``AllToAllStatus.split_dim`` and
+    all-to-all each chunk; returns the tuple of exchanged chunks.  Backward gathers."""
+    @staticmethod
+    def forward(ctx, input, is_compress=False, group=None):
+        ctx.group, ctx.is_compress = group, bool(is_compress)
+        ctx.num_split, ctx.split_dim = max(int(AllToAllStatus.num_split), 1), int(AllToAllStatus.split_dim)
+        chunks = [c.contiguous() for c in input.chunk(ctx.num_split, dim=ctx.split_dim)]
+        return tuple(_a2a_chunks(chunks, group, ctx.is_compress))
+
+    @staticmethod
+    def backward(ctx, *grads):
+        outs = _a2a_chunks([g.contiguous() for g in grads], ctx.group, ctx.is_compress)
+        return torch.cat(outs, dim=ctx.split_dim), None, None
+
+
+class AllToAllGatherAsync(torch.autograd.Function):
+    """All-to-all each chunk and concatenate them along ``AllToAllStatus.split_dim``.  Backward scatters."""
+    @staticmethod
+    def forward(ctx, is_compress, *inputs):
+        group = None
+        ctx.group, ctx.is_compress = group, bool(is_compress)
+        ctx.num_split, ctx.split_dim = len(inputs), int(AllToAllStatus.split_dim)
+        outs = _a2a_chunks([t.contiguous() for t in inputs], group, ctx.is_compress)
+        return torch.cat(outs, dim=ctx.split_dim)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        chunks = [c.contiguous() for c in grad_output.chunk(ctx.num_split, dim=ctx.split_dim)]
+        return (None,) + tuple(_a2a_chunks(chunks, ctx.group, ctx.is_compress))
+
+
 def _local_size():
     return int(os.environ.get('LOCAL_SIZE', 1))
 

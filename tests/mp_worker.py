@@ -115,6 +115,29 @@ def cpu_collectives():
     net.barrier()
 
 
+def cpu_async_a2a_functions():
+    """Chunked scatter / gather all-to-all Functions and the stream hand-over Functions against plain
+    all_to_all_single, forward and backward."""
+    from planmoe_b200.impls import communicate as C
+    rank, world, dev = _init()
+    C.AllToAllStatus.init(None, 2, 1)
+    torch.manual_seed(rank)
+    x = torch.randn(world * 2, 4, 3, device=dev, requires_grad=True)
+    ref = torch.empty_like(x)
+    dist.all_to_all_single(ref, x.detach().contiguous())
+    chunks = C.AllToAllScatterAsync.apply(C.CurrentStreamRelease.apply(x, 0), False)
+    assert len(chunks) == 2 and chunks[0].shape == (world * 2, 2, 3)
+    assert torch.equal(torch.cat(chunks, dim=1), ref)
+    back = C.CurrentStreamAcquire.apply(C.AllToAllGatherAsync.apply(False, *chunks), 1)
+    assert torch.allclose(back, x.detach())                 # a2a of an a2a with equal splits is the identity
+    w = torch.arange(back.numel(), dtype=back.dtype).view_as(back)
+    (back * w).sum().backward()
+    assert torch.allclose(x.grad, w)
+    y = C.AllToAll2DAsync.apply(x.detach())
+    assert torch.equal(y, ref)
+    print('async a2a functions ok')
+
+
 def cpu_zero_optimizer():
     rank, world, dev = _init()
     from planmoe_b200 import net

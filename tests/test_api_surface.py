@@ -32,6 +32,11 @@ def test_alias_packages_expose_the_same_modules():
                  'fast_cumsum_sub_one'):
         assert hasattr(moe, name), name
     assert callable(jit.create_cuda_kernel)
+    for name in ('AllToAllStatus', 'pre_expert_permute', 'post_expert_permute', 'CurrentStreamRelease',
+                 'CurrentStreamAcquire', 'NcclStreamRelease', 'NcclStreamAcquire', 'AllToAll2DAsync',
+                 'AllToAllScatterAsync', 'AllToAllGatherAsync', 'RestoreBackward', 'PrimAllToAll2D', 'PrimAllToAll',
+                 'PrimBwdAllreduce', 'PrimFwdAllreduce', 'PrimReducescatter', 'PrimAllgather', 'PrimSpatialSplit'):
+        assert hasattr(c2, name), name
     from planmoe.gates.top import Gate  # noqa: F401
     from planmoe.gates.cosine_top import Gate as G2  # noqa: F401
     from planmoe.experts.ffn import ExpertModule  # noqa: F401

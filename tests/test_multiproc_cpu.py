@@ -21,6 +21,10 @@ def test_net_collectives():
     run_workers('cpu_collectives', 4)
 
 
+def test_async_a2a_functions():
+    run_workers('cpu_async_a2a_functions', 2)
+
+
 def test_zero_optimizer():
     run_workers('cpu_zero_optimizer', 2)
 
