@@ -138,6 +138,37 @@ def cpu_async_a2a_functions():
     print('async a2a functions ok')
 
 
+def cpu_checkpoint_gather_and_reload():
+    """Per-rank shards -> full state (all_gather) -> shards of a world of another size -> same tensors."""
+    import tempfile
+    from planmoe_b200 import moe
+    from planmoe_b200.utils import checkpoint as ck
+    rank, world, dev = _init()
+    layer = moe.moe_layer(gate_type={'type': 'top', 'k': 2}, model_dim=16,
+                          experts={'type': 'ffn', 'count_per_node': 2, 'hidden_size_per_expert': 24,
+                                   'activation_fn': 'relu'}, seeds=(1, 10 + rank, 3))
+    full = ck.gather_expert_state(layer.state_dict())
+    assert full['experts.batched_fc1_w'].shape[0] == 2 * world
+    mine = ck.shard_expert_state(full, rank, world)
+    for k, v in layer.state_dict().items():
+        assert torch.equal(mine[k], v), k
+    # a world of half the size would hold twice the experts per rank, in global expert order
+    half = ck.shard_expert_state(full, 0, max(world // 2, 1))
+    assert torch.equal(half['experts.batched_fc1_w'][:2], full['experts.batched_fc1_w'][:2])
+    prefix = os.path.join(tempfile.gettempdir(), 'planmoe_ck_%s' % os.environ['MASTER_PORT'])
+    ck.save_sharded(layer, prefix)
+    dist.barrier()
+    other = moe.moe_layer(gate_type={'type': 'top', 'k': 2}, model_dim=16,
+                          experts={'type': 'ffn', 'count_per_node': 2, 'hidden_size_per_expert': 24,
+                                   'activation_fn': 'relu'}, seeds=(5, 50 + rank, 7))
+    ck.load_sharded(other, prefix)
+    for (k, a), (_, b) in zip(layer.state_dict().items(), other.state_dict().items()):
+        assert torch.equal(a, b), k
+    dist.barrier()
+    os.remove('%s.rank%d-of-%d.pt' % (prefix, rank, world))
+    print('checkpoint helpers ok')
+
+
 def cpu_zero_optimizer():
     rank, world, dev = _init()
     from planmoe_b200 import net

@@ -25,6 +25,10 @@ def test_async_a2a_functions():
     run_workers('cpu_async_a2a_functions', 2)
 
 
+def test_checkpoint_gather_and_reload():
+    run_workers('cpu_checkpoint_gather_and_reload', 2)
+
+
 def test_zero_optimizer():
     run_workers('cpu_zero_optimizer', 2)
 

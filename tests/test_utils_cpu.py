@@ -40,3 +40,50 @@ def test_clock_sampler_without_nvml_or_gpu_reports_no_samples():
     s.start()
     res = s.stop()
     assert set(res) >= {'sm_mhz', 'sm_max_mhz', 'reasons', 'samples'}
+
+
+def test_expert_shards_reshard_between_world_sizes(tmp_path):
+    import torch
+    from planmoe_b200.utils import checkpoint as ck
+    torch.manual_seed(0)
+    E, M, H = 8, 6, 10
+    full = {'gates.0.wg.weight': torch.randn(E, M), 'experts.batched_fc1_w': torch.randn(E, M, H),
+            'experts.batched_fc2_w': torch.randn(E, H, M), 'experts.batched_fc1_bias': torch.randn(E, H),
+            'experts.batched_fc2_bias': torch.randn(E, M), 'decoder.layers.1.moe.experts.batched_fc1_w': torch.randn(E, M, H)}
+    four = [ck.shard_expert_state(full, r, 4) for r in range(4)]
+    assert four[1]['experts.batched_fc1_w'].shape == (2, M, H)
+    assert torch.equal(four[3]['experts.batched_fc1_w'], full['experts.batched_fc1_w'][6:8])
+    assert torch.equal(four[2]['gates.0.wg.weight'], full['gates.0.wg.weight'])          # replicated
+    assert torch.equal(four[1]['decoder.layers.1.moe.experts.batched_fc1_w'],
+                       full['decoder.layers.1.moe.experts.batched_fc1_w'][2:4])
+    two = ck.reshard_state_dicts(four, 2)
+    eight = ck.reshard_state_dicts(two, 8)
+    back = ck.reshard_state_dicts(eight, 4)
+    for a, b in zip(four, back):
+        for k in a:
+            assert torch.equal(a[k], b[k]), k
+    one = ck.reshard_state_dicts(four, 1)[0]
+    for k in full:
+        assert torch.equal(one[k], full[k])
+    import pytest
+    with pytest.raises(ValueError):
+        ck.shard_expert_state(full, 0, 3)
+
+
+def test_sharded_save_and_load_round_trip_single_rank(tmp_path):
+    import torch
+    from planmoe_b200 import moe
+    from planmoe_b200.utils import checkpoint as ck
+
+    def make(seed):
+        return moe.moe_layer(gate_type={'type': 'top', 'k': 2}, model_dim=16,
+                             experts={'type': 'ffn', 'count_per_node': 4, 'hidden_size_per_expert': 32,
+                                      'activation_fn': 'relu'}, seeds=(seed, seed + 1, seed + 2))
+    a, b = make(1), make(7)
+    prefix = str(tmp_path / 'ckpt')
+    ck.save_sharded(a, prefix)
+    ck.load_sharded(b, prefix)
+    for (ka, va), (kb, vb) in zip(a.state_dict().items(), b.state_dict().items()):
+        assert ka == kb and torch.equal(va, vb)
+    x = torch.randn(32, 16)
+    assert torch.equal(a(x), b(x))
