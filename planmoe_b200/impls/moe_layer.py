@@ -180,6 +180,8 @@ class MOELayer(torch.nn.Module):
         self._scheduler = None
         self._fused = None
         self.last_stats = None
+        from ..utils import metrics
+        self.collect_stats = metrics.enabled_by_env()    # routing counters in last_stats (utils/metrics.py)
 
     # ------------------------------------------------------------------------------------
     def extra_repr(self):
@@ -320,6 +322,13 @@ class MOELayer(torch.nn.Module):
                 y = y.view(self.num_global_experts, -1, y.size(2))
 
         y = fast_decode(y.to(logits_dtype), crit, self.is_postscore)
+        self.last_stats = dict(capacity=int(crit[4]), degree=degree, path='generic')
+        if self.collect_stats:
+            from ..utils import metrics
+            self.last_stats.update(metrics.routing_stats(crit[1], crit[2], self.num_global_experts, int(crit[4])))
+            self.last_stats.update(metrics.wire_stats(self.num_global_experts, int(crit[4]), x.size(-1),
+                                                      x.element_size(), self.world_size, self.compress_name,
+                                                      self.comm_name, degree))
         return y, l_aux
 
 

@@ -345,4 +345,9 @@ def forward(layer, x, gctx, top_k, capacity_factor, degree):
     y = _FusedExperts.apply(x.contiguous(), gates, ex.batched_fc1_w, ex.batched_fc1_bias,
                             ex.batched_fc2_w, ex.batched_fc2_bias, meta)
     layer.last_stats = dict(capacity=capacity, degree=degree, path='fused')
+    if getattr(layer, 'collect_stats', False):
+        from ..utils import metrics
+        layer.last_stats.update(metrics.routing_stats(idx, loc, E, capacity))
+        layer.last_stats.update(metrics.wire_stats(E, capacity, M, x.element_size(), st.tr.world, layer.compress_name,
+                                                   layer.comm_name, degree))
     return y, l_aux.to(logits.dtype)

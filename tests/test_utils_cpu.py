@@ -87,3 +87,26 @@ def test_sharded_save_and_load_round_trip_single_rank(tmp_path):
         assert ka == kb and torch.equal(va, vb)
     x = torch.randn(32, 16)
     assert torch.equal(a(x), b(x))
+
+
+def test_routing_counters_on_the_cpu_path():
+    import torch
+    from planmoe_b200 import moe
+    from planmoe_b200.utils import metrics
+    torch.manual_seed(0)
+    layer = moe.moe_layer(gate_type={'type': 'top', 'k': 2, 'capacity_factor': 0.5}, model_dim=16,
+                          experts={'type': 'ffn', 'count_per_node': 4, 'hidden_size_per_expert': 32,
+                                   'activation_fn': 'relu'}, seeds=(1, 2, 3))
+    x = torch.randn(64, 16)
+    layer(x)
+    assert 'tokens_dropped' not in layer.last_stats                      # off by default
+    layer.collect_stats = True
+    layer(x)
+    st = metrics.as_python(layer.last_stats)
+    assert st['path'] == 'generic' and st['codec'] == 'no' and st['degree'] == 1
+    assert sum(st['tokens_routed_per_expert']) == 2 * 64                  # every token picks two experts
+    assert all(k <= st['capacity'] for k in st['tokens_kept_per_expert'])
+    assert st['tokens_dropped'] == sum(st['tokens_routed_per_expert']) - sum(st['tokens_kept_per_expert'])
+    assert st['tokens_dropped'] > 0                                       # capacity factor 0.5 must drop some
+    assert st['a2a_raw_bytes_per_rank'] == 4 * st['capacity'] * 16 * 4
+    assert 0.0 < st['slot_utilisation'] <= 1.0
