@@ -131,7 +131,8 @@ def _sm_count():
 
 
 def _fuse_send(world):
-    """Whether the dispatch send runs inside the flag-gated GEMM launch (two copy warps in every CTA).
+    """Whether the dispatch send runs inside the flag-gated GEMM launch (a copy warp in every CTA, on the
+    bulk-copy engine).
     With peers it does: transfer and math then overlap in one kernel.  With one rank nothing crosses
     NVLink and a separate copy kernel on the whole machine, run first, is the default; the environment
     variable PLANMOE_FUSE_SEND=0/1 overrides either way."""
