@@ -25,3 +25,23 @@ def fast_cumsum_sub_one(data, dim=0):
         return torch_cumsum_sub_one(data)
     out = native.lib().cumsum_sub_one(data.to(torch.int32).contiguous())
     return out.to(data.dtype)
+
+
+def _tutel_ops_cumsum(x):
+    """``torch.ops.tutel_ops.cumsum``: column-wise inclusive cumsum minus one of a 2-D int mask."""
+    return fast_cumsum_sub_one(x, dim=0)
+
+
+def _register_torch_op():
+    # The reference exposes its scan kernel as the torch operator tutel_ops::cumsum
+    # (PlanMoE/custom/custom_kernel.cpp:385); callers reach it as torch.ops.tutel_ops.cumsum(mask).
+    try:
+        lib = torch.library.Library('tutel_ops', 'DEF')
+        lib.define('cumsum(Tensor x) -> Tensor')
+        lib.impl('cumsum', _tutel_ops_cumsum, 'CompositeExplicitAutograd')
+        return lib
+    except Exception:       # already defined by an earlier import of this module under another name
+        return None
+
+
+_TORCH_LIB = _register_torch_op()

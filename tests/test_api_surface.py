@@ -48,6 +48,13 @@ def test_alias_packages_expose_the_same_modules():
         assert hasattr(k, name), name
 
 
+def test_tutel_ops_cumsum_torch_operator():
+    import planmoe_b200.jit_kernels.gating  # noqa: F401  (registers the operator)
+    mask = (torch.rand(37, 5) > 0.5).to(torch.int32)
+    out = torch.ops.tutel_ops.cumsum(mask)
+    assert torch.equal(out, torch.cumsum(mask, dim=0) - 1)
+
+
 def test_system_cache_and_timer():
     from planmoe_b200 import system
     system.cache().reset()
