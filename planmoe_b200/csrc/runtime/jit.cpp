@@ -4,6 +4,10 @@
 #include <cuda_runtime.h>
 #include <dlfcn.h>
 #include <nvrtc.h>
+#include <unistd.h>
+
+#include <cstdio>
+#include <cstdlib>
 #include <pybind11/stl.h>
 
 #include <map>
@@ -74,8 +78,56 @@ std::vector<Kernel>& kernels() {
 
 std::string g_sdk_home = "/usr/local/cuda";
 
+// nvcc route: write the source to a temporary file and run `<sdk>/bin/nvcc --cubin` as a child process
+// (the reference's default route, PlanMoE/custom/jit.h:87-118, with its -gencode derived from the live
+// device; here the target is always sm_100a).  Used when USE_NVRTC=0 or libnvrtc cannot be loaded.
+std::string compile_cubin_nvcc(const std::string& source, const std::string& name) {
+  char src_path[] = "/tmp/planmoe_jit_XXXXXX.cu";
+  const int fd = mkstemps(src_path, 3);
+  if (fd < 0) throw std::runtime_error("planmoe jit: cannot create a temporary source file");
+  const std::string cubin_path = std::string(src_path) + ".cubin";
+  const std::string log_path = std::string(src_path) + ".log";
+  {
+    FILE* f = fdopen(fd, "w");
+    if (f == nullptr) { close(fd); throw std::runtime_error("planmoe jit: cannot open the temporary source file"); }
+    fwrite(source.data(), 1, source.size(), f);
+    fclose(f);
+  }
+  const std::string cmd = "'" + g_sdk_home + "/bin/nvcc' --cubin -gencode arch=compute_100a,code=sm_100a -O3 -std=c++17 "
+                          "--use_fast_math -o '" + cubin_path + "' '" + src_path + "' > '" + log_path + "' 2>&1";
+  const int rc = std::system(cmd.c_str());
+  auto slurp = [](const std::string& path) {
+    std::string out;
+    if (FILE* f = fopen(path.c_str(), "rb")) {
+      char buf[4096];
+      size_t got;
+      while ((got = fread(buf, 1, sizeof(buf), f)) > 0) out.append(buf, got);
+      fclose(f);
+    }
+    return out;
+  };
+  std::string cubin = rc == 0 ? slurp(cubin_path) : std::string();
+  const std::string log = slurp(log_path);
+  unlink(src_path); unlink(cubin_path.c_str()); unlink(log_path.c_str());
+  if (rc != 0 || cubin.empty())
+    throw std::runtime_error("planmoe jit: nvcc failed for kernel `" + name + "`:\n" + log);
+  return cubin;
+}
+
+bool want_nvrtc() {
+  const char* e = getenv("USE_NVRTC");
+  return !(e != nullptr && e[0] == '0');
+}
+
 std::string compile_cubin(const std::string& source, const std::string& name) {
-  Nvrtc& n = nvrtc();
+  if (!want_nvrtc()) return compile_cubin_nvcc(source, name);
+  Nvrtc* np = nullptr;
+  try {
+    np = &nvrtc();
+  } catch (const std::exception&) {
+    return compile_cubin_nvcc(source, name);       // no libnvrtc on this machine: fall back to nvcc
+  }
+  Nvrtc& n = *np;
   nvrtcProgram prog;
   if (n.create(&prog, source.c_str(), (name + ".cu").c_str(), 0, nullptr, nullptr) != NVRTC_SUCCESS)
     throw std::runtime_error("nvrtcCreateProgram failed");

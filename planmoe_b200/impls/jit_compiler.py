@@ -4,9 +4,11 @@ Reference: ``PlanMoE/impls/jit_compiler.py:1-53`` on top of the native JIT engin
 ``PlanMoE/custom/jit.h`` (nvcc/NVRTC -> cuModuleLoad -> cuLaunchKernel, launch extents parsed
 from ``// [thread_extent] blockIdx.x = N`` comments, kernel name = first ``void`` function).
 
-Here the engine is the native extension's NVRTC path: the source is compiled for
-``sm_100a``, cached per (source, device), and launched on the *current* stream (the reference
-launches on the default stream).  ``@key@`` placeholders are substituted from ``keyword_dict``.
+Here the engine is the native extension's JIT: the source is compiled for ``sm_100a`` by NVRTC
+(or, with ``USE_NVRTC=0`` or no libnvrtc, by an ``nvcc --cubin`` child process from the SDK home
+set through ``update_sdk_home``), cached per (source, device), and launched on the *current*
+stream (the reference launches on the default stream).  ``@key@`` placeholders are substituted
+from ``keyword_dict``.
 """
 
 import re

@@ -110,3 +110,28 @@ def test_routing_counters_on_the_cpu_path():
     assert st['tokens_dropped'] > 0                                       # capacity factor 0.5 must drop some
     assert st['a2a_raw_bytes_per_rank'] == 4 * st['capacity'] * 16 * 4
     assert 0.0 < st['slot_utilisation'] <= 1.0
+
+
+_JIT_SRC = '''
+extern "C" __global__ void scale_by(float* __restrict__ x, int n) {
+  // [thread_extent] blockIdx.x = 4
+  // [thread_extent] threadIdx.x = 256
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) x[i] *= @factor@;
+}
+'''
+
+
+def test_user_kernels_compile_for_sm100a_without_a_gpu_nvrtc_and_nvcc(monkeypatch):
+    """Both compilation routes of the JIT engine produce an sm_100a cubin on a machine without a GPU."""
+    from planmoe_b200 import jit
+    for use_nvrtc in ('1', '0'):
+        monkeypatch.setenv('USE_NVRTC', use_nvrtc)
+        fn = jit.create_cuda_kernel(_JIT_SRC, {'factor': '2.0f'})
+        size = int(fn.compile())
+        assert size > 1000, (use_nvrtc, size)
+    monkeypatch.setenv('USE_NVRTC', '0')
+    bad = jit.create_cuda_kernel('extern "C" __global__ void broken(float* x) { x[0] = undefined_symbol; }')
+    import pytest
+    with pytest.raises(RuntimeError, match='nvcc failed'):
+        bad.compile()
