@@ -238,7 +238,8 @@ class RefTorchLayer:
 def main():
     args = parse()
     if args.impl == 'reference':
-        reference_unavailable()
+        if int(os.environ.get('RANK', '0')) == 0:          # one line per job, also under torchrun
+            reference_unavailable()
         return 0
 
     import torch
