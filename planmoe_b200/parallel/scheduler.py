@@ -14,6 +14,10 @@ fixed issue order (PlanMoE/impls/overlap.py:59-74).  This module supplies the mi
      comm algorithm, so later runs skip calibration.
 
 The measurement costs no host synchronisation until the single read at the end of calibration.
+
+The end of the module holds the analytic counterpart (a three-machine flow-shop model of the chunk
+pipeline, ``predict_degree`` / ``codec_pays_off`` / ``rank_candidates``): it explains the measured
+choice from per-stage times and orders candidates, but decisions are taken by measurement.
 """
 
 import json
@@ -138,3 +142,49 @@ class AdaptiveScheduler:
                 cache = _load_cache()
                 cache[self.key] = {'degree': self.frozen, 'ms': self.report['ms']}
                 _store_cache(cache)
+
+
+# ---------------------------------------------------------------------------------------------------
+# Analytic pipeline model (decision support; the scheduler above decides by measurement)
+# ---------------------------------------------------------------------------------------------------
+# A layer split into d chunks is a three-machine flow shop with d identical jobs: the dispatch link
+# (send of a chunk), the SMs (expert FFN of a chunk) and the return link (combine send of a chunk).
+# With per-chunk times a, b, c and a fixed cost per chunk o (flag round trips, tile quantisation, extra
+# launches) the makespan of such a shop is
+#
+#       T(d) = a + b + c + (d - 1) * max(a, b, c) + d * o,      a = t_send / d, b = t_ffn / d, c = t_return / d.
+#
+# d = 1 is the unpipelined sum; a large d approaches the slowest resource plus the per-chunk costs.  The
+# same arithmetic says whether a codec pays for itself on a link: it does when encode + decode + the
+# shrunken transfer beat the raw transfer.
+
+def flow_shop_makespan(t_send, t_ffn, t_return, degree, per_chunk_overhead=0.0):
+    """Predicted time of one pipelined pass (any unit) for ``degree`` chunks."""
+    d = max(int(degree), 1)
+    a, b, c = t_send / d, t_ffn / d, t_return / d
+    return a + b + c + (d - 1) * max(a, b, c) + d * per_chunk_overhead
+
+
+def predict_degree(t_send, t_ffn, t_return, candidates=_CANDIDATES, per_chunk_overhead=0.0):
+    """The candidate degree with the smallest predicted makespan, and the predictions."""
+    pred = {d: flow_shop_makespan(t_send, t_ffn, t_return, d, per_chunk_overhead) for d in candidates}
+    best = min(candidates, key=lambda d: (pred[d], d))
+    return best, pred
+
+
+def codec_pays_off(t_encode, t_decode, t_transfer_raw, ratio):
+    """True when compressing a payload by ``ratio`` shortens its trip: encode + decode + transfer / ratio
+    against the raw transfer (all in the same unit)."""
+    if ratio <= 1.0:
+        return False
+    return t_encode + t_decode + t_transfer_raw / ratio < t_transfer_raw
+
+
+def rank_candidates(stage_us, candidates=_CANDIDATES, per_chunk_overhead_us=3.0):
+    """Order candidate degrees by the model, from stage times as reported by ``utils.stage_timer.summary()``
+    at degree 1 (keys containing 'dispatch', 'gemm' and 'combine'); stages it cannot find count as zero."""
+    def pick(word):
+        return sum(v['median_us'] if isinstance(v, dict) else float(v) for k, v in stage_us.items() if word in k)
+    t_send, t_ffn, t_return = pick('dispatch'), pick('gemm'), pick('combine')
+    _, pred = predict_degree(t_send, t_ffn, t_return, candidates, per_chunk_overhead_us)
+    return sorted(candidates, key=lambda d: (pred[d], d)), pred

@@ -135,3 +135,22 @@ def test_user_kernels_compile_for_sm100a_without_a_gpu_nvrtc_and_nvcc(monkeypatc
     import pytest
     with pytest.raises(RuntimeError, match='nvcc failed'):
         bad.compile()
+
+
+def test_pipeline_model_of_the_scheduler():
+    from planmoe_b200.parallel import scheduler as sc
+    # link-bound layer: chunking hides the FFN behind the transfers
+    assert sc.flow_shop_makespan(80., 100., 80., 1) == 260.
+    assert sc.flow_shop_makespan(80., 100., 80., 4) == 20. + 25. + 20. + 3 * 25.
+    best, pred = sc.predict_degree(80., 100., 80., (1, 2, 4, 8), per_chunk_overhead=0.)
+    assert best == 8 and pred[8] < pred[4] < pred[2] < pred[1]
+    # a per-chunk cost makes deep pipelines lose again
+    best, pred = sc.predict_degree(80., 100., 80., (1, 2, 4, 8), per_chunk_overhead=12.)
+    assert best in (2, 4) and pred[8] > pred[best]
+    # nothing to overlap: degree 1 wins as soon as chunks cost anything
+    assert sc.predict_degree(0., 100., 0., (1, 2, 4, 8), per_chunk_overhead=1.)[0] == 1
+    assert sc.codec_pays_off(10., 10., 100., 2.0) and not sc.codec_pays_off(30., 30., 100., 2.0)
+    assert not sc.codec_pays_off(0., 0., 100., 1.0)
+    order, pred = sc.rank_candidates({'fwd.dispatch': {'median_us': 80.}, 'fwd.gemm1': 60., 'fwd.gemm2': 40.,
+                                      'fwd.combine_push': {'median_us': 80.}})
+    assert order[0] in (4, 8) and set(order) == {1, 2, 4, 8}
