@@ -465,29 +465,29 @@ def main():
         assert losses_read == args.steps
         e2e_ms = e2e_s.elapsed_time(e2e_e)
     else:
-      barrier()
-      e2e_s.record()
-      prefetch(0)
-      for i in range(args.steps):
-          b = i & 1
-          if i + 1 < args.steps:
-              prefetch(i + 1)
-          cur.wait_event(x_ready[b])
-          loss = step(x_bufs[b])
-          x_free[b].record(cur)
-          loss_host[b].copy_(loss.detach().float().reshape(1), non_blocking=True)
-          loss_done[b].record(cur)
-          if i > 0:                                      # read the previous step's loss while this one runs
-              loss_done[b ^ 1].synchronize()
-              _ = float(loss_host[b ^ 1][0])
-              losses_read += 1
-      loss_done[(args.steps - 1) & 1].synchronize()
-      _ = float(loss_host[(args.steps - 1) & 1][0])
-      losses_read += 1
-      e2e_e.record()
-      barrier()
-      assert losses_read == args.steps
-      e2e_ms = e2e_s.elapsed_time(e2e_e)
+        barrier()
+        e2e_s.record()
+        prefetch(0)
+        for i in range(args.steps):
+            b = i & 1
+            if i + 1 < args.steps:
+                prefetch(i + 1)
+            cur.wait_event(x_ready[b])
+            loss = step(x_bufs[b])
+            x_free[b].record(cur)
+            loss_host[b].copy_(loss.detach().float().reshape(1), non_blocking=True)
+            loss_done[b].record(cur)
+            if i > 0:                                      # read the previous step's loss while this one runs
+                loss_done[b ^ 1].synchronize()
+                _ = float(loss_host[b ^ 1][0])
+                losses_read += 1
+        loss_done[(args.steps - 1) & 1].synchronize()
+        _ = float(loss_host[(args.steps - 1) & 1][0])
+        losses_read += 1
+        e2e_e.record()
+        barrier()
+        assert losses_read == args.steps
+        e2e_ms = e2e_s.elapsed_time(e2e_e)
 
     if args.impl == 'ours':
         from planmoe_b200.parallel import transport
