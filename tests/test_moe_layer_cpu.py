@@ -128,3 +128,44 @@ def test_batch_prioritized_and_load_importance_loss_run():
     y = layer(x)
     (y.sum() + y.l_aux).backward()
     assert torch.isfinite(x.grad).all() and torch.isfinite(y.l_aux)
+
+
+@pytest.mark.parametrize("E,k,cf,S", [(1, 1, 1.0, 37), (2, 1, 0.5, 64), (4, 4, 1.0, 50), (8, 2, 0.25, 96), (3, 2, 2.0, 10)])
+def test_edge_shapes_match_dense_oracle(E, k, cf, S):
+    """One expert, top-1, top-k = all experts, tight capacity (many dropped tokens), odd token counts."""
+    M, H = 32, 48
+    layer = _build(E=E, M=M, H=H, k=k, cf=cf)
+    torch.manual_seed(3)
+    x = torch.randn(S, M, requires_grad=True)
+    y = layer(x)
+    (y.sum() + y.l_aux).backward()
+    ex = layer.experts
+    params = [layer.gates[0].wg.weight, ex.batched_fc1_w, ex.batched_fc1_bias, ex.batched_fc2_w, ex.batched_fc2_bias]
+    refp = [p.detach().clone().requires_grad_(True) for p in params]
+    xr = x.detach().clone().requires_grad_(True)
+    yr, l_aux = dense_moe_reference(xr, *refp, top_k=k, capacity_factor=cf, alignment=4)
+    (yr.sum() + l_aux).backward()
+    assert torch.allclose(y, yr, atol=2e-5, rtol=1e-4)
+    assert torch.allclose(x.grad, xr.grad, atol=2e-4, rtol=1e-3)
+    for p, r in zip(params, refp):
+        assert torch.allclose(p.grad, r.grad, atol=2e-4, rtol=1e-3)
+
+
+def test_all_tokens_to_one_expert_and_an_idle_expert():
+    """A gate that sends every token to expert 0: the other experts see no token (zero gradients), tokens
+    beyond the capacity are dropped, and the layer still matches the oracle."""
+    E, M, H, S = 4, 16, 24, 40
+    layer = _build(E=E, M=M, H=H, k=1, cf=1.0)
+    with torch.no_grad():
+        layer.gates[0].wg.weight.zero_()
+        layer.gates[0].wg.weight[0].fill_(5.0)
+    x = (torch.rand(S, M) + 0.5).requires_grad_(True)          # positive inputs: expert 0 always wins
+    y = layer(x)
+    y.sum().backward()
+    ex = layer.experts
+    assert ex.batched_fc1_w.grad[1:].abs().max() == 0 and ex.batched_fc2_w.grad[1:].abs().max() == 0
+    cap = layer.last_stats['capacity']
+    assert (y.abs().sum(dim=1) > 0).sum() == min(cap, S)       # tokens beyond the capacity produce zeros
+    params = [layer.gates[0].wg.weight, ex.batched_fc1_w, ex.batched_fc1_bias, ex.batched_fc2_w, ex.batched_fc2_bias]
+    yr, _ = dense_moe_reference(x.detach(), *[p.detach() for p in params], top_k=1, capacity_factor=1.0, alignment=4)
+    assert torch.allclose(y, yr, atol=2e-5, rtol=1e-4)
