@@ -7,11 +7,17 @@ capacity_factor 1.0, GELU, bf16, synthetic N(0,1) input, random-init weights, se
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference|ref-torch]
 
+``--impl reference`` builds the same layer from the reference's own package (``schemoe.moe.moe_layer``,
+installed into ``baseline/_ref`` by ``baseline/build_reference.py``; nothing of this repository's package is
+imported in that process), comm ``naive``, codec ``no``, its default pipeline degree 1, and runs the same step
+under the same timing protocol (eager loop, one event pair per step, L2 flushed between steps).
+
 For N > 1 launch one process per GPU with ``python -m torch.distributed.run --nproc-per-node N``.
 Rank 0 prints ONE JSON line.  ``value`` is whole-job tokens/s from CUDA-event timing of exactly
 K steps (max over ranks).  By default the step (forward + backward + SGD) is captured once as a
 two-step CUDA graph and the K steps are K/2 replays inside one event bracket; a step touches about
-0.6 GB, several times the L2, so no step finds its inputs cached.  ``--no-graph`` (and any run in
+0.6 GB, several times the L2, so no step finds its inputs cached.  The K-step bracket is repeated ``--repeats`` times and the median bracket is
+reported (``spread`` holds every bracket).  ``--no-graph`` (and any run in
 which capture fails) times the eager loop instead, one event pair per step with a 256 MiB L2 flush
 between steps outside the brackets.  ``e2e`` repeats the measurement through the public API
 including, every step, the pinned-host -> device copy of the step's input (on a copy stream, one
@@ -46,6 +52,8 @@ def parse():
     ap.add_argument('--compress', default='no')
     ap.add_argument('--stages', action='store_true', help='also print per-stage device times (stderr)')
     ap.add_argument('--no-graph', action='store_true', help='time the eager loop instead of CUDA-graph replays')
+    ap.add_argument('--repeats', type=int, default=5, help='how many times the K-step bracket is timed (median reported)')
+    ap.add_argument('--ref-degree', type=int, default=1, help='pipeline degree of the reference arm (its default is 1)')
     return ap.parse_args()
 
 
@@ -161,15 +169,33 @@ class ClockSampler:
         return res
 
 
-def reference_unavailable():
-    why = ("reference cannot be installed offline unmodified: setup.py lists sources under ./schemoe/ that do "
-           "not exist (the tree is named PlanMoE/) and links a privately patched libzfp from /home/xinglinpan/zfp")
-    note = os.path.join(ROOT, 'baseline', 'install_outcome.txt')
-    if os.path.exists(note):
-        first = open(note).read().strip().splitlines()
-        if first:
-            why = first[0]
-    print(json.dumps({'impl': 'reference', 'unavailable': why}))
+REF_DIR = os.path.join(ROOT, 'baseline', '_ref')
+
+
+def unavailable(why):
+    """The reference arm's line when it cannot produce a number (one per job, also under torchrun)."""
+    if int(os.environ.get('RANK', '0')) == 0:
+        print(json.dumps({'impl': 'reference', 'unavailable': ' '.join(str(why).split())[:400]}))
+    return 0
+
+
+def pin_to_gpu_numa_node(local_rank):
+    """Bind this process (and so its pinned allocations) to the CPUs next to its GPU.  Harness-level, the same
+    for every arm: NVML's CPU affinity of the GPU when it can be read, otherwise an even split of the visible
+    CPUs over the local ranks.  Only scheduling affinity of this process is touched."""
+    try:
+        import pynvml as nv
+        nv.nvmlInit()
+        h = nv.nvmlDeviceGetHandleByIndex(local_rank)
+        words = nv.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64)
+        cpus = {64 * w + b for w, m in enumerate(words) for b in range(64) if (m >> b) & 1}
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            return len(cpus)
+    except Exception:
+        pass
+    return 0
 
 
 def build_ours(args, device, group_world):
@@ -186,10 +212,35 @@ def build_ours(args, device, group_world):
     return layer.to(device).to(torch.bfloat16)
 
 
+def build_reference(args, device, rank):
+    """The reference's own layer through its own public API (``schemoe.moe.moe_layer``,
+    PlanMoE/impls/moe_layer.py:44-64), imported from ``baseline/_ref`` only."""
+    import torch
+    import torch.nn.functional as F
+    sys.path.insert(0, REF_DIR)
+    for name in [m for m in sys.modules if m == 'schemoe' or m.startswith('schemoe.') or m == 'schemoe_custom_kernel']:
+        del sys.modules[name]
+    import schemoe
+    import schemoe_custom_kernel
+    for mod in (schemoe, schemoe_custom_kernel):
+        where = os.path.realpath(mod.__file__)
+        assert where.startswith(os.path.realpath(REF_DIR) + os.sep), 'reference imported from %s' % where
+    assert not any(m == 'planmoe_b200' or m.startswith('planmoe_b200.') for m in sys.modules)
+    from schemoe.moe import moe_layer
+    layer = moe_layer(
+        gate_type={'type': 'top', 'k': CFG['top_k'], 'capacity_factor': CFG['capacity_factor'], 'fp32_gate': False},
+        model_dim=CFG['model_dim'],
+        experts={'type': 'ffn', 'count_per_node': CFG['local_experts'], 'hidden_size_per_expert': CFG['hidden'],
+                 'activation_fn': lambda t: F.gelu(t)},
+        seeds=(1, 2 + rank, 3), a2a_ffn_overlap_degree=args.ref_degree, compress_name='no', comm_name='naive')
+    return layer.to(device).to(torch.bfloat16)
+
+
 class RefTorchLayer:
     """REF-TORCH: what the reference executes, restated with stock PyTorch only — ATen routing
     (one-hot masks, cumsum), index_add scatter / gather, NCCL ``all_to_all_single``, permute copies and
-    ``torch.matmul`` experts, in the chunk order of ``PlanMoE/impls/overlap.py:59-74``."""
+    ``torch.matmul`` experts, in the chunk order of ``PlanMoE/impls/overlap.py:59-74``.  Context only: the
+    anchored comparison is ``--impl reference``."""
 
     def __init__(self, device, world):
         import torch
@@ -207,7 +258,6 @@ class RefTorchLayer:
 
     def __call__(self, x):
         import torch
-        import torch.distributed as dist
         import torch.nn.functional as F
         from planmoe_b200.ops import dispatch as D
         from planmoe_b200.impls import fast_dispatch as FD
@@ -237,26 +287,48 @@ class RefTorchLayer:
 
 def main():
     args = parse()
-    if args.impl == 'reference':
-        if int(os.environ.get('RANK', '0')) == 0:          # one line per job, also under torchrun
-            reference_unavailable()
-        return 0
-
-    import torch
-    import torch.distributed as dist
-
     world = int(os.environ.get('WORLD_SIZE', '1'))
     rank = int(os.environ.get('RANK', '0'))
     local_rank = int(os.environ.get('LOCAL_RANK', '0'))
+
+    if args.impl == 'reference':
+        if not os.path.isdir(os.path.join(REF_DIR, 'schemoe')):
+            return unavailable('baseline/_ref is absent: the reference has not been built on this machine '
+                               '(python baseline/build_reference.py --src <reference checkout>)')
+        if world == 1:
+            # AllToAllStatus.init returns before init_nccl when the group has one rank (PlanMoE/impls/communicate.py:
+            # 218-220), the native world size stays 0 and NaiveComm::all_to_all divides the byte count by it
+            # (PlanMoE/custom/comm/naive.cpp:14): an integer division by zero on the host.
+            return unavailable('the reference cannot run with one rank: AllToAllStatus.init returns early for world '
+                               'size 1 (communicate.py:218-220) and NaiveComm::all_to_all then divides by a world '
+                               'size of 0 on the host (naive.cpp:14)')
+        try:
+            return run(args, world, rank, local_rank)
+        except BaseException as exc:                      # build / import / run error of the reference: say which
+            if isinstance(exc, (KeyboardInterrupt, SystemExit)):
+                raise
+            import traceback
+            last = traceback.format_exception_only(type(exc), exc)[-1].strip()
+            print(traceback.format_exc(), file=sys.stderr)
+            return unavailable('reference failed on this box: ' + last)
+    return run(args, world, rank, local_rank)
+
+
+def run(args, world, rank, local_rank):
+    import datetime
+    import torch
+    import torch.distributed as dist
+
     if world != args.gpus:
         if world == 1 and args.gpus > 1:
             print('bench.py: --gpus %d needs torch.distributed.run with %d processes' % (args.gpus, args.gpus),
                   file=sys.stderr)
             return 2
+    affinity_cpus = pin_to_gpu_numa_node(local_rank)
     torch.cuda.set_device(local_rank)
     device = torch.device('cuda', local_rank)
     if world > 1:
-        dist.init_process_group('nccl', device_id=device)
+        dist.init_process_group('nccl', device_id=device, timeout=datetime.timedelta(seconds=300))
 
     S, M = CFG['batch'] * CFG['tokens'], CFG['model_dim']
     if args.impl == 'ours':
@@ -264,6 +336,10 @@ def main():
         params = [p for p in layer.parameters()]
         from planmoe_b200.ops import native
         launch_count = native.lib().launch_count
+    elif args.impl == 'reference':
+        layer = build_reference(args, device, rank)
+        params = [p for p in layer.parameters()]
+        launch_count = lambda: 0  # noqa: E731
     else:
         layer = RefTorchLayer(device, world)
         params = layer.parameters()
@@ -292,17 +368,19 @@ def main():
 
     for _ in range(max(args.warmup, 3)):
         step(x_dev)
-    chosen = args.degree
+    chosen = args.degree if args.impl == 'ours' else (args.ref_degree if args.impl == 'reference' else 1)
+    sched_report = None
     if args.impl == 'ours' and args.degree == 'auto':
         # the adaptive scheduler times every candidate degree over a few steps and then freezes one;
         # keep warming up (untimed) until it has, so that the timed steps all run the frozen plan
-        for _ in range(64):
+        for _ in range(256):
             sched = getattr(layer, '_scheduler', None)
             if sched is not None and sched.frozen is not None:
                 break
             step(x_dev)
         sched = getattr(layer, '_scheduler', None)
         chosen = 'auto->%s' % (sched.frozen if sched is not None else '?')
+        sched_report = getattr(sched, 'report', None)
     barrier()
     if args.stages and args.impl == 'ours':
         # separate, untimed pass with per-stage CUDA events (the timed regions below run without them)
@@ -349,98 +427,93 @@ def main():
             graphed.replay()
         barrier()
 
-    # ---- device-timed region -------------------------------------------------------------
+    # ---- device-timed region: `repeats` brackets of exactly K steps each ----------------------
     sampler = ClockSampler(local_rank, getattr(torch.cuda.get_device_properties(device), 'uuid', None))
     if rank == 0:
         sampler.start()
-    l0 = launch_count()
-    barrier()
-    host_t0 = time.perf_counter()
-    if graphed is not None:
-        # K steps = K // 2 replays of the two-step graph (+ one eager step if K is odd), one event bracket
-        # around all of them.  The working set of a step (about 0.6 GB of activations, receive buffers and
-        # weights) is several times the 126 MB L2, so no step finds its inputs cached.
-        t_s, t_e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t_s.record()
-        for _ in range(args.steps // 2):
-            graphed.replay()
-        if args.steps & 1:
-            step(x_dev)
-        t_e.record()
-        host_ms = (time.perf_counter() - host_t0) * 1e3 / args.steps
+    repeats = max(int(args.repeats), 1)
+    bracket_ms, host_ms_all, launches = [], [], 0
+    for _rep in range(repeats):
+        l0 = launch_count()
         barrier()
-        launches = launches_per_step * args.steps
-        ms = t_s.elapsed_time(t_e)
-        l2_note = 'working set per step (~0.6 GB) exceeds L2; K steps timed as one bracket of CUDA-graph replays'
-    else:
-        starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-        ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-        for i in range(args.steps):
-            flush.fill_(i & 0xff)
-            starts[i].record()
-            step(x_dev)
-            ends[i].record()
-        host_ms = (time.perf_counter() - host_t0) * 1e3 / args.steps      # host time to enqueue one step
-        barrier()
-        launches = launch_count() - l0
-        ms = sum(s.elapsed_time(e) for s, e in zip(starts, ends))
-        l2_note = 'flushed between timed steps (256 MiB write outside the event brackets)'
+        host_t0 = time.perf_counter()
+        if graphed is not None:
+            # K steps = K // 2 replays of the two-step graph (+ one eager step if K is odd), one event bracket
+            # around all of them.  The working set of a step (about 0.6 GB of activations, receive buffers and
+            # weights) is several times the 126 MB L2, so no step finds its inputs cached.
+            t_s, t_e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t_s.record()
+            for _ in range(args.steps // 2):
+                graphed.replay()
+            if args.steps & 1:
+                step(x_dev)
+            t_e.record()
+            host_ms_all.append((time.perf_counter() - host_t0) * 1e3 / args.steps)
+            barrier()
+            launches = launches_per_step * args.steps
+            bracket_ms.append(t_s.elapsed_time(t_e))
+            l2_note = 'working set per step (~0.6 GB) exceeds L2; K steps timed as one bracket of CUDA-graph replays'
+        else:
+            starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+            ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+            for i in range(args.steps):
+                flush.fill_(i & 0xff)
+                starts[i].record()
+                step(x_dev)
+                ends[i].record()
+            host_ms_all.append((time.perf_counter() - host_t0) * 1e3 / args.steps)   # host time to enqueue one step
+            barrier()
+            launches = launch_count() - l0
+            bracket_ms.append(sum(s.elapsed_time(e) for s, e in zip(starts, ends)))
+            l2_note = 'flushed between timed steps (256 MiB write outside the event brackets)'
     clocks = sampler.stop() if rank == 0 else None
+    host_ms = statistics.median(host_ms_all)
 
     # ---- end-to-end region: pinned H2D of the input + D2H of the loss, every step ---------------
-    # The way a training loop feeds a GPU: the input of step i + 1 is copied from pinned host memory on a
-    # copy stream while step i computes (two device buffers), and the loss of step i is copied to pinned
-    # host memory behind step i and read by the host one step later, so neither copy stalls the compute
+    # The way a training loop feeds a GPU: the input of a later step is copied from pinned host memory on a
+    # copy stream while the current step computes (a ring of device buffers), and the loss of step i is copied to
+    # pinned host memory behind step i and read by the host one step later, so neither copy stalls the compute
     # stream.  Every step's input is copied and every step's loss is read inside the timed region.
     copy_stream = torch.cuda.Stream(device=device)
-    x_bufs = [torch.empty_like(x_dev) for _ in range(2)]
-    x_ready = [torch.cuda.Event() for _ in range(2)]
-    x_free = [torch.cuda.Event() for _ in range(2)]
-    loss_host = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(2)]
-    loss_done = [torch.cuda.Event() for _ in range(2)]
     cur = torch.cuda.current_stream()
     losses_read = 0
-
-    def prefetch(i):
-        b = i & 1
-        with torch.cuda.stream(copy_stream):
-            copy_stream.wait_event(x_free[b])          # the step that last read this buffer has finished
-            x_bufs[b].copy_(host_x, non_blocking=True)
-            x_ready[b].record(copy_stream)
-
     e2e_s = torch.cuda.Event(enable_timing=True)
     e2e_e = torch.cuda.Event(enable_timing=True)
-    for b in range(2):
-        x_free[b].record(cur)
     if graphed is not None:
-        # Graph mode: a replay runs two steps on two static inputs.  The inputs of the next replay are copied
-        # host -> device into staging buffers on the copy stream while this replay computes, moved into the
-        # static inputs by two device copies right before the replay, and the two losses of a replay are copied
-        # to pinned host memory behind it and read one replay later.
-        pair_ready, pair_free = torch.cuda.Event(), torch.cuda.Event()
+        # Graph mode: a replay runs two steps on two static inputs.  The inputs of the next replays are copied
+        # host -> device into a ring of staging pairs on the copy stream (up to two replays ahead) while this replay
+        # computes, moved into the static inputs by two device copies right before the replay, and the two losses of
+        # a replay are copied to pinned host memory behind it and read one replay later.
+        depth = 3
+        stage_pairs = [[torch.empty_like(x_dev), torch.empty_like(x_dev)] for _ in range(depth)]
+        pair_ready = [torch.cuda.Event() for _ in range(depth)]
+        pair_free = [torch.cuda.Event() for _ in range(depth)]
         loss_pair = [torch.zeros(2, dtype=torch.float32).pin_memory() for _ in range(2)]
         pair_done = [torch.cuda.Event() for _ in range(2)]
 
-        def prefetch_pair():
+        def prefetch_pair(r):
+            b = r % depth
             with torch.cuda.stream(copy_stream):
-                copy_stream.wait_event(pair_free)
-                x_bufs[0].copy_(host_x, non_blocking=True)
-                x_bufs[1].copy_(host_x, non_blocking=True)
-                pair_ready.record(copy_stream)
+                copy_stream.wait_event(pair_free[b])
+                stage_pairs[b][0].copy_(host_x, non_blocking=True)
+                stage_pairs[b][1].copy_(host_x, non_blocking=True)
+                pair_ready[b].record(copy_stream)
 
         n_rep = args.steps // 2
-        pair_free.record(cur)
+        for b in range(depth):
+            pair_free[b].record(cur)
         barrier()
         e2e_s.record()
-        if n_rep:
-            prefetch_pair()
+        for r in range(min(depth - 1, n_rep)):
+            prefetch_pair(r)
         for r in range(n_rep):
-            cur.wait_event(pair_ready)
-            x_static[0].copy_(x_bufs[0], non_blocking=True)
-            x_static[1].copy_(x_bufs[1], non_blocking=True)
-            pair_free.record(cur)
-            if r + 1 < n_rep:
-                prefetch_pair()
+            b = r % depth
+            cur.wait_event(pair_ready[b])
+            x_static[0].copy_(stage_pairs[b][0], non_blocking=True)
+            x_static[1].copy_(stage_pairs[b][1], non_blocking=True)
+            pair_free[b].record(cur)
+            if r + depth - 1 < n_rep:
+                prefetch_pair(r + depth - 1)
             outs = graphed.replay()
             loss_pair[r & 1][0:1].copy_(outs[0], non_blocking=True)
             loss_pair[r & 1][1:2].copy_(outs[1], non_blocking=True)
@@ -465,21 +538,38 @@ def main():
         assert losses_read == args.steps
         e2e_ms = e2e_s.elapsed_time(e2e_e)
     else:
+        depth = 3
+        x_bufs = [torch.empty_like(x_dev) for _ in range(depth)]
+        x_ready = [torch.cuda.Event() for _ in range(depth)]
+        x_free = [torch.cuda.Event() for _ in range(depth)]
+        loss_host = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(2)]
+        loss_done = [torch.cuda.Event() for _ in range(2)]
+
+        def prefetch(i):
+            b = i % depth
+            with torch.cuda.stream(copy_stream):
+                copy_stream.wait_event(x_free[b])          # the step that last read this buffer has finished
+                x_bufs[b].copy_(host_x, non_blocking=True)
+                x_ready[b].record(copy_stream)
+
+        for b in range(depth):
+            x_free[b].record(cur)
         barrier()
         e2e_s.record()
-        prefetch(0)
+        for i in range(min(depth - 1, args.steps)):
+            prefetch(i)
         for i in range(args.steps):
-            b = i & 1
-            if i + 1 < args.steps:
-                prefetch(i + 1)
+            b = i % depth
+            if i + depth - 1 < args.steps:
+                prefetch(i + depth - 1)
             cur.wait_event(x_ready[b])
             loss = step(x_bufs[b])
             x_free[b].record(cur)
-            loss_host[b].copy_(loss.detach().float().reshape(1), non_blocking=True)
-            loss_done[b].record(cur)
+            loss_host[i & 1].copy_(loss.detach().float().reshape(1), non_blocking=True)
+            loss_done[i & 1].record(cur)
             if i > 0:                                      # read the previous step's loss while this one runs
-                loss_done[b ^ 1].synchronize()
-                _ = float(loss_host[b ^ 1][0])
+                loss_done[(i - 1) & 1].synchronize()
+                _ = float(loss_host[(i - 1) & 1][0])
                 losses_read += 1
         loss_done[(args.steps - 1) & 1].synchronize()
         _ = float(loss_host[(args.steps - 1) & 1][0])
@@ -493,10 +583,12 @@ def main():
         from planmoe_b200.parallel import transport
         transport.get_transport(None).check()
 
-    t = torch.tensor([ms, e2e_ms], device=device, dtype=torch.float64)
+    t = torch.tensor(bracket_ms + [e2e_ms], device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, e2e_ms = t.tolist()
+    t = t.tolist()
+    bracket_ms, e2e_ms = t[:-1], t[-1]
+    ms = statistics.median(bracket_ms)
 
     if rank == 0:
         tokens = S * world * args.steps
@@ -514,15 +606,22 @@ def main():
                 'global_batch': CFG['batch'] * world, 'seq_len': CFG['tokens'],
                 'parallelism': 'ep%d' % world, 'step': 'forward + backward + SGD update',
                 'l2': l2_note, 'cuda_graph': graphed is not None,
-                'degree': chosen, 'comm': args.comm, 'compress': args.compress,
+                'degree': chosen, 'comm': args.comm if args.impl == 'ours' else 'naive',
+                'compress': args.compress if args.impl == 'ours' else 'no',
             },
             'clocks': clocks,
+            'spread': {'brackets': len(bracket_ms), 'ms_per_step': [round(b / args.steps, 5) for b in bracket_ms],
+                       'min': min(bracket_ms) / args.steps, 'max': max(bracket_ms) / args.steps,
+                       'reported': 'median bracket of K steps, max over ranks per bracket'},
             'e2e': {'value': tokens / (e2e_ms / 1e3), 'unit': 'tokens/s',
                     'h2d_bytes_per_step': host_x.numel() * host_x.element_size(),
                     'd2h_bytes_per_step': host_loss.numel() * host_loss.element_size()},
             'gpu_launches': int(launches),
             'host_enqueue_ms_per_step': round(host_ms, 4),
+            'cpu_affinity': affinity_cpus,
         }
+        if sched_report is not None:
+            out['scheduler'] = sched_report
         print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()
