@@ -547,7 +547,7 @@ Tensor native_codec_roundtrip_op(const std::string& name, const Tensor& t, int64
 // ---- stand-alone transfers --------------------------------------------------------------------
 void xfer_op(int64_t src_ptr, const Tensor& msgs, int64_t ctas_per_msg, int64_t heap_bases_ptr, int64_t flag_off,
              int64_t wait_flags_ptr, const c10::optional<Tensor>& wait_idx, int64_t want, int64_t budget_ms,
-             int64_t status_ptr, int64_t local_dst_ptr) {
+             int64_t status_ptr, int64_t local_dst_ptr, int64_t len_off, int64_t len_base) {
   count_launch(1);
   TORCH_CHECK(msgs.is_cuda() && msgs.scalar_type() == at::kLong && msgs.is_contiguous() && msgs.dim() == 2 &&
               msgs.size(1) == 6, "msgs must be a contiguous CUDA int64 [n, 6] tensor");
@@ -557,7 +557,7 @@ void xfer_op(int64_t src_ptr, const Tensor& msgs, int64_t ctas_per_msg, int64_t 
               msgs.size(0), ctas_per_msg, reinterpret_cast<const unsigned long long*>(heap_bases_ptr), flag_off,
               reinterpret_cast<const unsigned long long*>(wait_flags_ptr), n_wait ? wait_idx->data_ptr<int>() : nullptr,
               n_wait, want, (unsigned long long)budget_ms * 1000000ull, reinterpret_cast<int*>(status_ptr),
-              reinterpret_cast<void*>(local_dst_ptr), cur_stream());
+              reinterpret_cast<void*>(local_dst_ptr), cur_stream(), len_off, (unsigned long long)len_base);
 }
 
 void wait_flags_op(int64_t flags_ptr, int64_t n, int64_t want, int64_t budget_ms, int64_t status_ptr) {
@@ -596,8 +596,17 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("native_compressor_names", &compressor_names);
   m.def("native_comm_all_to_all", &native_comm_all_to_all_op);
   m.def("native_codec_run", &native_codec_roundtrip_op);
-  m.def("xfer", &xfer_op);
+  m.def("xfer", &xfer_op, py::arg("src_ptr"), py::arg("msgs"), py::arg("ctas_per_msg"), py::arg("heap_bases_ptr"),
+        py::arg("flag_off"), py::arg("wait_flags_ptr"), py::arg("wait_idx"), py::arg("want"), py::arg("budget_ms"),
+        py::arg("status_ptr"), py::arg("local_dst_ptr"), py::arg("len_off") = -1, py::arg("len_base") = 0);
+  m.def("lz_layout", [](int64_t raw_bytes) {
+    // (payload capacity per slice, byte offset of the u32 holding the code size, header bytes) of an LZ slice
+    long long len_off = 0, header = 0;
+    lz_slice_layout(raw_bytes, &len_off, &header);
+    return std::make_tuple((int64_t)lz_payload_capacity(raw_bytes), (int64_t)len_off, (int64_t)header);
+  });
   m.def("wait_flags", &wait_flags_op);
+  m.def("delay", [](int64_t ns) { count_launch(1); launch_delay((unsigned long long)(ns < 0 ? 0 : ns), cur_stream()); });
   m.def("gemm_push_arrivals", &gemm_push_arrivals);
   m.def("launch_count", [] { return (long long)g_launches.load(); });
 

@@ -20,6 +20,9 @@ void launch_zfp_decode(const uint8_t* stream, void* x, int elem, long long lead,
 // per slice: u32 n_blocks, u32 offsets[n_blocks + 1], then the packed blocks.  sizes[slice] = bytes used.
 size_t lz_payload_capacity(long long raw_bytes);
 size_t lz_scratch_bytes(long long slices, long long raw_bytes);
+// Where a slice says how long it is: the u32 at byte *len_off holds the bytes of packed code that follow the
+// *header_bytes of header, so a slice occupies header_bytes + that value.
+void lz_slice_layout(long long raw_bytes, long long* len_off, long long* header_bytes);
 void lz_encode_cpu(const uint8_t* raw, uint8_t* payload, int* sizes, long long slices, long long raw_bytes,
                    long long payload_stride, int sym);
 void lz_decode_cpu(const uint8_t* payload, uint8_t* raw, long long slices, long long raw_bytes,

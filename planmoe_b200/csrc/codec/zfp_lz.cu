@@ -407,6 +407,11 @@ size_t lz_payload_capacity(long long raw_bytes) {
   const long long nb = lz_blocks(raw_bytes);
   return (size_t)((lz_header_bytes(nb) + nb * kLzSlotBytes + 15) / 16 * 16);
 }
+void lz_slice_layout(long long raw_bytes, long long* len_off, long long* header_bytes) {
+  const long long nb = lz_blocks(raw_bytes);
+  *len_off = 4 * (1 + nb);
+  *header_bytes = lz_header_bytes(nb);
+}
 size_t lz_scratch_bytes(long long slices, long long raw_bytes) {
   const long long nb = lz_blocks(raw_bytes);
   return (size_t)(slices * nb * (kLzSlotBytes + 4) + 16);

@@ -7,7 +7,10 @@
 //   heap_bases[dest] + dst_off     (a peer's or this rank's heap), or
 //   local_dst + dst_off            (dest < 0: plain local output tensor),
 // and finally, if the message carries a flag index, issues a system-scope fence and a release-add
-// on that flag in the destination rank's heap.  Layout transforms of the hierarchical algorithms
+// on that flag in the destination rank's heap.  Messages may be self-describing (`len_off >= 0`): the
+// u32 at byte `len_off` of the message's source holds its payload size, and only `len_base` + that many
+// bytes (rounded up to 16) are moved.  That is how the variable-length slices of the LZ codec travel
+// without the host ever reading a size: the header goes with the data, hop by hop.  Layout transforms of the hierarchical algorithms
 // are folded into the (src_off, dst_off) pairs, so no staging transpose kernels exist
 // (reference: PlanMoE/custom/comm/layout_transform.cu:3-83 and the memStrideCopy kernels of
 // PlanMoE/custom/jit.h:301-312).  The ncclSend/ncclRecv groups of custom/comm/{naive,pipe,hetu}.cpp
@@ -27,7 +30,8 @@ __global__ void __launch_bounds__(32)
 xfer_kernel(const unsigned char* __restrict__ src_base, const long long* __restrict__ msgs, int n_msgs,
             const unsigned long long* __restrict__ heap_bases, unsigned long long flag_off,
             const unsigned long long* __restrict__ wait_flags, const int* __restrict__ wait_idx, int n_wait,
-            unsigned long long want, unsigned long long budget_ns, int* status, unsigned char* local_dst) {
+            unsigned long long want, unsigned long long budget_ns, int* status, unsigned char* local_dst,
+            long long len_off, unsigned long long len_base) {
   extern __shared__ __align__(128) unsigned char xs[];
   __shared__ unsigned long long bars[kXferSlots];
   const int lane = threadIdx.x;
@@ -37,7 +41,7 @@ xfer_kernel(const unsigned char* __restrict__ src_base, const long long* __restr
   const long long flag_idx = msgs[m * 6 + 1];
   const unsigned long long src_off = (unsigned long long)msgs[m * 6 + 2];
   const unsigned long long dst_off = (unsigned long long)msgs[m * 6 + 3];
-  const unsigned long long bytes = (unsigned long long)msgs[m * 6 + 4];
+  unsigned long long bytes = (unsigned long long)msgs[m * 6 + 4];
   const long long wait_one = msgs[m * 6 + 5];
 
   // ---- what this message reads must have arrived (bounded) --------------------------------------
@@ -56,6 +60,11 @@ xfer_kernel(const unsigned char* __restrict__ src_base, const long long* __restr
   if (lane < kXferSlots) mbar_init(smem_u32(&bars[lane]), 1);
   fence_barrier_init();
   __syncwarp();
+  if (len_off >= 0) {                              // self-describing message: move the valid prefix only
+    const unsigned v = *reinterpret_cast<const volatile unsigned*>(src_base + src_off + len_off);
+    const unsigned long long valid = (len_base + (unsigned long long)v + 15ull) & ~15ull;
+    if (valid < bytes) bytes = valid;
+  }
 
   // ---- my slice of the message, in 16 KiB units, through the bulk-copy engine --------------------
   // Lane l owns slot l: load a unit into it, wait for the bytes, store it to the destination, and reuse
@@ -100,7 +109,8 @@ xfer_kernel(const unsigned char* __restrict__ src_base, const long long* __restr
 void launch_xfer(const void* src_base, const long long* msgs, int n_msgs, int ctas_per_msg,
                  const unsigned long long* heap_bases, unsigned long long flag_off,
                  const unsigned long long* wait_flags, const int* wait_idx, int n_wait, unsigned long long want,
-                 unsigned long long budget_ns, int* status, void* local_dst, cudaStream_t stream) {
+                 unsigned long long budget_ns, int* status, void* local_dst, cudaStream_t stream, long long len_off,
+                 unsigned long long len_base) {
   if (n_msgs <= 0) return;
   if (ctas_per_msg < 1) ctas_per_msg = 1;
   constexpr int smem = kXferSlots * kXferSlotBytes;
@@ -112,7 +122,7 @@ void launch_xfer(const void* src_base, const long long* msgs, int n_msgs, int ct
   dim3 grid(ctas_per_msg, n_msgs);
   xfer_kernel<<<grid, 32, smem, stream>>>(reinterpret_cast<const unsigned char*>(src_base), msgs, n_msgs, heap_bases,
                                         flag_off, wait_flags, wait_idx, n_wait, want, budget_ns, status,
-                                        reinterpret_cast<unsigned char*>(local_dst));
+                                        reinterpret_cast<unsigned char*>(local_dst), len_off, len_base);
 }
 
 // A kernel that only waits (used by tests of the bounded-wait path and by host code that needs a
@@ -126,6 +136,19 @@ void launch_wait_flags(const unsigned long long* flags, int n, unsigned long lon
                        int* status, cudaStream_t stream) {
   if (n <= 0) return;
   wait_flags_kernel<<<1, 128, 0, stream>>>(flags, n, want, budget_ns, status);
+}
+
+// Occupies the stream for `ns` nanoseconds (at most 200 ms) without touching memory.  Host code that wants to
+// time a burst of launches on the device enqueues this first, so that the burst is fully queued before its
+// first kernel starts and runs without launch gaps.
+__global__ void delay_kernel(unsigned long long ns) {
+  const unsigned long long t0 = global_timer_ns();
+  while (global_timer_ns() - t0 < ns) __nanosleep(1000);
+}
+
+void launch_delay(unsigned long long ns, cudaStream_t stream) {
+  if (ns > 200000000ull) ns = 200000000ull;
+  delay_kernel<<<1, 1, 0, stream>>>(ns);
 }
 
 }  // namespace planmoe

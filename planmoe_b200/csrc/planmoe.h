@@ -81,12 +81,17 @@ void launch_int8_decode(const unsigned char* q, const float* scale, const float*
 // ---- kernels/a2a.cu --------------------------------------------------------------------------
 // msgs: device int64 [n_msgs][6] = (dest rank or -1, flag index to signal or -1, src_off, dst_off, bytes,
 // position in wait_flags this message alone waits for, or -1 = all of wait_idx).
+// len_off >= 0: every message is self-describing; the u32 at byte len_off of its source is its payload size and
+// only len_base + that many bytes (rounded up to 16) are moved.
 void launch_xfer(const void* src_base, const long long* msgs, int n_msgs, int ctas_per_msg,
                  const unsigned long long* heap_bases, unsigned long long flag_off,
                  const unsigned long long* wait_flags, const int* wait_idx, int n_wait, unsigned long long want,
-                 unsigned long long budget_ns, int* status, void* local_dst, cudaStream_t stream);
+                 unsigned long long budget_ns, int* status, void* local_dst, cudaStream_t stream,
+                 long long len_off = -1, unsigned long long len_base = 0);
 void launch_wait_flags(const unsigned long long* flags, int n, unsigned long long want, unsigned long long budget_ns,
                        int* status, cudaStream_t stream);
+// keeps the stream busy for ns nanoseconds (clamped to 200 ms)
+void launch_delay(unsigned long long ns, cudaStream_t stream);
 
 // ---- kernels/gemm_tcgen05.cu -----------------------------------------------------------------
 // Grouped bf16 GEMM  D[g] (Mg x N) = A[g] (Mg x K) . B[g] (K x N), fp32 accumulation in TMEM.

@@ -15,8 +15,9 @@ Two execution paths:
     (``impls.overlap``) -> decode.
 
 ``a2a_ffn_overlap_degree`` may be an int (fixed chunk count, as in the reference) or
-``'auto'`` / 0: the adaptive scheduler (``planmoe_b200.parallel.scheduler``) then measures
-candidate degrees during the first steps and freezes the fastest.
+``'auto'`` / 0, and ``comm_name`` may be ``'auto'``: the adaptive scheduler
+(``planmoe_b200.parallel.scheduler``) then calibrates once at the first forward (device-timed
+repetitions of this layer's own forward + backward) and freezes one plan for all ranks.
 
 Sharded experts (fewer experts than ranks) work in both modes the reference declares but
 cannot run: ``parallel_type='model'`` splits the hidden dimension and sums partial outputs,
@@ -203,13 +204,78 @@ class MOELayer(torch.nn.Module):
         return y.reshape(y.size(0), y.size(1), -1)
 
     # ------------------------------------------------------------------------------------
-    def _resolve_degree(self, degree, x):
-        if isinstance(degree, str) or not degree:
-            from ..parallel import scheduler
-            if self._scheduler is None:
-                self._scheduler = scheduler.AdaptiveScheduler.for_layer(self)
-            return self._scheduler
-        return None
+    def _plan(self, degree, x, gctx, top_k, cf, reserve_shape):
+        """(degree, comm_name) of this call.  An integer degree and a named algorithm are used as given; 'auto'
+        (degree 0 / 'auto', comm_name 'auto') goes through the adaptive scheduler, which calibrates at the first
+        call, collectively over the layer's group, and then always returns the frozen plan."""
+        degree_auto = isinstance(degree, str) or not degree
+        comm_auto = self.comm_name == 'auto'
+        if not degree_auto and not comm_auto:
+            return int(degree), self.comm_name
+        from ..parallel import scheduler
+        if self._scheduler is None:
+            self._scheduler = scheduler.AdaptiveScheduler.for_layer(self, x, top_k, cf, degree_auto=degree_auto)
+            if not degree_auto:
+                self._scheduler.degrees = [int(degree)]
+        sched = self._scheduler
+        if sched.frozen is None:
+            E = self.num_global_experts
+            base_cap = top_k * int(cf * ((x.size(0) + E - 1) // E)) if cf > 0 else 0
+
+            def allowed(d):
+                # chunks must divide the capacity once it is aligned to 4 * shards * d
+                return d <= 32 and (base_cap == 0 or base_cap >= 4 * self.sharded_count * d)
+
+            params = [p for p in self.parameters() if p.requires_grad]
+
+            def run_candidate(d, comm):
+                with torch.enable_grad():
+                    xin = x.detach().requires_grad_(True)
+                    y, l_aux = self._forward_core(xin, gctx, top_k, cf, int(d), reserve_shape,
+                                                  comm_name=comm or self.comm_name)
+                    outs = [y] if l_aux is None or not l_aux.requires_grad else [y, l_aux]
+                    grads = [torch.ones_like(o) for o in outs]
+                    torch.autograd.grad(outs, [xin] + params, grads, allow_unused=True)
+
+            was_training = self.save_count
+            sched.resolve(run_candidate, x.device, allowed_degree=allowed,
+                          stage_split=lambda: self._roofline_stage_split(x, top_k, cf),
+                          codec_info=self._codec_verdict(x, top_k, cf))
+            self.save_count = was_training
+        comm = sched.frozen_comm or (self.comm_name if not comm_auto else 'naive')
+        return sched.frozen, comm
+
+    def _roofline_stage_split(self, x, top_k, cf):
+        """(send, ffn, return) times of one forward + backward at degree 1, from shapes: NVLink bytes at the
+        measured peer bandwidth and expert FLOPs at the measured sustained bf16 rate.  Input of the scheduler's
+        flow-shop model."""
+        W, E = self.world_size, self.num_global_experts
+        M = x.size(-1)
+        H = getattr(self.experts, 'hidden_size_per_expert', M) // max(self.sharded_count, 1)
+        C = top_k * int(max(cf, 1.0) * ((x.size(0) + E - 1) // E))
+        wire = E * C * M * x.element_size() * (W - 1) / max(W, 1)
+        if self.compress_name in ('int8', 'zfp'):
+            wire /= 2.0
+        t_link = 2.0 * wire / 770e9                              # forward + backward use each direction twice
+        # per rank E_l * W * C rows through two GEMMs of 2 * M * H FLOPs per row, forward + dgrad + wgrad
+        flops = 3.0 * 2.0 * 2.0 * max(E // max(W, 1), 1) * W * C * M * H
+        t_ffn = flops / 1.4e15
+        return t_link * 1e3, t_ffn * 1e3, t_link * 1e3
+
+    def _codec_verdict(self, x, top_k, cf):
+        """For a configured codec: whether, by the model, its encode + decode time is paid back by the bytes it
+        takes off NVLink (kernels at their measured rates; recorded in the scheduler's report)."""
+        if self.compress_name in ('no', None):
+            return None
+        from ..parallel import scheduler
+        W, E = self.world_size, self.num_global_experts
+        C = top_k * int(max(cf, 1.0) * ((x.size(0) + E - 1) // E))
+        raw = E * C * x.size(-1) * x.element_size()
+        rates = {'int8': (1800e9, 2300e9, 2.0), 'zfp': (190e9, 160e9, 2.0), 'lz': (20e9, 230e9, 1.2)}
+        enc, dec, ratio = rates.get(self.compress_name, (1e12, 1e12, 1.0))
+        t_raw = raw * (W - 1) / max(W, 1) / 770e9
+        pays = scheduler.codec_pays_off(raw / enc, raw / dec, t_raw, ratio)
+        return {'name': self.compress_name, 'ratio': ratio, 'pays_off_on_nvlink': bool(pays)}
 
     def _route(self, x, gctx, top_k, capacity_factor, degree):
         logits = gctx(x)
@@ -232,19 +298,30 @@ class MOELayer(torch.nn.Module):
             alignment=4 * self.sharded_count * degree)
         return logits.dtype, crit, l_aux
 
-    def _fused_path_ok(self, x, gctx):
+    def _fused_path_ok(self, x, gctx, top_k, cf, degree, comm_name):
+        """Whether this call can run on the fused sm_100a kernels; everything else takes the generic path."""
         if not x.is_cuda or os.environ.get('PLANMOE_FUSED', '1') == '0':
             return False
         if self.experts_type != 'ffn' or self.sharded_count != 1:
             return False
-        # the fused kernels move raw bf16 rows; a codec takes the generic compress -> all-to-all -> decompress path
-        if self.compress_name != 'no' or self.comm_name not in ('naive', 'pipe'):
+        if getattr(self.experts, 'skip_expert', False):
             return False
-        if self.batch_prioritized_routing or not self.is_gshard_loss:
+        # codecs: raw bf16 rows or int8 rows (quantised by the sender, de-quantised in front of the GEMM);
+        # zfp / lz take the generic compress -> all-to-all -> decompress pipeline
+        if self.compress_name not in ('no', 'int8'):
+            return False
+        # on one NVSwitch domain the flat push is Pipe-A2A's equal (every peer is one hop away at full rate);
+        # the hierarchical algorithms exist on the generic path
+        if comm_name not in ('naive', 'pipe'):
+            return False
+        if not self.is_gshard_loss:
             return False
         if getattr(gctx, 'gate_kind', None) not in ('top', 'cosine_top'):
             return False
         if self.num_global_experts > 64 or x.size(-1) % 64 != 0:
+            return False
+        from ..ops import fused_moe
+        if min(int(top_k), self.num_global_experts) > fused_moe.MAX_TOP_K or int(degree) > fused_moe.MAX_CHUNKS:
             return False
         return self.experts.fused_ok(x)
 
@@ -265,31 +342,27 @@ class MOELayer(torch.nn.Module):
         gctx = self.gates[gate_index]
         degree = self.a2a_ffn_overlap_degree if a2a_ffn_overlap_degree is None \
             else a2a_ffn_overlap_degree
-        sched = self._resolve_degree(degree, x)
-        if sched is not None:
-            degree = sched.next_degree()
         top_k = gctx.top_k if top_k is None else top_k
         cf = gctx.capacity_factor if capacity_factor is None else capacity_factor
+        reserve_shape = original_shape[-reserve_dims:]
+        degree, comm_name = self._plan(degree, x, gctx, top_k, cf, reserve_shape)
         if self.training:
             self.save_count += 1
-
-        if sched is not None:
-            sched.begin_step(x)
-
-        if self._fused_path_ok(x, gctx) and cf > 0:
-            from ..ops import fused_moe
-            y, l_aux = fused_moe.forward(self, x, gctx, top_k, cf, int(degree))
-        else:
-            y, l_aux = self._generic_forward(x, gctx, top_k, cf, int(degree),
-                                             original_shape[-reserve_dims:])
-        if sched is not None:
-            sched.end_step(x)
+        y, l_aux = self._forward_core(x, gctx, top_k, cf, int(degree), reserve_shape, comm_name)
 
         y = y.view(list(original_shape)).to(original_dtype)
         self.l_aux = y.l_aux = l_aux
         return self.result_func(y) if self.result_func is not None else y
 
-    def _generic_forward(self, x, gctx, top_k, cf, degree, reserve_shape):
+    def _forward_core(self, x, gctx, top_k, cf, degree, reserve_shape, comm_name=None):
+        comm_name = comm_name or self.comm_name
+        if self._fused_path_ok(x, gctx, top_k, cf, degree, comm_name):
+            from ..ops import fused_moe
+            return fused_moe.forward(self, x, gctx, top_k, cf, int(degree))
+        return self._generic_forward(x, gctx, top_k, cf, int(degree), reserve_shape, comm_name)
+
+    def _generic_forward(self, x, gctx, top_k, cf, degree, reserve_shape, comm_name=None):
+        comm_name = comm_name or self.comm_name
         if x.is_cuda:
             with torch.autocast('cuda', enabled=False):
                 logits_dtype, crit, l_aux = self._route(x, gctx, top_k, cf, degree)
@@ -313,7 +386,7 @@ class MOELayer(torch.nn.Module):
 
         y = a2a_ffn_overlap_forward(
             y, expert_fn=expert_fn, a2a_ffn_overlap_degree=degree, use_2dh=self.use_2dh,
-            group=self.group, compress_name=self.compress_name, comm_name=self.comm_name)
+            group=self.group, compress_name=self.compress_name, comm_name=comm_name)
 
         if self.num_global_experts < self.world_size:
             if self.use_model_parallel:
@@ -322,13 +395,13 @@ class MOELayer(torch.nn.Module):
                 y = y.view(self.num_global_experts, -1, y.size(2))
 
         y = fast_decode(y.to(logits_dtype), crit, self.is_postscore)
-        self.last_stats = dict(capacity=int(crit[4]), degree=degree, path='generic')
+        self.last_stats = dict(capacity=int(crit[4]), degree=degree, path='generic', comm=comm_name)
         if self.collect_stats:
             from ..utils import metrics
             self.last_stats.update(metrics.routing_stats(crit[1], crit[2], self.num_global_experts, int(crit[4])))
             self.last_stats.update(metrics.wire_stats(self.num_global_experts, int(crit[4]), x.size(-1),
                                                       x.element_size(), self.world_size, self.compress_name,
-                                                      self.comm_name, degree))
+                                                      comm_name, degree))
         return y, l_aux
 
 

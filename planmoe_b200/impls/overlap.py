@@ -45,7 +45,12 @@ class ChunkHandle:
 
     def _run(self, t):
         packed = self.codec.compress(self.comm.pre_comm(t), self.comm.world_size)
-        packed.wires = [self.comm.all_to_all(w) for w in packed.wires]
+        var_len = getattr(packed, 'var_len', None)
+        if var_len is not None and hasattr(self.comm, 'all_to_all_var'):
+            packed.wires = [self.comm.all_to_all_var(packed.wires[0], *var_len)] + \
+                           [self.comm.all_to_all(w) for w in packed.wires[1:]]
+        else:
+            packed.wires = [self.comm.all_to_all(w) for w in packed.wires]
         return packed
 
     def launch(self, t):

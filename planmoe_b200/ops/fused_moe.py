@@ -40,7 +40,8 @@ from .gemm import ACT_CODES, EPI_BIAS_ACT, EPI_DACT, EPI_PUSH, EPI_STORE, groupe
 from ..parallel import transport as T
 from ..utils.stage_timer import stage
 
-MAX_CHUNKS = 32
+MAX_CHUNKS = 32      # flag slots reserved per phase: [phase][chunk][source rank]
+MAX_TOP_K = 4        # the fused gate kernel keeps at most four picks per token
 PH_DISPATCH, PH_COMBINE, PH_COMBINE_BWD, PH_DISPATCH_BWD = 0, 1, 2, 3
 
 
@@ -328,6 +329,7 @@ def forward(layer, x, gctx, top_k, capacity_factor, degree):
     S, M = x.shape
     E = layer.num_global_experts
     top_k = min(int(top_k), E)
+    assert degree <= MAX_CHUNKS and top_k <= MAX_TOP_K, "plan outside the fused kernels' limits"
 
     with torch.autocast('cuda', enabled=False), stage('fwd.gate_linear'):
         logits = gctx(x)

@@ -14,8 +14,17 @@ arithmetic, including the layout transforms of the hierarchical algorithms.
 N = W / L groups, n = bytes per (source, destination) pair.
 
 Staging buffers and flags live in the symmetric heap and are double-buffered by call parity; flags
-are cumulative arrival counters.  The result is copied out of the heap into an ordinary tensor by
-the last launch, so callers own their output.
+are cumulative arrival counters.  By default the result is copied out of the heap into an ordinary
+tensor by the last launch, so callers own their output.  ``heap_out=True`` skips that copy: the last
+launch only waits for the arrivals and the caller gets a view of the receive buffer in the heap, which
+stays valid until this rank's next all-to-all of the same algorithm and parity, i.e. across exactly one
+further call (peers can only overwrite it after this rank has entered the call after the next).
+
+Variable-length payloads (``var_len=(len_off, len_base)``): every (source, destination) slice carries
+its own size in a u32 at byte ``len_off`` and only ``len_base`` + that many bytes of the slice are
+moved, at every hop of every algorithm, with no host read of the sizes (the LZ codec's wire).
+Staging blocks are sized to the next power of two of the per-pair payload, so payload sizes that drift
+reuse their block instead of growing the heap call by call.
 """
 
 import os
@@ -68,7 +77,9 @@ class A2AChannel:
             return cur
         from .transport import HeapBlock
         W, L = self.W, self.L
-        cap = max(n, 1 << 20)
+        cap = 1 << 20
+        while cap < n:
+            cap <<= 1
         if algo == 'hetu':
             sizes = dict(a=L * W * cap, b=L * W * cap, c=W * cap)
         elif algo == 'dd':
@@ -172,7 +183,7 @@ class A2AChannel:
         count = {'flat': [W], 'pipe': [W], 'dd': [W, W], 'hetu': [W, N * L * L, N * L * L]}[algo][logical]
         return max(1, min(592 // max(count, 1), max(1, n >> 16)))
 
-    def run(self, t, algo='flat'):
+    def run(self, t, algo='flat', var_len=None, heap_out=False):
         lib = native.lib()
         tr = self.tr
         W = self.W
@@ -187,7 +198,9 @@ class A2AChannel:
         self.calls += 1
         bufs = self._ensure(algo, parity, n)
         built, arrivals = self._tables(algo, parity, n, bufs)
-        out = torch.empty_like(t)
+        out = None if heap_out else torch.empty_like(t)
+        len_off, len_base = (-1, 0) if var_len is None else (int(var_len[0]), int(var_len[1]))
+        result = out
 
         # cumulative arrivals every flag of every pushing phase will have reached after this call
         for logical, per_call in arrivals.items():
@@ -214,7 +227,15 @@ class A2AChannel:
                 for ev in side_events:
                     cur.wait_event(ev)
                 side_events = []
-                lib.xfer(src_ptr, msgs, ctas, bases, flag_off, wait_ptr, wait, want, budget, status, out.data_ptr())
+                if ph.logical is None and heap_out:
+                    # last phase without the copy-out: a stream-ordered "everything has arrived" point
+                    idx = ph.wait_idx
+                    assert idx == list(range(len(idx)))
+                    lib.wait_flags(wait_ptr, len(idx), want, budget, status)
+                    result = bufs[ph.src].tensor(t.dtype, tuple(t.shape))
+                else:
+                    lib.xfer(src_ptr, msgs, ctas, bases, flag_off, wait_ptr, wait, want, budget, status,
+                             out.data_ptr() if out is not None else 0, len_off, len_base)
             else:
                 if self.side is None:
                     self.side = [torch.cuda.Stream(device=tr.device) for _ in range(2)]
@@ -222,7 +243,7 @@ class A2AChannel:
                 s.wait_stream(cur)
                 with torch.cuda.stream(s):
                     lib.xfer(src_ptr, msgs, ctas, bases, flag_off, wait_ptr, wait, want, budget, status,
-                             out.data_ptr())
+                             out.data_ptr() if out is not None else 0, len_off, len_base)
                     side_events.append(s.record_event())
                 t.record_stream(s)
-        return out
+        return result

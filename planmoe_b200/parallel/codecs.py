@@ -21,14 +21,25 @@ from ..ops import native
 
 
 class Packed:
-    """Wire form of one tensor: ``wires`` are moved by the all-to-all; ``meta`` stays local."""
-    __slots__ = ('wires', 'meta')
+    """Wire form of one tensor: ``wires`` are moved by the all-to-all; ``meta`` stays local.
 
-    def __init__(self, wires, meta):
-        self.wires, self.meta = wires, meta
+    ``var_len`` (optional) marks wire 0 as ``[W, cap]`` bytes of self-describing slices: ``(len_off,
+    len_base)`` as understood by ``AbstractComm.all_to_all_var``."""
+    __slots__ = ('wires', 'meta', 'var_len')
+
+    def __init__(self, wires, meta, var_len=None):
+        self.wires, self.meta, self.var_len = wires, meta, var_len
 
     def wire_bytes(self):
-        return sum(w.numel() * w.element_size() for w in self.wires)
+        """Bytes that cross the link (a statistic: for a variable-length wire it reads the slice headers, which
+        synchronises with the device)."""
+        total = sum(w.numel() * w.element_size() for w in self.wires[1 if self.var_len else 0:])
+        if self.var_len:
+            off, base = self.var_len
+            w0 = self.wires[0]
+            sizes = w0[:, off:off + 4].contiguous().view(torch.int32).to(torch.int64) + base
+            total += int(((sizes + 15) // 16 * 16).sum().item())
+        return total
 
 
 class AbstractCompressor:
@@ -125,12 +136,19 @@ class ZfpCompressor(AbstractCompressor):
 class LzCompressor(AbstractCompressor):
     """Lossless LZ (sliding-window 32, 2 KiB blocks) on raw 16-/32-bit symbols.
 
-    Each destination slice is compressed on its own.  Wire: a small int32 header with the
-    per-slice byte count, and a payload padded to the largest slice, so the all-to-all moves
-    ``W * max_slice_bytes`` instead of the raw volume.  The padded size needs one host read of
-    the header (the price of a variable-length exchange on a fixed-size collective).
+    Each destination slice is compressed on its own into a self-describing record: a header (block count,
+    block offsets, total code bytes) followed by the packed code.  The wire is ONE byte tensor ``[W, cap]``
+    with ``cap`` the worst-case slice size; it is marked variable-length, so a transport that can read the
+    header on the device (the symmetric-heap all-to-all kernels) moves only ``header + code`` bytes per slice
+    and the host never reads a size.  Every rank therefore offers the same shape to the exchange whatever
+    its data compresses to.
     """
     name, lossless = 'lz', True
+
+    @staticmethod
+    def _layout(raw_bytes, cuda):
+        lib = native.lib()
+        return lib.lz_layout(int(raw_bytes))          # (cap, len_off, header_bytes)
 
     def compress(self, t, world_size=1):
         t = t.contiguous()
@@ -139,21 +157,20 @@ class LzCompressor(AbstractCompressor):
         sym = t.element_size()
         assert sym in (2, 4), "lz codec works on 16- or 32-bit element types"
         raw = t.view(torch.uint8).reshape(W, -1)
-        payload, sizes = native.lib().lz_encode(raw, sym)    # uint8 [W, cap], int32 [W]
-        width = int(sizes.max().item())
-        width = (width + 15) // 16 * 16
-        return Packed([payload[:, :width].contiguous(), sizes.view(W, 1)],
-                      (t.dtype, tuple(t.shape), sym))
+        payload, _sizes = native.lib().lz_encode(raw, sym)    # uint8 [W, cap]; sizes also sit in the headers
+        _cap, len_off, header = self._layout(raw.size(1), t.is_cuda)
+        return Packed([payload], (t.dtype, tuple(t.shape), sym), var_len=(len_off, header))
 
     def decompress(self, packed):
         dtype, shape, sym = packed.meta
-        payload, sizes = packed.wires
+        payload = packed.wires[0]
         W = payload.size(0)
         numel = 1
         for s in shape:
             numel *= s
         raw_bytes = numel * sym // W
-        out = native.lib().lz_decode(payload, sizes.view(-1), raw_bytes, sym)   # uint8 [W, raw]
+        sizes = torch.empty(0, dtype=torch.int32, device=payload.device)
+        out = native.lib().lz_decode(payload.contiguous(), sizes, raw_bytes, sym)   # uint8 [W, raw]
         return out.view(dtype).view(shape)
 
 

@@ -53,6 +53,27 @@ class AbstractComm:
     def all_to_all(self, t):
         raise NotImplementedError
 
+    def all_to_all_var(self, t, len_off, len_base):
+        """All-to-all of self-describing slices: ``t`` is ``[W, cap]`` bytes and the u32 at byte ``len_off`` of
+        every slice holds how many bytes follow its ``len_base`` bytes of header.  Returns ``[W, width]`` with
+        ``width <= cap``; bytes past a slice's own length are undefined.
+
+        On the symmetric-heap transport the kernels read the sizes on the device and move only the valid
+        prefix of each slice (no host synchronisation, so the call can be captured in a CUDA graph).  The
+        library collectives behind the CPU / NCCL transports need one width for all ranks: the ranks agree on
+        the maximum with one all-reduce and a host read."""
+        t = t.contiguous()
+        if self.world_size == 1 or C.TUTEL_SKIP_A2A:
+            return t
+        algo = getattr(self, 'algo', None)
+        if algo is not None and self._use_transport(t):
+            return self._transport().all_to_all(t, algo=algo, var_len=(len_off, len_base))
+        sizes = t[:, len_off:len_off + 4].contiguous().view(torch.int32).view(-1).to(torch.int64) + len_base
+        width = sizes.max().reshape(1)
+        dist.all_reduce(width, op=dist.ReduceOp.MAX, group=self.group)
+        width = min((int(width.item()) + 15) // 16 * 16, t.size(1))
+        return self.all_to_all(t[:, :width].contiguous())
+
     # -- helpers ------------------------------------------------------------------------
     def _use_transport(self, t):
         return t.is_cuda and self.world_size > 1
@@ -69,7 +90,7 @@ def _gloo_a2a(t, group):
 
 
 class NaiveComm(AbstractComm):
-    name = 'naive'
+    name, algo = 'naive', 'flat'
 
     def all_to_all(self, t):
         if self.world_size == 1 or C.TUTEL_SKIP_A2A:
@@ -93,7 +114,7 @@ class NcclComm(AbstractComm):
 class PipeComm(AbstractComm):
     """Pipe-A2A: peers inside my group and peers outside it are served by two independent
     channels that run concurrently."""
-    name = 'pipe'
+    name, algo = 'pipe', 'pipe'
 
     def all_to_all(self, t):
         if self.world_size == 1 or C.TUTEL_SKIP_A2A:
@@ -129,7 +150,7 @@ def _subgroups(L):
 class DdComm(AbstractComm):
     """2DH: phase 1 exchanges inside the group so that every rank holds what its group sends
     to its own local index everywhere; phase 2 exchanges between groups."""
-    name = 'dd'
+    name, algo = 'dd', 'dd'
 
     def all_to_all(self, t):
         W, L = self.world_size, self.local_size
@@ -155,7 +176,7 @@ class HeTuComm(AbstractComm):
     """Hierarchical leader algorithm: gather -> transform -> leaders' exchange -> transform
     -> scatter.  Works for any dtype and rank of tensor (the reference's scratch sizing only
     fits 2-D fp32)."""
-    name = 'hetu'
+    name, algo = 'hetu', 'hetu'
 
     def all_to_all(self, t):
         W, L = self.world_size, self.local_size

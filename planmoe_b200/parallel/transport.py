@@ -139,11 +139,14 @@ class Transport:
                 self.rank, STATUS_NAMES.get(st[0], 'error %d' % st[0]), st[1:4]))
 
     # -- collectives --------------------------------------------------------------------------
-    def all_to_all(self, t, algo='flat'):
+    def all_to_all(self, t, algo='flat', var_len=None, heap_out=False):
+        """``var_len=(len_off, len_base)``: slices are self-describing and only their valid prefix moves;
+        ``heap_out=True``: return a view of the receive buffer in the heap instead of a copy (valid across one
+        further call of the same algorithm, see ``parallel/a2a.py``)."""
         from . import a2a
         if self._a2a is None:
             self._a2a = a2a.A2AChannel(self)
-        return self._a2a.run(t, algo)
+        return self._a2a.run(t, algo, var_len=var_len, heap_out=heap_out)
 
     def close(self):
         for seg in self.segments:
@@ -190,7 +193,8 @@ def emulated_alloc(ts, nbytes):
 
 def get_transport(group=None):
     is_world = group is None or (dist.is_available() and dist.is_initialized() and group is dist.group.WORLD)
-    key = 0 if is_world else id(group)
+    # keyed by the member ranks, not by the object's id (an id can be reused after a group is collected)
+    key = 0 if is_world else tuple(dist.get_process_group_ranks(group))
     if key not in _TRANSPORTS:
         _TRANSPORTS[key] = Transport(group)
     return _TRANSPORTS[key]

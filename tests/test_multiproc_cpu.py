@@ -17,6 +17,13 @@ def test_ep_layer_chunked_and_int8():
     run_workers('cpu_layer', 2, args=('naive', 'int8', 1))
 
 
+@pytest.mark.parametrize("compress", ['lz', 'zfp'])
+def test_ep_layer_two_ranks_lz_and_zfp(compress):
+    # every rank's data compresses to a different size: the exchange must still agree on one shape
+    run_workers('cpu_layer', 2, args=('naive', compress, 1))
+    run_workers('cpu_layer', 2, args=('naive', compress, 2))
+
+
 def test_net_collectives():
     run_workers('cpu_collectives', 4)
 
