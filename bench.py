@@ -385,11 +385,18 @@ def run(args, world, rank, local_rank):
     if args.stages and args.impl == 'ours':
         # separate, untimed pass with per-stage CUDA events (the timed regions below run without them)
         from planmoe_b200.utils import stage_timer
+        from planmoe_b200.ops import native as _native
         stage_timer.enable(True)
         for _ in range(10):
+            # a delay kernel first: the host enqueues the whole step while the device waits, so the events around
+            # each stage bracket kernels that run back to back (device time, not the host's launch rate)
+            _native.lib().delay(4_000_000)
             step(x_dev)
         barrier()
         print('rank %d stages: %s' % (rank, json.dumps(stage_timer.summary(skip=2))), file=sys.stderr, flush=True)
+        if os.environ.get('PLANMOE_GEMM_TRACE', '0') == '1':
+            from planmoe_b200.ops import fused_moe
+            print('rank %d trace: %s' % (rank, json.dumps(fused_moe.last_trace())), file=sys.stderr, flush=True)
         stage_timer.enable(False)
         stage_timer.reset()
     if args.impl == 'ours':

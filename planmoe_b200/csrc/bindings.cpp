@@ -179,6 +179,31 @@ std::vector<Tensor> dispatch_gate_grad_scaled_op(const Tensor& disp, const Tenso
   return {out, scaled};
 }
 
+// The same for expert outputs that arrived as uint8 rows with a (scale, low) pair per 128 columns and row (the int8
+// push epilogue's layout): `disp_ptr` uint8 [E * C, M], `scales_ptr` fp32 [M / 128][group_rows][2].  `gates` may be
+// absent (then no scaled copies are produced and the second result is empty).
+std::vector<Tensor> dispatch_gate_grad_q8_op(int64_t disp_ptr, int64_t scales_ptr, int64_t group_rows, const Tensor& dy,
+                                             const Tensor& idx, const Tensor& loc, const c10::optional<Tensor>& gates,
+                                             int64_t C, bool want_scaled) {
+  count_launch(1);
+  TORCH_CHECK(dy.is_cuda() && dy.is_contiguous() && dy.dim() == 2 && dy.size(1) % 128 == 0);
+  const int K = idx.size(0), S = idx.size(1), M = dy.size(1);
+  c10::cuda::CUDAGuard guard(dy.device());
+  Tensor out = torch::empty({K, S}, dy.options().dtype(at::kFloat));
+  Tensor scaled;
+  if (want_scaled) {
+    TORCH_CHECK(gates.has_value() && gates->defined(), "scaled copies need the gates");
+    scaled = torch::empty({(int64_t)S * K, (int64_t)M}, dy.options());
+  }
+  DISPATCH_FLOAT(dy, "dispatch_gate_grad_q8", [&] {
+    launch_gate_grad<scalar_t>(reinterpret_cast<const scalar_t*>(disp_ptr), reinterpret_cast<const scalar_t*>(dy.data_ptr()),
+                               idx.data_ptr<int>(), loc.data_ptr<int>(), out.data_ptr<float>(), opt_f32(gates),
+                               want_scaled ? reinterpret_cast<scalar_t*>(scaled.data_ptr()) : nullptr, K, S, M, C,
+                               cur_stream(), reinterpret_cast<const float*>(scales_ptr), group_rows);
+  });
+  return {out, want_scaled ? scaled : Tensor()};
+}
+
 // ---- fused gate -------------------------------------------------------------------------------
 // returns (idx[K,S] i32, loc[K,S] i32, gates[K,S] f32, slot_map[E*C] i32, top1_count[E] i32, l_aux[1] f32)
 std::vector<Tensor> gate_forward_op(const Tensor& logits, int64_t K, int64_t C, bool normalize) {
@@ -271,15 +296,19 @@ struct GemmOpts {
   c10::optional<Tensor> bias, aux, out;
   // flag gate
   int64_t gate_flags_ptr = 0, gate_rows = 0, gate_want = 0, gate_want_ptr = 0;
+  int64_t gate_mode = 0, gate_nblk = 0, perm_w = 0, perm_seg_rows = 0;
   // push
   int64_t heap_bases_ptr = 0, push_data_off = 0, push_flag_off = 0, push_rows = 0, push_C = 0, push_c0 = 0,
-          push_chunk = 0, W = 1, my_rank = 0, chunk_groups = 0;
+          push_chunk = 0, W = 1, my_rank = 0, chunk_groups = 0, push_q8 = 0, push_scale_off = 0;
   int64_t budget_ms = 0, status_ptr = 0, max_ctas = 0, cta_group = 0;
   std::vector<int64_t> heap_bases_host;      // peers' mapped base addresses (push epilogue with bulk stores)
   // dispatch send fused into the launch (copy role)
   c10::optional<Tensor> copy_x, copy_slot_map, copy_gates;
   int64_t copy_K = 0, copy_E_local = 0, copy_C = 0, copy_chunks = 0, copy_ctas = 0, copy_data_off = 0,
-          copy_flag_off = 0;
+          copy_flag_off = 0, copy_nblk = 0;
+  // de-quantiser role (int8 wire): local landing buffer, arrival flags (set by peers), ready flags (set by the role)
+  int64_t dq_ptr = 0, dq_arrival_ptr = 0, dq_ready_ptr = 0;
+  int64_t trace_ptr = 0;                     // optional u64 [grid][8] role trace (see GemmArgs::trace)
 };
 
 GemmOperand operand_of(const Tensor& t, bool mn_major) {
@@ -341,14 +370,17 @@ Tensor grouped_gemm_op(const Tensor& A, bool a_mn, const Tensor& B, bool b_mn, c
   g.gate_flags = reinterpret_cast<const unsigned long long*>(o.gate_flags_ptr);
   g.gate_rows = o.gate_rows; g.gate_want = o.gate_want;
   g.gate_want_ptr = reinterpret_cast<const unsigned long long*>(o.gate_want_ptr);
+  g.gate_mode = o.gate_mode; g.gate_nblk = o.gate_nblk; g.perm_w = o.perm_w; g.perm_seg_rows = o.perm_seg_rows;
   g.heap_bases = reinterpret_cast<const unsigned long long*>(o.heap_bases_ptr);
   g.push_data_off = o.push_data_off; g.push_flag_off = o.push_flag_off; g.push_rows = o.push_rows;
   g.push_C = o.push_C; g.push_c0 = o.push_c0; g.push_chunk = o.push_chunk; g.W = o.W; g.my_rank = o.my_rank;
   g.chunk_groups = o.chunk_groups;
+  g.push_q8 = o.push_q8; g.push_scale_off = o.push_scale_off;
   std::vector<unsigned long long> bases_host(o.heap_bases_host.begin(), o.heap_bases_host.end());
   if (!bases_host.empty() && (int64_t)bases_host.size() == o.W) g.heap_bases_host = bases_host.data();
   g.budget_ns = (unsigned long long)o.budget_ms * 1000000ull;
   g.status = reinterpret_cast<int*>(o.status_ptr);
+  g.trace = reinterpret_cast<unsigned long long*>(o.trace_ptr);
   g.max_ctas = o.max_ctas;
   g.cta_group = o.cta_group;
   if (o.epilogue == kEpiPush) TORCH_CHECK(g.heap_bases != nullptr, "push epilogue needs heap bases");
@@ -356,8 +388,8 @@ Tensor grouped_gemm_op(const Tensor& A, bool a_mn, const Tensor& B, bool b_mn, c
     TORCH_CHECK(o.copy_x.has_value() && o.copy_slot_map.has_value(), "copy role needs x and slot_map");
     const Tensor& cx = *o.copy_x;
     const Tensor& sm = *o.copy_slot_map;
-    TORCH_CHECK(cx.is_cuda() && cx.scalar_type() == at::kBFloat16 && cx.dim() == 2 && cx.is_contiguous(),
-                "copy role: x must be contiguous bf16 [S, M]");
+    TORCH_CHECK(cx.is_cuda() && (cx.scalar_type() == at::kBFloat16 || cx.scalar_type() == at::kByte) && cx.dim() == 2 &&
+                cx.is_contiguous(), "copy role: x must be contiguous rows, bf16 [S, M] or uint8 [S, M + 16]");
     TORCH_CHECK(sm.is_cuda() && sm.scalar_type() == at::kInt && sm.is_contiguous(), "copy role: slot_map must be int32");
     TORCH_CHECK(g.heap_bases != nullptr && o.copy_K > 0 && o.copy_E_local > 0 && o.copy_C > 0 && o.copy_chunks > 0,
                 "copy role: incomplete geometry");
@@ -372,6 +404,13 @@ Tensor grouped_gemm_op(const Tensor& A, bool a_mn, const Tensor& B, bool b_mn, c
     }
     g.copy.K = o.copy_K; g.copy.E_local = o.copy_E_local; g.copy.C = o.copy_C; g.copy.chunks = o.copy_chunks;
     g.copy.ctas = o.copy_ctas; g.copy.data_off = o.copy_data_off; g.copy.flag_off = o.copy_flag_off;
+    g.copy.nblk = o.copy_nblk; g.copy.row_bytes = (int)(cx.size(1) * cx.element_size());
+  }
+  if (o.dq_ptr != 0) {
+    g.dequant.q = reinterpret_cast<const void*>(o.dq_ptr);
+    g.dequant.arrival = reinterpret_cast<const unsigned long long*>(o.dq_arrival_ptr);
+    g.dequant.ready = reinterpret_cast<unsigned long long*>(o.dq_ready_ptr);
+    g.dequant.M = g.K;
   }
   check_cuda(launch_grouped_gemm(g, cur_stream()), "grouped_gemm");
   return out;
@@ -398,6 +437,21 @@ Tensor colsum_op(const Tensor& x, int64_t fold, bool as_bf16) {
   return buf.narrow(0, 0, out_groups * N).view({out_groups, (int64_t)N});
 }
 
+// rows [R, M] -> uint8 [R, M + 16]: M quantised bytes + {scale, low, 0, 0} (the wire rows of the fused send)
+Tensor int8_rows_encode_op(const Tensor& x) {
+  count_launch(1);
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.is_contiguous() && x.size(1) % 16 == 0,
+              "int8_rows_encode: contiguous CUDA [R, M] with M % 16 == 0");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int R = x.size(0), M = x.size(1);
+  Tensor out = torch::empty({(int64_t)R, (int64_t)M + 16}, x.options().dtype(at::kByte));
+  DISPATCH_FLOAT(x, "int8_rows_encode", [&] {
+    launch_int8_rows_encode<scalar_t>(reinterpret_cast<const scalar_t*>(x.data_ptr()), out.data_ptr<uint8_t>(), R, M,
+                                      cur_stream());
+  });
+  return out;
+}
+
 // ---- push / wait wrappers for the fused MoE path ------------------------------------------------
 void scatter_push_op(const Tensor& x, const Tensor& slot_map, const c10::optional<Tensor>& gates, int64_t K, int64_t E,
                      int64_t C, int64_t heap_bases_ptr, int64_t data_off, int64_t flag_off, int64_t W, int64_t my_rank,
@@ -420,7 +474,8 @@ void scatter_push_op(const Tensor& x, const Tensor& slot_map, const c10::optiona
 
 Tensor gather_wait_op(int64_t disp_ptr, at::ScalarType dtype, int64_t M, const Tensor& idx, const Tensor& loc,
                       const c10::optional<Tensor>& gates, int64_t C, int64_t flags_ptr, int64_t n_flags, int64_t want,
-                      int64_t budget_ms, int64_t status_ptr, int64_t want_ptr) {
+                      int64_t budget_ms, int64_t status_ptr, int64_t want_ptr, int64_t q8_scales_ptr,
+                      int64_t q8_group_rows) {
   count_launch(1);
   c10::cuda::CUDAGuard guard(idx.device());
   const int K = idx.size(0), S = idx.size(1);
@@ -431,9 +486,10 @@ Tensor gather_wait_op(int64_t disp_ptr, at::ScalarType dtype, int64_t M, const T
   wa.want_ptr = reinterpret_cast<const unsigned long long*>(want_ptr);
   wa.status = reinterpret_cast<int*>(status_ptr);
   DISPATCH_FLOAT(out, "gather_wait", [&] {
-    launch_gather_rows<scalar_t>(reinterpret_cast<const void*>(disp_ptr), nullptr, idx.data_ptr<int>(),
-                                 loc.data_ptr<int>(), opt_f32(gates), reinterpret_cast<scalar_t*>(out.data_ptr()), K, S,
-                                 M, C, flags_ptr ? &wa : nullptr, cur_stream());
+    launch_gather_rows<scalar_t>(reinterpret_cast<const void*>(disp_ptr), reinterpret_cast<const float*>(q8_scales_ptr),
+                                 idx.data_ptr<int>(), loc.data_ptr<int>(), opt_f32(gates),
+                                 reinterpret_cast<scalar_t*>(out.data_ptr()), K, S, M, C, flags_ptr ? &wa : nullptr,
+                                 cur_stream(), q8_scales_ptr ? q8_group_rows : 0);
   });
   return out;
 }
@@ -578,16 +634,18 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("dispatch_gather", &dispatch_gather_op);
   m.def("dispatch_gate_grad", &dispatch_gate_grad_op);
   m.def("dispatch_gate_grad_scaled", &dispatch_gate_grad_scaled_op);
+  m.def("dispatch_gate_grad_q8", &dispatch_gate_grad_q8_op);
   m.def("gate_forward", &gate_forward_op);
   m.def("gate_backward", &gate_backward_op);
   m.def("cumsum_sub_one", &cumsum_sub_one_op);
   m.def("int8_encode", &int8_encode_op);
   m.def("int8_decode", &int8_decode_op);
+  m.def("int8_rows_encode", &int8_rows_encode_op);
   m.def("colsum", &colsum_op, py::arg("x"), py::arg("fold") = 1, py::arg("as_bf16") = false);
   m.def("scatter_push", &scatter_push_op);
   m.def("gather_wait", &gather_wait_op, py::arg("disp_ptr"), py::arg("dtype"), py::arg("M"), py::arg("idx"), py::arg("loc"),
         py::arg("gates"), py::arg("C"), py::arg("flags_ptr"), py::arg("n_flags"), py::arg("want"), py::arg("budget_ms"),
-        py::arg("status_ptr"), py::arg("want_ptr") = 0);
+        py::arg("status_ptr"), py::arg("want_ptr") = 0, py::arg("q8_scales_ptr") = 0, py::arg("q8_group_rows") = 0);
   m.def("zfp_encode", &zfp_encode_op);
   m.def("zfp_decode", &zfp_decode_op);
   m.def("lz_encode", &lz_encode_op);
@@ -621,6 +679,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_readwrite("gate_rows", &GemmOpts::gate_rows)
       .def_readwrite("gate_want", &GemmOpts::gate_want)
       .def_readwrite("gate_want_ptr", &GemmOpts::gate_want_ptr)
+      .def_readwrite("gate_mode", &GemmOpts::gate_mode)
+      .def_readwrite("gate_nblk", &GemmOpts::gate_nblk)
+      .def_readwrite("perm_w", &GemmOpts::perm_w)
+      .def_readwrite("perm_seg_rows", &GemmOpts::perm_seg_rows)
+      .def_readwrite("copy_nblk", &GemmOpts::copy_nblk)
+      .def_readwrite("trace_ptr", &GemmOpts::trace_ptr)
+      .def_readwrite("dq_ptr", &GemmOpts::dq_ptr)
+      .def_readwrite("dq_arrival_ptr", &GemmOpts::dq_arrival_ptr)
+      .def_readwrite("dq_ready_ptr", &GemmOpts::dq_ready_ptr)
       .def_readwrite("heap_bases_ptr", &GemmOpts::heap_bases_ptr)
       .def_readwrite("push_data_off", &GemmOpts::push_data_off)
       .def_readwrite("push_flag_off", &GemmOpts::push_flag_off)
@@ -628,6 +695,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_readwrite("push_C", &GemmOpts::push_C)
       .def_readwrite("push_c0", &GemmOpts::push_c0)
       .def_readwrite("push_chunk", &GemmOpts::push_chunk)
+      .def_readwrite("push_q8", &GemmOpts::push_q8)
+      .def_readwrite("push_scale_off", &GemmOpts::push_scale_off)
       .def_readwrite("W", &GemmOpts::W)
       .def_readwrite("my_rank", &GemmOpts::my_rank)
       .def_readwrite("chunk_groups", &GemmOpts::chunk_groups)

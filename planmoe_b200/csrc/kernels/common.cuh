@@ -60,6 +60,13 @@ __device__ __forceinline__ float warp_min(float v) {
 __device__ __forceinline__ void red_release_sys_add(unsigned long long* p, unsigned long long v) {
   asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
+// Flag update without release semantics: for a sender whose data writes have already COMPLETED (bulk async
+// stores after cp.async.bulk.wait_group), so that nothing is left for a release to order.  A release or fence
+// at system scope at this point would wait for every store the SM still has in flight to other GPUs, which
+// serialises a streaming sender on the link's round-trip time.
+__device__ __forceinline__ void red_relaxed_sys_add(unsigned long long* p, unsigned long long v) {
+  asm volatile("red.relaxed.sys.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
 __device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
   unsigned long long v;
   asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");

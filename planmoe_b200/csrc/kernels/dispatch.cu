@@ -206,12 +206,12 @@ struct WaitGeom {
 // MAXK bounds the number of picks per token held in registers: 2 covers top-1 / top-2 gates and keeps
 // the kernel at 32 registers, so that eight CTAs (all 64 warps) fit on an SM and the whole token range
 // is resident in one wave; 8 is the general case.
-template <class T, bool DEQUANT, int MAXK>
+template <class T, int DEQUANT, int MAXK>
 __global__ void __launch_bounds__(kRowThreads, MAXK <= 2 ? 8 : 4)
 gather_rows_kernel(const void* __restrict__ disp_, const float* __restrict__ scale_bias,
                    const int* __restrict__ idx, const int* __restrict__ loc,
                    const float* __restrict__ gates, T* __restrict__ out, int K, int S, int M,
-                   int C, WaitGeom w) {
+                   int C, WaitGeom w, long long group_rows) {
   __shared__ int ok_s;
   if (w.flags != nullptr) {
     if (threadIdx.x == 0) ok_s = 1;
@@ -241,7 +241,34 @@ gather_rows_kernel(const void* __restrict__ disp_, const float* __restrict__ sca
       }
     }
     T* dst = out + (size_t)t * M;
-    if constexpr (!DEQUANT) {
+    if constexpr (DEQUANT == 2) {
+      // uint8 rows, one (scale, low) pair per 128 columns and row, pairs laid out [M / 128][group_rows]
+      const unsigned char* disp = reinterpret_cast<const unsigned char*>(disp_);
+      const float2* sc = reinterpret_cast<const float2*>(scale_bias);
+      for (int v = lane; v < M / 16; v += 32) {
+        float acc[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+#pragma unroll
+        for (int k = 0; k < MAXK; ++k) {
+          if (k < K && slot[k] >= 0) {
+            const float2 sl = sc[(size_t)(v >> 3) * group_rows + slot[k]];
+            const float a = sl.x * gw[k], b = sl.y * gw[k];
+            uint4 raw = *reinterpret_cast<const uint4*>(disp + slot[k] * M + (size_t)v * 16);
+            const unsigned char* q = reinterpret_cast<const unsigned char*>(&raw);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) acc[i] += fmaf(a, (float)q[i], b);
+          }
+        }
+#pragma unroll
+        for (int h = 0; h < 16 / V; ++h) {
+          Pack<T> o;
+#pragma unroll
+          for (int i = 0; i < V; ++i) o.v[i] = from_f32<T>(acc[h * V + i]);
+          st16(dst + (size_t)v * 16 + h * V, o);
+        }
+      }
+    } else if constexpr (DEQUANT == 0) {
       const T* disp = reinterpret_cast<const T*>(disp_);
       for (int v = lane; v < nvec; v += 32) {
         float acc[V];
@@ -299,7 +326,7 @@ gather_rows_kernel(const void* __restrict__ disp_, const float* __restrict__ sca
 template <class T>
 void launch_gather_rows(const void* disp, const float* scale_bias, const int* idx, const int* loc,
                         const float* gates, T* out, int K, int S, int M, int C,
-                        const WaitArgs* wait, cudaStream_t stream) {
+                        const WaitArgs* wait, cudaStream_t stream, long long group_rows) {
   WaitGeom w{};
   if (wait != nullptr) {
     w.flags = wait->flags; w.n_flags = wait->n_flags; w.want = wait->want; w.want_ptr = wait->want_ptr;
@@ -308,12 +335,14 @@ void launch_gather_rows(const void* disp, const float* scale_bias, const int* id
   int ctas = (S + kRowWarps - 1) / kRowWarps;
   if (ctas > 148 * 8) ctas = 148 * 8;
   if (ctas < 1) ctas = 1;
-  if (scale_bias != nullptr)
-    gather_rows_kernel<T, true, 8><<<ctas, kRowThreads, 0, stream>>>(disp, scale_bias, idx, loc, gates, out, K, S, M, C, w);
+  if (scale_bias != nullptr && group_rows > 0)
+    gather_rows_kernel<T, 2, 8><<<ctas, kRowThreads, 0, stream>>>(disp, scale_bias, idx, loc, gates, out, K, S, M, C, w, group_rows);
+  else if (scale_bias != nullptr)
+    gather_rows_kernel<T, 1, 8><<<ctas, kRowThreads, 0, stream>>>(disp, scale_bias, idx, loc, gates, out, K, S, M, C, w, 0);
   else if (K <= 2)
-    gather_rows_kernel<T, false, 2><<<ctas, kRowThreads, 0, stream>>>(disp, scale_bias, idx, loc, gates, out, K, S, M, C, w);
+    gather_rows_kernel<T, 0, 2><<<ctas, kRowThreads, 0, stream>>>(disp, scale_bias, idx, loc, gates, out, K, S, M, C, w, 0);
   else
-    gather_rows_kernel<T, false, 8><<<ctas, kRowThreads, 0, stream>>>(disp, scale_bias, idx, loc, gates, out, K, S, M, C, w);
+    gather_rows_kernel<T, 0, 8><<<ctas, kRowThreads, 0, stream>>>(disp, scale_bias, idx, loc, gates, out, K, S, M, C, w, 0);
 }
 
 // dgates[k][t] = <disp[slot_k(t)], dy[t]>.  With `scaled` != null the same pass also writes the
@@ -323,7 +352,8 @@ template <class T>
 __global__ void __launch_bounds__(kRowThreads, 8)
 gate_grad_kernel(const T* __restrict__ disp, const T* __restrict__ dy, const int* __restrict__ idx,
                  const int* __restrict__ loc, float* __restrict__ dgates, const float* __restrict__ gates,
-                 T* __restrict__ scaled, int K, int S, int M, int C) {
+                 T* __restrict__ scaled, int K, int S, int M, int C, const float* __restrict__ disp_scales,
+                 long long group_rows) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int V = Vec16<T>::N;
   const int nvec = M / V;
@@ -334,7 +364,30 @@ gate_grad_kernel(const T* __restrict__ disp, const T* __restrict__ dy, const int
       float acc = 0.f;
       if (e >= 0 && l >= 0 && l < C) {
         const T* a = disp + ((size_t)e * C + l) * M;
-        if (scaled != nullptr) {
+        if (disp_scales != nullptr) {
+          // the expert outputs arrived as uint8 rows with a (scale, low) pair per 128 columns and row
+          const size_t slot = (size_t)e * C + l;
+          const unsigned char* aq = reinterpret_cast<const unsigned char*>(disp) + slot * M;
+          const float2* sc = reinterpret_cast<const float2*>(disp_scales);
+          const float gw = gates != nullptr ? gates[(size_t)k * S + t] : 1.f;
+          T* o = scaled != nullptr ? scaled + ((size_t)t * K + k) * M : nullptr;
+          for (int v = lane; v < M / 16; v += 32) {
+            const float2 sl = sc[(size_t)(v >> 3) * group_rows + slot];
+            const uint4 raw = *reinterpret_cast<const uint4*>(aq + (size_t)v * 16);
+            const unsigned char* q = reinterpret_cast<const unsigned char*>(&raw);
+#pragma unroll
+            for (int h = 0; h < 16 / V; ++h) {
+              Pack<T> pb = ld16(b + (size_t)v * 16 + h * V), po;
+#pragma unroll
+              for (int i = 0; i < V; ++i) {
+                const float fb = to_f32(pb.v[i]);
+                acc += fmaf(sl.x, (float)q[h * V + i], sl.y) * fb;
+                po.v[i] = from_f32<T>(gw * fb);
+              }
+              if (o != nullptr) st16(o + (size_t)v * 16 + h * V, po);
+            }
+          }
+        } else if (scaled != nullptr) {
           const float gw = gates[(size_t)k * S + t];
           T* o = scaled + ((size_t)t * K + k) * M;
           for (int v = lane; v < nvec; v += 32) {
@@ -363,11 +416,13 @@ gate_grad_kernel(const T* __restrict__ disp, const T* __restrict__ dy, const int
 
 template <class T>
 void launch_gate_grad(const T* disp, const T* dy, const int* idx, const int* loc, float* dgates,
-                      const float* gates, T* scaled, int K, int S, int M, int C, cudaStream_t stream) {
+                      const float* gates, T* scaled, int K, int S, int M, int C, cudaStream_t stream,
+                      const float* disp_scales, long long group_rows) {
   int ctas = (S + kRowWarps - 1) / kRowWarps;
   if (ctas > 148 * 8) ctas = 148 * 8;
   if (ctas < 1) ctas = 1;
-  gate_grad_kernel<T><<<ctas, kRowThreads, 0, stream>>>(disp, dy, idx, loc, dgates, gates, scaled, K, S, M, C);
+  gate_grad_kernel<T><<<ctas, kRowThreads, 0, stream>>>(disp, dy, idx, loc, dgates, gates, scaled, K, S, M, C,
+                                                        disp_scales, group_rows);
 }
 
 #define INSTANTIATE(T)                                                                             \
@@ -375,9 +430,9 @@ void launch_gate_grad(const T* disp, const T* dy, const int* idx, const int* loc
                                        int, const PushArgs*, bool, cudaStream_t);                  \
   template void launch_gather_rows<T>(const void*, const float*, const int*, const int*,           \
                                       const float*, T*, int, int, int, int, const WaitArgs*,       \
-                                      cudaStream_t);                                               \
+                                      cudaStream_t, long long);                                    \
   template void launch_gate_grad<T>(const T*, const T*, const int*, const int*, float*, const float*, \
-                                    T*, int, int, int, int, cudaStream_t);
+                                    T*, int, int, int, int, cudaStream_t, const float*, long long);
 INSTANTIATE(float)
 INSTANTIATE(__nv_bfloat16)
 INSTANTIATE(__half)

@@ -2,12 +2,13 @@
 //
 //   D[g] (M x N) = A[g] (M x K) . B[g] (K x N)          g = 0 .. groups-1, fp32 accumulate
 //
-// Hand-written tcgen05 pipeline, one persistent CTA per SM, 352 threads in four roles.  By default two
+// Hand-written tcgen05 pipeline, one persistent CTA per SM, 384 threads in five roles.  By default two
 // CTAs form a cluster and compute one 256 x 256 tile with tcgen05.mma.cta_group::2 (each CTA stages
 // its own 128 rows of A and 128 of the 256 B columns; the even CTA issues the MMAs for both);
 // problems with at most 128 rows per group run the one-CTA variant (128 x 256 tiles).
 //   warp 0      TMA producer: cp.async.bulk.tensor (4-D maps, 128-byte swizzle) into a 5-stage
-//               shared-memory ring (3-stage in the one-CTA variant), completion on the mbarrier of
+//               shared-memory ring (3-stage in the one-CTA variant; one stage less in launches that
+//               carry a dispatch send, whose copy slots take the room), completion on the mbarrier of
 //               the MMA-issuing CTA.  When the A operand is a receive buffer that peer GPUs fill,
 //               the producer first acquire-waits (bounded) on the flag of every source rank whose
 //               rows the tile touches: the GEMM starts on a tile as soon as its rows have landed
@@ -25,13 +26,17 @@
 //   warp 10     dispatch send (optional): while the tensor cores work, this warp of every CTA moves
 //               token rows into the receive buffers of the ranks that own the experts with the
 //               bulk-copy engine: cp.async.bulk global -> shared (row picked by slot map), an
-//               optional gate scaling in shared memory, cp.async.bulk shared -> peer global; seven
-//               4 KiB slots are in flight per CTA, one per lane.  Chunks leave in order; after a
-//               chunk its stores are awaited and the (chunk, rank) flags on every destination get
-//               a release-add.  The producers of the same launch on every rank are the flag-gated
-//               consumers, so the all-to-all and the GEMM that follows it are one kernel and
-//               overlap tile by tile; the copy never waits on another CTA or rank, so no circular
-//               wait can form.
+//               optional int8 row quantisation in shared memory, cp.async.bulk shared -> peer
+//               global; 64 KiB of slots are in flight per CTA, one slot per lane.  Work items are 16
+//               rows for one destination, ordered the way the receivers consume them; when the stores
+//               of an item have completed, the flag of the 128-row block they belong to on the
+//               destination gets a release-add of the row count.  The producers of the same launch on
+//               every rank are the flag-gated consumers, so the all-to-all and the GEMM that follows
+//               it are one kernel and overlap 128 rows at a time; the copy never waits on another CTA
+//               or rank, so no circular wait can form.
+//   warp 11     de-quantiser (int8 wire only): waits for the arrival flag of a 128-row block of int8
+//               rows in this rank's landing buffer, expands 32 rows at a time to the bf16 A operand
+//               and release-adds the block's "ready" flag, which is what the TMA producer waits for.
 //
 // Operands may be K-major or MN-major (weights are stored input-major, and the weight-gradient
 // GEMMs contract over the token dimension), so all four FFN GEMM flavours — forward, dgrad,
@@ -63,10 +68,14 @@ namespace {
 constexpr int BM = 128, BN = 256, BK = 64;       // BM = accumulator rows per CTA (TMEM lanes)
 constexpr int UMMA_K = 16;
 constexpr int kAccStages = 2;
-constexpr int kThreads = 352;                     // TMA, MMA, 8 epilogue warps, copy warp
-constexpr uint32_t kCopySlot = 4096;              // bytes per bulk-copy slot (one bf16 row of 2048, or a piece of a longer row)
-constexpr int kCopyLanes = 7;                     // data slots = lanes of the copy warp that drive the bulk-copy engine
-constexpr uint32_t kSmemCopy = (kCopyLanes + 1) * kCopySlot;   // + one slot of zeros for empty expert slots
+constexpr int kThreads = 384;                     // TMA, MMA, 8 epilogue warps, copy warp, de-quantiser warp
+constexpr uint32_t kCopyBytes = 65536;            // bulk-copy slots of the dispatch send: 16 x 4 KiB, 8 x 8 KiB or 4 x 16 KiB
+constexpr uint32_t kCopyMinSlot = 4096, kCopyMaxSlot = 16384;
+constexpr int kCopyMaxLanes = (int)(kCopyBytes / kCopyMinSlot);
+constexpr uint32_t kZeroBytes = 1024;             // zeros, the source of rows for empty expert slots
+constexpr uint32_t kSmemCopy = kCopyBytes + kZeroBytes;
+constexpr int kGateBlock = 128;                   // rows per arrival flag of a flag-gated A operand (mode 1)
+constexpr int kDequantRows = 32;                  // rows a de-quantiser warp expands per work unit
 constexpr int kEpiWarps = 8;
 constexpr uint32_t kABytes = BM * BK * 2;          // 16 KiB
 constexpr uint32_t kStagingPerWarp = 32 * 128;     // one 32-row x 128-byte tile
@@ -79,16 +88,20 @@ constexpr uint32_t kSmemBars = 512;
 // tile with one tcgen05.mma.cta_group::2 stream issued by the even CTA; each CTA stages its own 128
 // rows of A and its own 128 of the 256 B columns (16 KiB each), so a K step costs 32 KiB of shared
 // memory traffic per CTA instead of 48 and the ring is 5 deep instead of 3.
-template <int CG> struct Geo {
+template <int CG, bool COPY> struct Geo {
   static constexpr int kBRows = BN / CG;                        // B columns staged per CTA
   static constexpr uint32_t kBBytes = kBRows * BK * 2;
   static constexpr uint32_t kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = CG == 1 ? 3 : 5;
+  static constexpr int kStages = (CG == 1 ? 3 : 5) - (COPY ? 1 : 0);
   static constexpr uint32_t kSmemRing = kStages * kStageBytes;
-  // ring | epilogue staging | bulk-copy slots of the dispatch send | bias | barriers.
+  static constexpr uint32_t kCopyArea = COPY ? kSmemCopy : 0;
+  // per epilogue warp 32 (scale, low) pairs of the int8 push epilogue (launches without a dispatch send only)
+  static constexpr uint32_t kScaleArea = COPY ? 0 : kEpiWarps * 256;
+  // ring | epilogue staging | bulk-copy slots of the dispatch send | bias | int8 scales | barriers.
   // No alignment slack: the dynamic shared array is declared 1024-byte aligned.
-  static constexpr uint32_t kSmemTotal = kSmemRing + kSmemStaging + kSmemCopy + kSmemBias + kSmemBars;
+  static constexpr uint32_t kSmemTotal = kSmemRing + kSmemStaging + kCopyArea + kSmemBias + kScaleArea + kSmemBars;
 };
+static_assert(Geo<2, true>::kSmemTotal <= 232448 && Geo<1, true>::kSmemTotal <= 232448, "shared memory budget");
 constexpr int kMaxStages = 6;
 constexpr uint32_t kTmemCols = 512;
 
@@ -228,14 +241,22 @@ struct KernelParams {
   const __nv_bfloat16* bias; long long bias_group_stride;
   const unsigned long long* gate_flags; int gate_rows; unsigned long long gate_want;
   const unsigned long long* gate_want_ptr;
+  int gate_mode, gate_nblk, perm_w, perm_q;
+  const void* a_ptr; long long a_row_stride, a_group_stride;   // the A operand as plain memory (de-quantiser output)
   const unsigned long long* heap_bases; unsigned long long push_data_off, push_flag_off;
   int push_rows, push_C, push_c0, push_chunk, W, my_rank;
+  int push_q8;                   // push epilogue writes uint8 rows + one (scale, low) pair per 128 columns and row
+  unsigned long long push_scale_off;   // heap offset of the pairs, fp32 [N / 128][rows of the destination buffer][2]
+  long long push_rows_total;     // rows of the destination buffer (W * experts * push_C)
   // chunk_groups > 0: groups are [chunk][expert] with chunk_groups experts; weights / bias are indexed
   // by the expert, flags and push offsets by the chunk.
   int chunk_groups;
   unsigned long long budget_ns; int* status;
   GemmArgs::CopyJob copy;        // copy.ctas > 0: the copy warp of every CTA runs the dispatch send
+  GemmArgs::DequantJob dequant;  // dequant.q != null: the de-quantiser warp of every CTA expands int8 rows
   int tma_out;                   // epilogue writes its staging tiles with bulk tensor stores (OutMaps valid)
+  unsigned long long* trace;     // optional [grid][8] ns timestamps / durations of the roles (see GemmArgs::trace)
+  int copy_dbg;                  // experiment switches of the copy role (PLANMOE_COPY_DBG)
 };
 
 // Tensor maps of the outputs, for the bulk tensor stores of the epilogue (box = 64 columns x 32 rows,
@@ -255,7 +276,7 @@ struct Ctl {
   uint64_t empty[kMaxStages];
   uint64_t acc_full[kAccStages];
   uint64_t acc_empty[kAccStages];
-  uint64_t copy_full[kCopyLanes];   // a row has landed in bulk-copy slot i
+  uint64_t copy_full[kCopyMaxLanes];   // a row has landed in bulk-copy slot i
   uint32_t tmem_base;
   volatile int abort;
   volatile int epi_abort[2];   // written by epilogue warps before a barrier, read after it
@@ -332,116 +353,263 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 }
 
 // ---------------------------------------------------------------------------------------------
+// Tile order.  A tile index runs over (group, m-tile, n-tile) with the n-tile fastest.  When the A operand
+// is filled by the fused dispatch send and every source rank's segment of a group holds perm_q > 1 tiles,
+// the m-tiles are visited segment-interleaved (tile 0 of every source, then tile 1 of every source, ...):
+// that is the order in which the senders deliver rows, so the tensor cores are never parked on a segment
+// whose rows leave last.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ int permute_mt(const KernelParams& p, int mt_lin) {
+  if (p.perm_q <= 1) return mt_lin;
+  return (mt_lin % p.perm_w) * p.perm_q + mt_lin / p.perm_w;
+}
+
+__device__ __forceinline__ void red_release_gpu_add(unsigned long long* p, unsigned long long v) {
+  asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+
+// ---------------------------------------------------------------------------------------------
 // Copy role (warp 10 of every CTA): the dispatch send, driven by the bulk-copy engine.
 //
-// A unit is one token row (or a 4 KiB piece of a longer row) for one destination.  The CTA owns the
-// rows blockIdx.x, blockIdx.x + gridDim.x, ... of every (chunk, destination).  Units are handled in
-// batches of seven, one per lane: the lane looks up the slot map, starts a bulk load of the token row
-// into its shared-memory slot (or, for an empty expert slot, a bulk store of the zero slot), waits
-// (bounded) for the row, the warp scales gate-weighted rows in shared memory, and the lane starts the
-// bulk store into the receive buffer [chunk][E_local][W_src][C/chunks][M] of the destination rank.
-// After a chunk every lane waits for its stores to complete, then the warp fences and adds one
-// arrival to the (chunk, my_rank) flag of every destination: one arrival per CTA of the grid.
+// The 64 KiB copy area is cut into slots of one row each (16 slots for rows of up to 4 KiB, 8 for 8 KiB,
+// 4 for 16 KiB), one lane per slot, in two sets that alternate from item to item.  A work item is `half`
+// consecutive rows of one (chunk, local expert) group for one destination rank, i.e. one contiguous range of
+// the destination's receive buffer [chunk][E_local][W_src][C/chunks][row]; item ids are ordered (group, row
+// range, destination), the order in which the destinations consume rows, and CTA b takes items b, b + grid, ...
+//
+// The loop is software-pipelined so that no step waits for something it has just started:
+//   iteration k   (1) the rows of item k, whose bulk loads were started one iteration ago, have landed in set
+//                     k & 1: start their bulk stores into the peer's buffer (an empty expert slot is stored as
+//                     zeros from a zero region instead) and commit them;
+//                 (2) the stores of item k-1 have read the other set: look up the rows of item k+1 in the slot
+//                     map and start their bulk loads into it;
+//                 (3) the stores of item k-1 have completed: lane 31, which never issues a copy, adds the
+//                     item's row count to the flag of the 128-row block it lies in on its destination (a
+//                     relaxed add: the data it publishes has already been performed).
+// Rows are moved as they are: int8 rows are quantised by the caller beforehand.  Nothing here waits on another
+// CTA or rank.
 // ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void bulk_wait_group_1() { asm volatile("cp.async.bulk.wait_group 1;" ::: "memory"); }
+
 __device__ __forceinline__ void copy_role(const KernelParams& p, uint8_t* cring, Ctl* ctl) {
   const GemmArgs::CopyJob& c = p.copy;
   const int lane = threadIdx.x & 31;
   const int Cc = c.C / c.chunks;
-  const int rows = c.E_local * Cc;                               // rows per (chunk, destination)
-  const uint32_t row_bytes = (uint32_t)c.M * 2u;
-  const int pieces = (int)((row_bytes + kCopySlot - 1) / kCopySlot);
-  const int my_rows = ((int)blockIdx.x < rows) ? (rows - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
-  const int units = p.W * my_rows * pieces;                      // per chunk, for this CTA
+  const uint32_t row_bytes = (uint32_t)c.row_bytes;              // the same at the source and at the destination
+  uint32_t slot_bytes = kCopyMinSlot;
+  while (slot_bytes < row_bytes) slot_bytes <<= 1;               // host guarantees row_bytes <= kCopyMaxSlot
+  const int slots = (int)(kCopyBytes / slot_bytes);
+  const int half = slots / 2;                                    // rows per item
+  const int items_per_seg = (Cc + half - 1) / half;
+  const long long n_items = (long long)c.chunks * c.E_local * items_per_seg * p.W;
   const uint8_t* x = reinterpret_cast<const uint8_t*>(c.x);
-  uint8_t* my_slot = cring + lane * kCopySlot;
-  const uint32_t my_slot_s = smem_u32(my_slot);
-  const uint32_t zero_s = smem_u32(cring + kCopyLanes * kCopySlot);
-  const uint32_t my_bar = smem_u32(&ctl->copy_full[lane < kCopyLanes ? lane : 0]);
+  const uint32_t my_slot_s = smem_u32(cring + (lane < slots ? lane : 0) * slot_bytes);
+  const uint32_t zero_s = smem_u32(cring + kCopyBytes);
+  const uint32_t my_bar = smem_u32(&ctl->copy_full[lane < slots ? lane : 0]);
+  const int my_set = lane < slots ? lane / half : -1;
+  const int li = lane < slots ? lane - my_set * half : 0;        // my row within an item of my set
   uint32_t phase = 0;                                            // parity of my slot's barrier
   bool ok = true;
 
-  for (uint32_t i = lane; i < kCopySlot / 16; i += 32)
-    reinterpret_cast<uint4*>(cring + kCopyLanes * kCopySlot)[i] = make_uint4(0, 0, 0, 0);
+  for (uint32_t i = lane; i < kZeroBytes / 16; i += 32)
+    reinterpret_cast<uint4*>(cring + kCopyBytes)[i] = make_uint4(0, 0, 0, 0);
   fence_proxy_async();                                           // zeros visible to the bulk-copy engine
   __syncwarp();
 
-  for (int j = 0; j < c.chunks && ok; ++j) {
-    for (int base = 0; base < units; base += kCopyLanes) {
-      const int u = base + lane;
-      const bool mine = lane < kCopyLanes && u < units;
-      bool loaded = false;
-      float gw = 1.f;
-      uint8_t* dst = nullptr;
-      uint32_t bytes = 0;
-      if (mine) {
-        const int piece = u % pieces;
-        const int k = (u / pieces) % my_rows;
-        const int rr = u / (pieces * my_rows);
-        // destinations start at my right-hand neighbour, staggered by CTA so that all links are busy
-        const int r = (p.my_rank + 1 + rr + (int)blockIdx.x) % p.W;
-        const int row = (int)blockIdx.x + k * (int)gridDim.x;
-        const int el = row / Cc, cc = row - el * Cc;
-        const int owner = c.slot_map[(size_t)(r * c.E_local + el) * c.C + j * Cc + cc];
-        bytes = min(kCopySlot, row_bytes - (uint32_t)piece * kCopySlot);
-        dst = reinterpret_cast<uint8_t*>(p.heap_bases[r]) + c.data_off +
-              ((((size_t)j * c.E_local + el) * p.W + p.my_rank) * Cc + cc) * row_bytes + (size_t)piece * kCopySlot;
-        bulk_wait_read_all();                                    // my previous store has left the slot
-        if (owner >= 0) {
-          const int t = owner / c.K, kk = owner - t * c.K;
-          if (c.gates != nullptr) gw = c.gates[(size_t)kk * c.S + t];
-          mbar_expect_tx(my_bar, bytes);
-          bulk_load(my_slot_s, x + (size_t)t * row_bytes + (size_t)piece * kCopySlot, bytes, my_bar);
-          loaded = true;
-        } else {
-          bulk_store(dst, zero_s, bytes);                        // empty expert slot: a row of zeros
-          bulk_commit();
-        }
-      }
-      if (loaded) {
+  // geometry of an item (uniform over the warp)
+  struct Item { int r, g, j, el, row0, nrows; };
+  auto decode = [&](long long item) {
+    Item it;
+    const int rr = (int)(item % p.W);
+    long long t = item / p.W;
+    const int sub = (int)(t % items_per_seg);
+    it.g = (int)(t / items_per_seg);                             // chunk * E_local + local expert
+    it.j = it.g / c.E_local; it.el = it.g - it.j * c.E_local;
+    it.r = (p.my_rank + 1 + rr) % p.W;                           // start at my right-hand neighbour
+    it.row0 = sub * half;
+    it.nrows = min(half, Cc - it.row0);
+    return it;
+  };
+  // my row of the item in flight in my set: where it goes and whether a bulk load is bringing it
+  uint8_t* dst = nullptr;
+  bool have_row = false, loaded = false;
+  auto start_row = [&](const Item& it) {        // called by the lanes of the item's set
+    have_row = li < it.nrows;
+    loaded = false;
+    if (!have_row) return;
+    const int cc = it.row0 + li;
+    const int owner = c.slot_map[(size_t)(it.r * c.E_local + it.el) * c.C + it.j * Cc + cc];
+    dst = reinterpret_cast<uint8_t*>(p.heap_bases[it.r]) + c.data_off +
+          (((size_t)it.g * p.W + p.my_rank) * Cc + cc) * row_bytes;
+    if (owner >= 0) {
+      // source row = token of the pick (gate-weighted sources hold one row per (token, pick): K == 1 then)
+      const int tok = owner / c.K;
+      bulk_wait_read_all();                                      // the store that last used my slot has read it
+      mbar_expect_tx(my_bar, row_bytes);
+      bulk_load(my_slot_s, x + (size_t)tok * row_bytes, row_bytes, my_bar);
+      loaded = true;
+    }
+  };
+
+  // the two items whose stores may still be in flight ([0] = the older one): destination rank, group, first row
+  // in the group, rows
+  int pend_n = 0;
+  int pend_r[2] = {0, 0}, pend_g[2] = {0, 0}, pend_first[2] = {0, 0}, pend_rows[2] = {0, 0};
+  auto signal_oldest = [&]() {
+    // rows [first, first + rows) of group g on rank r have landed
+    unsigned long long* flags = reinterpret_cast<unsigned long long*>(
+        reinterpret_cast<uint8_t*>(p.heap_bases[pend_r[0]]) + c.flag_off) + (size_t)pend_g[0] * c.nblk;
+    // The item's bulk stores have completed (wait_group in the lanes that issued them, then __syncwarp), so the
+    // flag update needs no release of its own; PLANMOE_COPY_DBG=1 restores fence + release for comparison.
+    if (p.copy_dbg & 1) __threadfence_system();
+    int first = pend_first[0], left = pend_rows[0];
+    while (left > 0) {
+      const int blk = first / kGateBlock;
+      const int n = min(left, (blk + 1) * kGateBlock - first);
+      if (p.copy_dbg & 1) red_release_sys_add(flags + blk, (unsigned long long)n);
+      else                red_relaxed_sys_add(flags + blk, (unsigned long long)n);
+      first += n; left -= n;
+    }
+  };
+  auto pop_oldest = [&]() {
+    pend_r[0] = pend_r[1]; pend_g[0] = pend_g[1]; pend_first[0] = pend_first[1]; pend_rows[0] = pend_rows[1];
+    --pend_n;
+  };
+
+  long long item = blockIdx.x;
+  int set = 0;
+  if (item < n_items && my_set == 0) start_row(decode(item));
+  for (; item < n_items && ok; item += gridDim.x, set ^= 1) {
+    const Item it = decode(item);
+    // (1) item `item`: rows have landed (or are zeros) -> stores
+    if (my_set == set) {
+      if (have_row && loaded) {
         ok = mbar_wait(my_bar, phase, ctl, p.budget_ns, p.status, 3, lane);
         phase ^= 1u;
+        if (ok) bulk_store(dst, my_slot_s, row_bytes);
+      } else if (have_row) {
+        for (uint32_t o = 0; o < row_bytes; o += kZeroBytes)     // empty expert slot: a row of zeros
+          bulk_store(dst + o, zero_s, min(kZeroBytes, row_bytes - o));
       }
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      // gate-weighted rows (pre-score dispatch, gate-weighted dY): scale in shared memory, the whole
-      // warp on one slot at a time
-      unsigned scaled = __ballot_sync(0xffffffffu, loaded && gw != 1.f);
-      while (scaled) {
-        const int sl = __ffs(scaled) - 1;
-        scaled &= scaled - 1;
-        const float g = __shfl_sync(0xffffffffu, gw, sl);
-        const uint32_t nb = __shfl_sync(0xffffffffu, bytes, sl);
-        uint4* q = reinterpret_cast<uint4*>(cring + sl * kCopySlot);
-        for (uint32_t i = lane; i < nb / 16; i += 32) {
-          uint4 v = q[i];
-          __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float2 f = __bfloat1622float2(h[e]);
-            h[e] = __floats2bfloat162_rn(f.x * g, f.y * g);
-          }
-          q[i] = v;
-        }
-        fence_proxy_async();                                     // my writes -> the bulk store below
-      }
-      __syncwarp();
-      if (loaded) {
-        bulk_store(dst, my_slot_s, bytes);
-        bulk_commit();
-      }
+      bulk_commit();                 // one group per lane and item of its set, empty if the item has no row for me
     }
-    // chunk j handed to the copy engine everywhere: wait for the stores, then publish it
-    bulk_wait_all();
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) break;
+    // (2) the next item of this CTA goes into the other set
+    if (item + gridDim.x < n_items && my_set == (set ^ 1)) start_row(decode(item + gridDim.x));
+    // (3) the other set's lanes wait for their stores, those of the item before this one, to complete (the loads
+    // of the next item and the stores of this one are in flight meanwhile); this set's lanes keep this item
+    // pending.  The item before is then complete and can be published.
+    if (my_set == set) bulk_wait_group_1(); else bulk_wait_all();
     __syncwarp();
-    if (lane == 0) __threadfence_system();
-    __syncwarp();
-    if (lane < p.W) {
-      unsigned long long* flags = reinterpret_cast<unsigned long long*>(
-          reinterpret_cast<uint8_t*>(p.heap_bases[lane]) + c.flag_off);
-      red_release_sys_add(flags + (size_t)j * p.W + p.my_rank, 1ull);
+    if (pend_n == 1) {
+      if (lane == 31 && !(p.copy_dbg & 2)) signal_oldest();
+      pop_oldest();
+    }
+    pend_r[pend_n] = it.r; pend_g[pend_n] = it.g; pend_first[pend_n] = p.my_rank * Cc + it.row0;
+    pend_rows[pend_n] = it.nrows;
+    ++pend_n;
+  }
+  bulk_wait_all();                                               // nothing of mine is in flight any more
+  __syncwarp();
+  while (ok && pend_n > 0) {
+    if (lane == 31 && !(p.copy_dbg & 2)) signal_oldest();
+    pop_oldest();
+  }
+  if (ok && (p.copy_dbg & 2) && lane == 31) {                    // experiment: all signals at the end
+    for (long long it2 = blockIdx.x; it2 < n_items; it2 += gridDim.x) {
+      const Item q = decode(it2);
+      pend_r[0] = q.r; pend_g[0] = q.g; pend_first[0] = p.my_rank * Cc + q.row0; pend_rows[0] = q.nrows;
+      signal_oldest();
     }
   }
-  bulk_wait_all();                                               // nothing of mine is in flight at teardown
+}
+
+// ---------------------------------------------------------------------------------------------
+// De-quantiser role (warp 11 of every CTA, int8 wire only).  Units of 32 rows, numbered in the order in
+// which the tiles of this launch consume them; CTA b takes units b, b + grid, ...  A unit waits (bounded,
+// lane 0) until the arrival flag of its 128-row block shows that all of the block's rows have landed, the
+// warp expands the rows q * scale + low to bf16 in the A operand, and lane 0 release-adds the unit's row
+// count to the block's ready flag.  The role depends only on peers' copy warps, which never wait.
+// ---------------------------------------------------------------------------------------------
+template <int CG>
+__device__ __forceinline__ void dequant_role(const KernelParams& p, __nv_bfloat16* a_base, long long a_row_stride,
+                                             long long a_group_stride, int mt_count) {
+  const GemmArgs::DequantJob& d = p.dequant;
+  const int lane = threadIdx.x & 31;
+  const unsigned long long uses = p.gate_want_ptr != nullptr ? *p.gate_want_ptr : p.gate_want;
+  constexpr int kUnitsPerBlock = kGateBlock / kDequantRows;
+  const long long n_units = (long long)p.groups * mt_count * CG * kUnitsPerBlock;
+  const size_t q_row = (size_t)d.M + 16;
+  const uint8_t* qbase = reinterpret_cast<const uint8_t*>(d.q);
+  for (long long u = blockIdx.x; u < n_units; u += gridDim.x) {
+    const int sub = (int)(u % kUnitsPerBlock);
+    long long t = u / kUnitsPerBlock;
+    const int b = (int)(t % CG); t /= CG;
+    const int mt = permute_mt(p, (int)(t % mt_count));
+    const int g = (int)(t / mt_count);
+    const int blk = mt * CG + b;
+    const int row0 = blk * kGateBlock + sub * kDequantRows;
+    if (row0 >= p.M) continue;
+    const int rows_blk = min(kGateBlock, p.M - blk * kGateBlock);
+    const int nrows = min(kDequantRows, p.M - row0);
+    bool ok = true;
+    if (lane == 0)
+      ok = wait_flag_ge(d.arrival + (size_t)g * p.gate_nblk + blk, uses * (unsigned long long)rows_blk, p.budget_ns,
+                        p.status, 2000 + blk);
+    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+    if (!ok) return;
+    // Two rows at a time, four 16-byte pieces per lane and row in flight (eight independent loads per lane), so
+    // that the warp streams instead of waiting for one load after the other.
+    const int pieces = d.M / 16;
+    for (int r = 0; r < nrows; r += 2) {
+      const bool two = r + 1 < nrows;
+      const uint8_t* src0 = qbase + ((size_t)g * p.M + row0 + r) * q_row;
+      const uint8_t* src1 = src0 + (two ? q_row : 0);
+      __nv_bfloat16* dst0 = a_base + (long long)g * a_group_stride + (long long)(row0 + r) * a_row_stride;
+      __nv_bfloat16* dst1 = dst0 + (two ? a_row_stride : 0);
+      const float2 sl0 = *reinterpret_cast<const float2*>(src0 + d.M);
+      const float2 sl1 = *reinterpret_cast<const float2*>(src1 + d.M);
+      for (int v0 = 0; v0 < pieces; v0 += 128) {
+        uint4 raw[2][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int v = v0 + i * 32 + lane;
+          if (v < pieces) {
+            raw[0][i] = *reinterpret_cast<const uint4*>(src0 + (size_t)v * 16);
+            raw[1][i] = *reinterpret_cast<const uint4*>(src1 + (size_t)v * 16);
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int v = v0 + i * 32 + lane;
+          if (v >= pieces) continue;
+#pragma unroll
+          for (int rr = 0; rr < 2; ++rr) {
+            if (rr == 1 && !two) continue;
+            const float2 sl = rr == 0 ? sl0 : sl1;
+            const uint32_t w[4] = {raw[rr][i].x, raw[rr][i].y, raw[rr][i].z, raw[rr][i].w};
+            uint32_t o[8];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float f0 = fmaf((float)(w[j] & 0xffu), sl.x, sl.y);
+              const float f1 = fmaf((float)((w[j] >> 8) & 0xffu), sl.x, sl.y);
+              const float f2 = fmaf((float)((w[j] >> 16) & 0xffu), sl.x, sl.y);
+              const float f3 = fmaf((float)(w[j] >> 24), sl.x, sl.y);
+              o[2 * j] = pack_bf16(f0, f1);
+              o[2 * j + 1] = pack_bf16(f2, f3);
+            }
+            __nv_bfloat16* dst = (rr == 0 ? dst0 : dst1) + (size_t)v * 16;
+            reinterpret_cast<uint4*>(dst)[0] = make_uint4(o[0], o[1], o[2], o[3]);
+            reinterpret_cast<uint4*>(dst)[1] = make_uint4(o[4], o[5], o[6], o[7]);
+          }
+        }
+      }
+    }
+    __threadfence();
+    __syncwarp();
+    if (lane == 0) red_release_gpu_add(d.ready + (size_t)g * p.gate_nblk + blk, (unsigned long long)nrows);
+  }
 }
 
 // Bias + activation on one thread's 64 accumulator values: the packed activation goes to `opk`, the
@@ -463,11 +631,11 @@ __device__ __forceinline__ void slab_bias_act(const uint32_t* v, const float* bi
   }
 }
 
-template <int CG, bool A_MN, bool B_MN, int EPI>
+template <int CG, bool A_MN, bool B_MN, int EPI, bool COPY>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ OutMaps om, const KernelParams p) {
-  using G = Geo<CG>;
+  using G = Geo<CG, COPY>;
   constexpr int kStages = G::kStages;
   constexpr uint32_t kStageBytes = G::kStageBytes;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -483,10 +651,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   uint8_t* ring = smem;
   uint8_t* staging = smem + G::kSmemRing;
   uint8_t* cring = smem + G::kSmemRing + kSmemStaging;
-  float* bias_s = reinterpret_cast<float*>(smem + G::kSmemRing + kSmemStaging + kSmemCopy);
-  Ctl* ctl = reinterpret_cast<Ctl*>(smem + G::kSmemRing + kSmemStaging + kSmemCopy + kSmemBias);
+  float* bias_s = reinterpret_cast<float*>(smem + G::kSmemRing + kSmemStaging + G::kCopyArea);
+  uint8_t* scale_s = smem + G::kSmemRing + kSmemStaging + G::kCopyArea + kSmemBias;
+  Ctl* ctl = reinterpret_cast<Ctl*>(smem + G::kSmemRing + kSmemStaging + G::kCopyArea + kSmemBias + G::kScaleArea);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  unsigned long long* trace = p.trace != nullptr ? p.trace + (size_t)blockIdx.x * 8 : nullptr;
+  if (trace != nullptr && threadIdx.x == 0) trace[0] = global_timer_ns();
 
   const int mt_count = (p.M + BM * CG - 1) / (BM * CG);
   const int nt_count = (p.N + BN - 1) / BN;
@@ -500,7 +671,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       mbar_init(smem_u32(&ctl->acc_full[a]), 1);
       mbar_init(smem_u32(&ctl->acc_empty[a]), kEpiWarps * CG);     // the epilogue warps of every CTA of the group
     }
-    for (int i = 0; i < kCopyLanes; ++i) mbar_init(smem_u32(&ctl->copy_full[i]), 1);
+    for (int i = 0; i < kCopyMaxLanes; ++i) mbar_init(smem_u32(&ctl->copy_full[i]), 1);
     ctl->abort = 0;
     ctl->epi_abort[0] = ctl->epi_abort[1] = 0;
     fence_barrier_init();
@@ -520,22 +691,33 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
+      unsigned long long gate_wait_ns = 0;
       const unsigned long long gate_want = p.gate_want_ptr != nullptr ? *p.gate_want_ptr : p.gate_want;
       for (int tile = unit; tile < tiles && ok; tile += nunits) {
         const int nt = tile % nt_count;
-        const int mt = (tile / nt_count) % mt_count;
+        const int mt = permute_mt(p, (tile / nt_count) % mt_count);
         const int g = tile / (nt_count * mt_count);
         const int m0 = mt * (BM * CG) + cr * BM;                         // my 128 rows of the tile
         const int n0 = nt * BN + cr * G::kBRows;                         // my share of the B columns
         const int gb = p.chunk_groups > 0 ? g % p.chunk_groups : g;      // group of the B operand
         if (p.gate_flags != nullptr && m0 < p.M) {
-          const int last_row = min(m0 + BM, p.M) - 1;
-          const int s_lo = m0 / p.gate_rows, s_hi = last_row / p.gate_rows;
-          for (int s = s_lo; s <= s_hi && ok; ++s)
-            ok = wait_flag_ge(p.gate_flags + (p.chunk_groups > 0 ? (g / p.chunk_groups) * p.W : 0) + s, gate_want,
-                              p.budget_ns, p.status, s);
+          const unsigned long long tw0 = trace != nullptr ? global_timer_ns() : 0ull;
+          if (p.gate_mode == 1) {
+            // one flag per 128-row block, counting rows: mine is complete after `gate_want` fillings
+            const int blk = m0 / kGateBlock;
+            const unsigned long long rows_blk = (unsigned long long)min(kGateBlock, p.M - blk * kGateBlock);
+            ok = wait_flag_ge(p.gate_flags + (size_t)g * p.gate_nblk + blk, gate_want * rows_blk, p.budget_ns,
+                              p.status, 1000 + blk);
+          } else {
+            const int last_row = min(m0 + BM, p.M) - 1;
+            const int s_lo = m0 / p.gate_rows, s_hi = last_row / p.gate_rows;
+            for (int s = s_lo; s <= s_hi && ok; ++s)
+              ok = wait_flag_ge(p.gate_flags + (p.chunk_groups > 0 ? (g / p.chunk_groups) * p.W : 0) + s, gate_want,
+                                p.budget_ns, p.status, s);
+          }
           if (!ok) { ctl->abort = 1; break; }
           fence_proxy_async();   // peers' generic-proxy stores -> this thread's async-proxy loads
+          if (trace != nullptr) gate_wait_ns += global_timer_ns() - tw0;
         }
         for (int kb = 0; kb < kb_total; ++kb) {
           ok = mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1u, ctl, p.budget_ns, p.status, 0, stage);
@@ -565,6 +747,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
       }
       if (!ok) __nanosleep(200000);   // let bulk copies already in flight land before teardown
+      if (trace != nullptr) trace[3] = gate_wait_ns;
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -605,9 +788,23 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
     }
     __syncwarp();
-  } else if (warp >= 2 + kEpiWarps) {
+  } else if (warp == 2 + kEpiWarps) {
     // ------------------------------------------------------------------ dispatch send (copy warp)
-    if (p.copy.ctas > 0) copy_role(p, cring, ctl);
+    if constexpr (COPY) {
+      if (p.copy.ctas > 0) {
+        if (trace != nullptr && lane == 0) trace[1] = global_timer_ns();
+        copy_role(p, cring, ctl);
+        if (trace != nullptr && lane == 0) trace[2] = global_timer_ns();
+      }
+    }
+  } else if (warp == 3 + kEpiWarps) {
+    // ------------------------------------------------------------------ de-quantiser warp (int8 wire)
+    if constexpr (COPY && !A_MN) {
+      if (p.dequant.q != nullptr)
+        dequant_role<CG>(p, const_cast<__nv_bfloat16*>(reinterpret_cast<const __nv_bfloat16*>(p.a_ptr)), p.a_row_stride,
+                         p.a_group_stride, mt_count);
+      if (trace != nullptr && lane == 0) trace[5] = global_timer_ns();
+    }
   } else {
     // ------------------------------------------------------------------ epilogue warps (8)
     // Warp pairs share a TMEM lane quarter (warp % 4); each warp of a pair drains one 128-column
@@ -621,7 +818,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     bool ok = true;
     for (int tile = unit; tile < tiles && ok; tile += nunits) {
       const int nt = tile % nt_count;
-      const int mt = (tile / nt_count) % mt_count;
+      const int mt = permute_mt(p, (tile / nt_count) % mt_count);
       const int g = tile / (nt_count * mt_count);
       const int m0 = mt * (BM * CG) + cr * BM, n0 = nt * BN;
 
@@ -718,13 +915,80 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
       };
 
+      // int8 push: the warp's 32 rows x 128 columns leave as uint8 with one (scale, low) pair per row: the
+      // accumulator is read twice from TMEM (row range first, then quantisation), the bytes are staged as one
+      // 32 x 128-byte tile and written with one bulk tensor store, the pairs with one bulk copy (they are
+      // contiguous for the slice: the pairs are laid out [column group][row]).
+      bool q8_done = false;
+      if constexpr (EPI == kEpiPush && !COPY) {
+        if (p.push_q8) {
+          q8_done = true;
+          const int c0 = half * 128;
+          const int nb = n0 + c0;
+          if (nb < p.N) {
+            uint32_t v[64];
+            float lo = INFINITY, hi = -INFINITY;
+#pragma unroll
+            for (int s2 = 0; s2 < 2; ++s2) {
+              tmem_ld32(t_row + s2 * 64, v);
+              tmem_ld32(t_row + s2 * 64 + 32, v + 32);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 64; ++i) {
+                const float f = __uint_as_float(v[i]) + bias_s[c0 + s2 * 64 + i];
+                lo = fminf(lo, f); hi = fmaxf(hi, f);
+              }
+            }
+            const float range = hi - lo;
+            const float inv = range > 0.f ? 255.f / range : 0.f;
+            stage_free();                          // the previous tile's stores have left the staging tile
+            float2* pair_s = reinterpret_cast<float2*>(scale_s + ewarp * 256);
+#pragma unroll
+            for (int s2 = 0; s2 < 2; ++s2) {
+              tmem_ld32(t_row + s2 * 64, v);
+              tmem_ld32(t_row + s2 * 64 + 32, v + 32);
+              tmem_ld_wait();
+#pragma unroll
+              for (int c = 0; c < 4; ++c) {        // 16 columns -> one 16-byte piece of the row
+                uint32_t w[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  uint32_t b[4];
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const int i = c * 16 + j * 4 + e;
+                    const float f = __uint_as_float(v[i]) + bias_s[c0 + s2 * 64 + i];
+                    b[e] = (uint32_t)fminf(fmaxf(rintf((f - lo) * inv), 0.f), 255.f);
+                  }
+                  w[j] = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
+                }
+                const int piece = s2 * 4 + c;
+                *reinterpret_cast<uint4*>(st0 + lane * 128 + ((piece ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+              }
+            }
+            pair_s[lane] = make_float2(range * (1.f / 255.f), lo);
+            fence_proxy_async();                   // staging tile and pairs -> the copy engine
+            __syncwarp();
+            if (lane == 0 && tile_row < p.M) {
+              tma_store_3d(&om.m[push_s], st0_s, nb, push_drow, 0);
+              const int nrows = min(32, p.M - tile_row);
+              uint8_t* pairs = reinterpret_cast<uint8_t*>(p.heap_bases[push_s]) + p.push_scale_off +
+                               ((size_t)(nb >> 7) * (size_t)p.push_rows_total + (size_t)push_drow) * 8;
+              bulk_store(pairs, smem_u32(pair_s), (uint32_t)nrows * 8u);
+              bulk_commit();
+            }
+            __syncwarp();
+          }
+        }
+      }
+
       // The accumulator is drained in two 64-column slabs.  The TMEM load of the second slab is issued
       // as soon as the first slab's values have been consumed, so it runs under the first slab's stores.
       // (The activation-backward epilogue also holds the saved derivatives in registers and issues each
       // load at the top of its slab instead.)
       constexpr bool kEarlyLd = EPI != kEpiDAct;
       uint32_t v[64];
-      if (kEarlyLd && n0 + half * 128 < p.N) {
+      if (!q8_done && kEarlyLd && n0 + half * 128 < p.N) {
         tmem_ld32(t_row, v);
         tmem_ld32(t_row + 32, v + 32);
       }
@@ -732,7 +996,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       for (int s2 = 0; s2 < 2; ++s2) {
         const int c0 = half * 128 + s2 * 64;       // first accumulator column of this slab
         const int nb = n0 + c0;                    // first global column
-        if (nb >= p.N) break;
+        if (nb >= p.N || q8_done) break;
         if constexpr (!kEarlyLd) {
           tmem_ld32(t_row + s2 * 64, v);
           tmem_ld32(t_row + s2 * 64 + 32, v + 32);
@@ -852,14 +1116,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (p.tma_out && lane == 0) bulk_wait_all();   // my bulk stores have been performed
         epi_bar_sync();                            // every row of the tile has been stored
         if (etid == 0) {
-          __threadfence_system();
+          // Bulk stores have completed, so the flag update needs no release; rows written with ordinary stores
+          // are published by a fence + release.
+          if (!p.tma_out) __threadfence_system();
           const int last_row = min(m0 + BM, p.M) - 1;
           const int s_lo = m0 / p.push_rows, s_hi = last_row / p.push_rows;
           for (int s = s_lo; s <= s_hi; ++s) {
             unsigned long long* flags = reinterpret_cast<unsigned long long*>(
                 reinterpret_cast<uint8_t*>(p.heap_bases[s]) + p.push_flag_off);
             const int chunk = p.chunk_groups > 0 ? g / p.chunk_groups : p.push_chunk;
-            red_release_sys_add(flags + (long long)chunk * p.W + p.my_rank, 1ull);
+            if (p.tma_out) red_relaxed_sys_add(flags + (long long)chunk * p.W + p.my_rank, 1ull);
+            else           red_release_sys_add(flags + (long long)chunk * p.W + p.my_rank, 1ull);
           }
         }
       }
@@ -875,6 +1142,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     tc_fence_after();
     tmem_dealloc<CG>(tmem_base, kTmemCols);
   }
+  if (trace != nullptr && threadIdx.x == 0) trace[4] = global_timer_ns();
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -900,7 +1168,7 @@ EncodeFn get_encode_fn() {
 // Encoded tensor maps are cached: a training step encodes the same handful of (address, shape) pairs
 // over and over, and an encode costs microseconds of host time.
 struct MapKey {
-  const void* ptr; unsigned long long d[4]; unsigned long long st[3]; unsigned box[4]; int rank;
+  const void* ptr; unsigned long long d[4]; unsigned long long st[3]; unsigned box[4]; int rank; int dtype;
   bool operator==(const MapKey& o) const { return std::memcmp(this, &o, sizeof(MapKey)) == 0; }
 };
 struct MapCache {
@@ -911,12 +1179,12 @@ struct MapCache {
 MapCache& map_cache() { static MapCache c; return c; }
 
 bool encode_cached(CUtensorMap* out, int rank, const void* ptr, const cuuint64_t* dims, const cuuint64_t* strides,
-                   const cuuint32_t* box) {
+                   const cuuint32_t* box, CUtensorMapDataType dtype = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16) {
   EncodeFn enc = get_encode_fn();
   if (enc == nullptr) return false;
   MapKey k;
   std::memset(&k, 0, sizeof(k));
-  k.ptr = ptr; k.rank = rank;
+  k.ptr = ptr; k.rank = rank; k.dtype = (int)dtype;
   for (int i = 0; i < rank; ++i) { k.d[i] = dims[i]; k.box[i] = box[i]; }
   for (int i = 0; i + 1 < rank; ++i) k.st[i] = strides[i];
   MapCache& c = map_cache();
@@ -924,7 +1192,7 @@ bool encode_cached(CUtensorMap* out, int rank, const void* ptr, const cuuint64_t
   for (int i = 0; i < c.used; ++i)
     if (c.key[i] == k) { *out = c.map[i]; return true; }
   cuuint32_t estr[4] = {1, 1, 1, 1};
-  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(ptr), dims, strides, box,
+  CUresult r = enc(out, dtype, (cuuint32_t)rank, const_cast<void*>(ptr), dims, strides, box,
                    estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return false;
@@ -944,6 +1212,15 @@ bool make_out_map(CUtensorMap* map, const void* ptr, long long cols, long long r
   return encode_cached(map, 3, ptr, dims, strides, box);
 }
 
+// uint8 output map over (bytes per row, rows, 1) with a (128, 32, 1) box: one epilogue warp's int8 staging tile.
+bool make_out_map_u8(CUtensorMap* map, const void* ptr, long long cols, long long rows) {
+  if ((reinterpret_cast<uintptr_t>(ptr) % 16) || (cols % 16)) return false;
+  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, 1};
+  cuuint64_t strides[2] = {(cuuint64_t)cols, (cuuint64_t)(rows * cols)};
+  cuuint32_t box[3] = {128, 32, 1};
+  return encode_cached(map, 3, ptr, dims, strides, box, CU_TENSOR_MAP_DATA_TYPE_UINT8);
+}
+
 // 4-D map over (cols, rows, groups, chunks) with a (64, box_rows, 1, 1) box and 128-byte swizzle.
 bool make_map(CUtensorMap* map, const GemmOperand& op, int groups, int box_rows) {
   if (get_encode_fn() == nullptr) return false;
@@ -956,11 +1233,11 @@ bool make_map(CUtensorMap* map, const GemmOperand& op, int groups, int box_rows)
   return encode_cached(map, 4, op.ptr, dims, strides, box);
 }
 
-template <int CG, bool A_MN, bool B_MN, int EPI>
+template <int CG, bool A_MN, bool B_MN, int EPI, bool COPY>
 cudaError_t launch_epi(const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& om, const KernelParams& kp, int ctas,
                        cudaStream_t stream) {
-  auto kern = grouped_gemm_kernel<CG, A_MN, B_MN, EPI>;
-  constexpr int smem = (int)Geo<CG>::kSmemTotal;
+  auto kern = grouped_gemm_kernel<CG, A_MN, B_MN, EPI, COPY>;
+  constexpr int smem = (int)Geo<CG, COPY>::kSmemTotal;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -983,11 +1260,27 @@ cudaError_t launch_epi(const CUtensorMap& ta, const CUtensorMap& tb, const OutMa
 template <int CG, bool A_MN, bool B_MN>
 cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& om, const KernelParams& kp,
                            int ctas, cudaStream_t stream) {
+  // The variant with a dispatch send (copy and de-quantiser roles, one ring stage less) exists for the launches
+  // that consume a dispatched A operand: K-major A with the bias + activation or activation-backward epilogue.
+  static int force_copy_variant = -1;              // PLANMOE_GEMM_COPY_VARIANT=1: measure the variant's ring depth alone
+  if (force_copy_variant < 0) {
+    const char* e = getenv("PLANMOE_GEMM_COPY_VARIANT");
+    force_copy_variant = (e != nullptr && e[0] == '1') ? 1 : 0;
+  }
+  const bool copy = kp.copy.ctas > 0 || kp.dequant.q != nullptr ||
+                    (force_copy_variant && !A_MN && (kp.epilogue == kEpiBiasAct || kp.epilogue == kEpiDAct));
+  if (copy) {
+    if constexpr (!A_MN) {
+      if (kp.epilogue == kEpiBiasAct) return launch_epi<CG, A_MN, B_MN, kEpiBiasAct, true>(ta, tb, om, kp, ctas, stream);
+      if (kp.epilogue == kEpiDAct) return launch_epi<CG, A_MN, B_MN, kEpiDAct, true>(ta, tb, om, kp, ctas, stream);
+    }
+    return cudaErrorInvalidValue;
+  }
   switch (kp.epilogue) {
-    case kEpiStore: return launch_epi<CG, A_MN, B_MN, kEpiStore>(ta, tb, om, kp, ctas, stream);
-    case kEpiBiasAct: return launch_epi<CG, A_MN, B_MN, kEpiBiasAct>(ta, tb, om, kp, ctas, stream);
-    case kEpiDAct: return launch_epi<CG, A_MN, B_MN, kEpiDAct>(ta, tb, om, kp, ctas, stream);
-    case kEpiPush: return launch_epi<CG, A_MN, B_MN, kEpiPush>(ta, tb, om, kp, ctas, stream);
+    case kEpiStore: return launch_epi<CG, A_MN, B_MN, kEpiStore, false>(ta, tb, om, kp, ctas, stream);
+    case kEpiBiasAct: return launch_epi<CG, A_MN, B_MN, kEpiBiasAct, false>(ta, tb, om, kp, ctas, stream);
+    case kEpiDAct: return launch_epi<CG, A_MN, B_MN, kEpiDAct, false>(ta, tb, om, kp, ctas, stream);
+    case kEpiPush: return launch_epi<CG, A_MN, B_MN, kEpiPush, false>(ta, tb, om, kp, ctas, stream);
     default: return cudaErrorInvalidValue;
   }
 }
@@ -1007,17 +1300,17 @@ cudaError_t launch_layout(const GemmArgs& a, const CUtensorMap& ta, const CUtens
 int max_pair_units() {
   static int units = 0;
   if (units == 0) {
-    auto kern = grouped_gemm_kernel<2, false, true, kEpiStore>;
+    auto kern = grouped_gemm_kernel<2, false, true, kEpiBiasAct, true>;
     int n = 0;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(2, 1, 1);
     cfg.blockDim = dim3(kThreads, 1, 1);
-    cfg.dynamicSmemBytes = Geo<2>::kSmemTotal;
+    cfg.dynamicSmemBytes = Geo<2, true>::kSmemTotal;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Geo<2>::kSmemTotal) != cudaSuccess ||
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Geo<2, true>::kSmemTotal) != cudaSuccess ||
         cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
       cudaGetLastError();
       n = 0;
@@ -1098,25 +1391,47 @@ cudaError_t launch_grouped_gemm(const GemmArgs& a, cudaStream_t stream) {
   kp.bias = reinterpret_cast<const __nv_bfloat16*>(a.bias); kp.bias_group_stride = a.bias_group_stride;
   kp.gate_flags = a.gate_flags; kp.gate_rows = a.gate_rows > 0 ? a.gate_rows : a.M; kp.gate_want = a.gate_want;
   kp.gate_want_ptr = a.gate_want_ptr;
+  kp.gate_mode = a.gate_mode; kp.gate_nblk = a.gate_nblk;
+  kp.perm_w = 0; kp.perm_q = 0;
+  if (a.perm_w > 1 && a.perm_seg_rows > BM * cg && a.perm_seg_rows % (BM * cg) == 0 &&
+      (long long)a.perm_w * a.perm_seg_rows == a.M) {
+    kp.perm_w = a.perm_w; kp.perm_q = a.perm_seg_rows / (BM * cg);   // every segment is perm_q > 1 whole tiles
+  }
+  kp.a_ptr = a.A.ptr; kp.a_row_stride = a.A.row_stride;
+  kp.a_group_stride = a.A.group_stride > 0 ? a.A.group_stride : a.A.rows * a.A.row_stride;
   kp.heap_bases = a.heap_bases; kp.push_data_off = a.push_data_off; kp.push_flag_off = a.push_flag_off;
   kp.push_rows = a.push_rows > 0 ? a.push_rows : a.M; kp.push_C = a.push_C; kp.push_c0 = a.push_c0;
   kp.push_chunk = a.push_chunk; kp.W = a.W; kp.my_rank = a.my_rank;
+  kp.push_q8 = (a.epilogue == kEpiPush && a.push_q8) ? 1 : 0; kp.push_scale_off = a.push_scale_off;
+  kp.push_rows_total = (long long)a.W * (a.chunk_groups > 0 ? a.chunk_groups : a.groups) * a.push_C;
   kp.chunk_groups = a.chunk_groups;
   kp.budget_ns = a.budget_ns ? a.budget_ns : 20000000000ull;
   kp.status = a.status;
+  kp.trace = a.trace;
+  {
+    static int dbg = -1;
+    if (dbg < 0) { const char* e = getenv("PLANMOE_COPY_DBG"); dbg = e != nullptr ? atoi(e) : 0; }
+    kp.copy_dbg = dbg;
+  }
   kp.copy = a.copy;
   if (kp.copy.ctas > 0) {
-    if (kp.copy.x == nullptr || kp.copy.slot_map == nullptr || a.heap_bases == nullptr || (kp.copy.M % 8) ||
-        kp.copy.chunks <= 0 || (kp.copy.C % kp.copy.chunks) || (reinterpret_cast<uintptr_t>(kp.copy.x) % 16))
+    if (kp.copy.x == nullptr || kp.copy.slot_map == nullptr || a.heap_bases == nullptr ||
+        kp.copy.chunks <= 0 || (kp.copy.C % kp.copy.chunks) || (reinterpret_cast<uintptr_t>(kp.copy.x) % 16) ||
+        kp.copy.row_bytes <= 0 || (size_t)kp.copy.row_bytes > kCopyMaxSlot || (kp.copy.row_bytes % 16) ||
+        kp.copy.nblk <= 0)
       return cudaErrorInvalidValue;
   } else {
     kp.copy.ctas = 0;
   }
+  kp.dequant = a.dequant;
+  if (kp.dequant.q != nullptr) {
+    if (a.A.mn_major || a.gate_mode != 1 || kp.dequant.arrival == nullptr || kp.dequant.ready == nullptr ||
+        kp.dequant.M != a.K || (a.K % 16) || (a.A.chunks > 1))
+      return cudaErrorInvalidValue;
+  }
 
   const int ctas = gemm_grid_ctas(a.groups, a.M, a.N, a.max_ctas, cg);
-  // With a copy job every CTA of the grid adds one arrival per (chunk, destination) flag; the caller
-  // computed its expected count from gemm_grid_ctas() and passes it back as copy.ctas.
-  if (kp.copy.ctas > 0 && kp.copy.ctas != ctas) return cudaErrorInvalidValue;
+  if (kp.copy.ctas > 0) kp.copy.ctas = ctas;
 
   // ---- output tensor maps for the bulk-store epilogue ------------------------------------------
   // Used whenever every 32-row slice of a tile maps to 32 consecutive destination rows: always for
@@ -1136,9 +1451,12 @@ cudaError_t launch_grouped_gemm(const GemmArgs& a, cudaStream_t stream) {
     if (a.epilogue == kEpiPush) {
       okm = a.heap_bases_host != nullptr && a.W >= 1 && a.W <= 8 && kp.push_rows % 32 == 0 && a.M % 32 == 0;
       const int nel = a.chunk_groups > 0 ? a.chunk_groups : a.groups;
-      for (int r = 0; okm && r < a.W; ++r)
-        okm = make_out_map(&om.m[r], reinterpret_cast<const void*>(a.heap_bases_host[r] + a.push_data_off), a.N,
-                           (long long)a.W * nel * a.push_C, 1, a.N, 0);
+      for (int r = 0; okm && r < a.W; ++r) {
+        const void* base = reinterpret_cast<const void*>(a.heap_bases_host[r] + a.push_data_off);
+        okm = kp.push_q8 ? make_out_map_u8(&om.m[r], base, a.N, (long long)a.W * nel * a.push_C)
+                         : make_out_map(&om.m[r], base, a.N, (long long)a.W * nel * a.push_C, 1, a.N, 0);
+      }
+      if (kp.push_q8 && (a.N % 128)) okm = false;
     } else {
       okm = make_out_map(&om.m[0], a.D, a.N, a.M, a.groups, a.d_row_stride, a.d_group_stride);
       if (okm && a.epilogue == kEpiBiasAct && a.aux != nullptr)
@@ -1146,6 +1464,7 @@ cudaError_t launch_grouped_gemm(const GemmArgs& a, cudaStream_t stream) {
     }
     kp.tma_out = okm ? 1 : 0;
   }
+  if (kp.push_q8 && !kp.tma_out) return cudaErrorInvalidValue;   // the int8 push exists in the bulk-store form only
 
   if (cg == 2) return launch_layout<2>(a, ta, tb, om, kp, ctas, stream);
   return launch_layout<1>(a, ta, tb, om, kp, ctas, stream);

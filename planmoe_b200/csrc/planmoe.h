@@ -47,14 +47,19 @@ template <class T>
 void launch_scatter_rows(const T* x, const int* slot_map, const float* gates, T* local_out, int K,
                          int S, int M, int E, int C, const PushArgs* push, bool quant,
                          cudaStream_t stream);
+// scale_bias: null (rows of T), or fp32 (range, low) per row with uint8 rows (int8 codec), or -- with
+// group_rows > 0 -- fp32 (scale, low) per (128-column group, row), laid out [M / 128][group_rows], with uint8 rows
+// (what the int8 push epilogue of the grouped GEMM writes)
 template <class T>
 void launch_gather_rows(const void* disp, const float* scale_bias, const int* idx, const int* loc,
                         const float* gates, T* out, int K, int S, int M, int C, const WaitArgs* wait,
-                        cudaStream_t stream);
+                        cudaStream_t stream, long long group_rows = 0);
 // `gates` / `scaled` optional: also write scaled[t * K + k] = gates[k][t] * dy[t]
+// disp_scales != null: disp holds uint8 rows with fp32 (scale, low) per (128-column group, row), [M / 128][E * C]
 template <class T>
 void launch_gate_grad(const T* disp, const T* dy, const int* idx, const int* loc, float* dgates,
-                      const float* gates, T* scaled, int K, int S, int M, int C, cudaStream_t stream);
+                      const float* gates, T* scaled, int K, int S, int M, int C, cudaStream_t stream,
+                      const float* disp_scales = nullptr, long long group_rows = 0);
 
 // ---- kernels/gate.cu -------------------------------------------------------------------------
 int gate_workspace_blocks(int S);
@@ -77,6 +82,10 @@ void launch_int8_encode(const T* x, unsigned char* q, float* scale, float* bias,
 template <class T>
 void launch_int8_decode(const unsigned char* q, const float* scale, const float* bias, T* out, int R,
                         int M, cudaStream_t stream);
+
+// rows of M + 16 bytes: M uint8 + {scale, low, 0, 0} (the wire rows of the fused MoE send); M % 16 == 0
+template <class T>
+void launch_int8_rows_encode(const T* x, unsigned char* out, int R, int M, cudaStream_t stream);
 
 // ---- kernels/a2a.cu --------------------------------------------------------------------------
 // msgs: device int64 [n_msgs][6] = (dest rank or -1, flag index to signal or -1, src_off, dst_off, bytes,
@@ -125,11 +134,23 @@ struct GemmArgs {
   // of every group become readable when gate_flags[s] >= gate_want.
   const unsigned long long* gate_flags; int gate_rows; unsigned long long gate_want;
   const unsigned long long* gate_want_ptr;   // if set: gate_want is read from this device word at kernel start
+  // gate_mode 1 (the fused dispatch send's protocol): one flag per 128-row block of a group,
+  // gate_flags[g * gate_nblk + row / 128], counting ROWS; a block is readable when its flag has reached
+  // gate_want * (rows in the block), gate_want being the number of times the buffer has been filled.
+  int gate_mode, gate_nblk;
+  // perm_w > 1: a group's rows are perm_w source segments of perm_seg_rows rows each; when a segment is a whole
+  // number (> 1) of tiles, the tiles are visited segment-interleaved (tile 0 of every source, then tile 1, ...),
+  // the order in which the fused send delivers rows
+  int perm_w, perm_seg_rows;
   // push epilogue: row m of group g belongs to rank s = m / push_rows; it is stored at
   // heap_bases[s] + push_data_off + ((my_rank*groups + g) * push_C + push_c0 + m % push_rows) * N
   // and flag (push_flag_off)[push_chunk * W + my_rank] on rank s is incremented once per tile.
   const unsigned long long* heap_bases; unsigned long long push_data_off, push_flag_off;
   int push_rows, push_C, push_c0, push_chunk, W, my_rank;
+  // push_q8: rows are stored as N bytes of uint8 at heap_bases[s] + push_data_off + row * N, and one fp32
+  // (scale, low) pair per row and 128-column group at push_scale_off + ((n / 128) * rows_total + row) * 8,
+  // value = q * scale + low.  Needs N % 128 == 0 and the bulk-store form (heap_bases_host, rows % 32 == 0).
+  int push_q8; unsigned long long push_scale_off;
   // host copy of heap_bases (optional): lets the push epilogue use bulk tensor stores into the peers' buffers
   const unsigned long long* heap_bases_host;
   // chunk_groups > 0: the `groups` of A / D / aux are [chunk][expert] with chunk_groups experts per
@@ -138,22 +159,35 @@ struct GemmArgs {
   // flag [chunk * W + my_rank].  One launch then covers all pipeline chunks.
   int chunk_groups;
   unsigned long long budget_ns; int* status;
+  // Optional role trace, device u64 [grid][8] (ns of %globaltimer): [0] kernel entry, [1] / [2] copy role begin / end,
+  // [3] time the TMA producer spent waiting on gate flags, [4] kernel exit, [5] de-quantiser role end.
+  unsigned long long* trace;
   int max_ctas;                    // 0 = one per SM
   int cta_group;                   // 0 = automatic (gemm_cta_group), 1, or 2 (two-CTA clusters, 256 x 256 tiles)
-  // Fused dispatch send ("copy role"): with copy.ctas > 0 two extra warps of every CTA gather token
-  // rows of copy.x by slot map (optionally gate-weighted) and store them straight into the receive
-  // buffer of the rank that owns each expert, chunk by chunk, then release-add the (chunk, my_rank)
-  // flag on every destination: one arrival per CTA, and copy.ctas must equal the grid size
-  // (gemm_grid_ctas).  The producers of the same launch on every rank are the flag-gated consumers of
-  // this exchange, so the transfer and the math overlap inside one kernel.  Uses heap_bases / W /
-  // my_rank above.
+  // Fused dispatch send ("copy role"): with copy.ctas > 0 one extra warp of every CTA moves token rows
+  // of copy.x, picked by slot map, with the bulk-copy engine straight into the receive buffer of the rank
+  // that owns each expert, 8 rows at a time, and release-adds the row count to the flag of the 128-row
+  // block the rows lie in on the destination (gate_mode 1 on the receiving side).  The producers of the
+  // same launch on every rank are the flag-gated consumers of this exchange, so the transfer and the math
+  // overlap inside one kernel.  Rows of at most 16 KiB.  Uses heap_bases / W / my_rank above.
   struct CopyJob {
-    const void* x;                 // bf16 [S][M]
+    const void* x;                 // source rows [S][row_bytes]: bf16 tokens, or int8 rows with their 16-byte trailer
     const int* slot_map;           // [E_global * C] -> token * K + k, or -1
-    const float* gates;            // fp32 [K][S] or null
+    const float* gates;            // unused (gate-weighted rows are prepared by the caller)
     int K, S, M, E_local, C, chunks, ctas;
-    unsigned long long data_off, flag_off;   // destination buffer / u64 flags [chunks][W] in the heap
+    unsigned long long data_off, flag_off;   // destination buffer / u64 row-count flags [groups][nblk] in the heap
+    int nblk;                      // 128-row blocks per group of the destination buffer (= ceil(W * C / chunks / 128))
+    int row_bytes;                 // bytes per row, the same at source and destination (a multiple of 16, <= 16384)
   } copy;
+  // De-quantiser role (int8 wire): expands the int8 rows that peers stored into this rank's landing buffer
+  // [groups][rows][M + 16] into the bf16 A operand, 32 rows per unit in the order the tiles are consumed, and
+  // release-adds the row count to ready_flags[g * nblk + row / 128] (= gate_flags of the same launch).
+  struct DequantJob {
+    const void* q;                         // local landing buffer, or null (role idle)
+    const unsigned long long* arrival;     // local flags the peers' copy warps add rows to
+    unsigned long long* ready;             // local flags this role adds rows to
+    int M;                                 // elements per row
+  } dequant;
 };
 
 // Returns cudaSuccess or the launch / tensor-map error.

@@ -42,6 +42,12 @@ from .overlap import a2a_ffn_overlap_forward
 _NAME_RE = re.compile(r'^[a-zA-Z0-9_]+$')
 
 
+def fused_codecs():
+    """Codecs the fused kernels carry on the wire themselves."""
+    from ..ops import fused_moe
+    return fused_moe.FUSED_CODECS
+
+
 def _import_builtin(kind, name):
     assert _NAME_RE.match(name), \
         "%s type must only include digits, letters and underline characters." % kind.capitalize()
@@ -308,8 +314,16 @@ class MOELayer(torch.nn.Module):
             return False
         # codecs: raw bf16 rows or int8 rows (quantised by the sender, de-quantised in front of the GEMM);
         # zfp / lz take the generic compress -> all-to-all -> decompress pipeline
-        if self.compress_name not in ('no', 'int8'):
+        if self.compress_name not in fused_codecs():
             return False
+        if self.compress_name == 'int8':
+            # int8 rows: quantised per token before the send (so no gate scaling on the way: post-score layers),
+            # 128-column groups in the push epilogue, the fused send as the carrier
+            from ..ops import fused_moe as _fm
+            out_dim = self.experts.batched_fc2_w.size(2)
+            if not self.is_postscore or x.size(-1) % 128 or out_dim % 128 or not _fm._fuse_send(self.world_size) \
+                    or (max(x.size(-1), out_dim) + 16) > _fm.MAX_ROW_BYTES:
+                return False
         # on one NVSwitch domain the flat push is Pipe-A2A's equal (every peer is one hop away at full rate);
         # the hierarchical algorithms exist on the generic path
         if comm_name not in ('naive', 'pipe'):

@@ -5,10 +5,11 @@ Forward, per pipeline chunk j of the capacity dimension (``degree`` chunks):
     fused gate kernel      softmax + top-k + slot scan + slot map + GShard loss
     dispatch + GEMM 1      ONE launch.  A copy warp in every CTA moves token rows (picked by slot
                            map) with the bulk-copy engine straight into the receive buffer of the
-                           rank that owns the expert and release-adds its flag; the tcgen05 GEMM of
-                           the same launch reads A tiles from its own receive buffer as soon as the
-                           flags of the source ranks they touch have arrived; bias + activation
-                           epilogue.  (With one rank a separate slot-major copy kernel runs first.)
+                           rank that owns the expert, 16 rows at a time, and release-adds the row
+                           count to the flag of the 128-row block they land in; the tcgen05 GEMM of
+                           the same launch reads a 128-row block of its own receive buffer as soon
+                           as that block is complete; bias + activation epilogue.  Transfer and math
+                           overlap 128 rows at a time, whatever the pipeline degree.
     expert GEMM 2          tcgen05; the epilogue stores rows straight into the combine buffer of
                            the rank that owns the token, + release-add on its flag
     combine   (gather)     waits for the flags, gate-weighted sum over the k picks
@@ -40,41 +41,66 @@ from .gemm import ACT_CODES, EPI_BIAS_ACT, EPI_DACT, EPI_PUSH, EPI_STORE, groupe
 from ..parallel import transport as T
 from ..utils.stage_timer import stage
 
-MAX_CHUNKS = 32      # flag slots reserved per phase: [phase][chunk][source rank]
+MAX_CHUNKS = 32      # largest pipeline degree (flag slots per phase are sized for it)
 MAX_TOP_K = 4        # the fused gate kernel keeps at most four picks per token
-PH_DISPATCH, PH_COMBINE, PH_COMBINE_BWD, PH_DISPATCH_BWD = 0, 1, 2, 3
+GATE_BLOCK = 128     # rows per arrival flag of a dispatched GEMM operand
+MAX_ROW_BYTES = 16384  # longest bf16 row the fused send moves (one bulk-copy slot)
+FUSED_CODECS = ('no', 'int8')  # wire formats of the fused kernels
+# flag regions of a buffer set: the four exchanges, then the "de-quantised and ready" flags of the two
+# dispatch-like exchanges when rows travel as int8
+PH_DISPATCH, PH_COMBINE, PH_COMBINE_BWD, PH_DISPATCH_BWD, PH_DISPATCH_READY, PH_COMBINE_BWD_READY = range(6)
+N_PHASES = 6
 
 
 class _BufferSet:
     """Symmetric receive buffers + flags for one in-flight forward/backward of one layer."""
 
     def __init__(self, tr, key):
-        E_l, W, C, M, O = key[:5]
+        E_l, W, C, M, O, d, q8 = key[:7]
         self.tr = tr
-        el = 2
-        self.sz_x = E_l * W * C * M * el         # dispatch receive      [d][E_l][W][Cc][M]
-        self.sz_y = E_l * W * C * O * el         # combine receive       [E_g][C][O]
-        flags = 4 * MAX_CHUNKS * W * 8
-        total = 2 * self.sz_x + 2 * self.sz_y + flags
-        self.block = tr.alloc(total)
-        self.off_x = self.block.offset
-        self.off_y = self.off_x + self.sz_x
-        self.off_dy = self.off_y + self.sz_y
-        self.off_dx = self.off_dy + self.sz_y
-        self.off_flags = self.off_dx + self.sz_x
+        rows = E_l * W * C
+        self.q8 = bool(q8)
+        self.sz_x = rows * M * 2                  # dispatch receive (bf16 GEMM operand)  [d][E_l][W][Cc][M]
+        self.sz_dy = rows * O * 2                 # combine-backward receive (bf16 GEMM operand)
+        if q8:
+            self.sz_y = rows * (O + O // 16)      # combine receive, int8 rows + one (scale, low) per 128 columns
+            self.sz_dx = rows * (M + M // 16)
+            self.sz_qx = rows * (M + 16)          # int8 landing buffers of the two dispatch-like exchanges
+            self.sz_qdy = rows * (O + 16)
+        else:
+            self.sz_y = rows * O * 2              # combine receive       [E_g][C][O]
+            self.sz_dx = rows * M * 2
+            self.sz_qx = self.sz_qdy = 0
+        # flags of one phase: [chunk][source] arrivals (push epilogues, unfused send) or one row counter per
+        # 128-row block of every (chunk, expert) group (fused send)
+        self.flag_slots = max(MAX_CHUNKS * W, E_l * (W * C // GATE_BLOCK + MAX_CHUNKS) + 8)
+        sizes = [self.sz_x, self.sz_y, self.sz_dy, self.sz_dx, self.sz_qx, self.sz_qdy, N_PHASES * self.flag_slots * 8]
+        sizes = [(v + 1023) // 1024 * 1024 for v in sizes]
+        self.block = tr.alloc(sum(sizes))
+        offs = [self.block.offset]
+        for v in sizes[:-1]:
+            offs.append(offs[-1] + v)
+        self.off_x, self.off_y, self.off_dy, self.off_dx, self.off_qx, self.off_qdy, self.off_flags = offs
         self.W = W
         # Cumulative arrivals expected on every flag of a phase.  The count lives in device memory and is
         # advanced by a tiny add kernel in stream order before each use, and the waiting kernels read it
         # from there: nothing about the step's history is baked into kernel arguments, so a captured
         # CUDA graph of a step can be replayed.
-        self.want_dev = torch.zeros(4, dtype=torch.int64, device=tr.device)
-        self.want_views = [self.want_dev[i:i + 1] for i in range(4)]
+        self.want_dev = torch.zeros(N_PHASES, dtype=torch.int64, device=tr.device)
+        self.want_views = [self.want_dev[i:i + 1] for i in range(N_PHASES)]
         self.bases_host = self.block.bases_host   # peers' base addresses, for tensor maps over their buffers
         self.held = False
 
     def off_of(self, phase):
-        """Heap offset of the receive buffer the given phase writes."""
+        """Heap offset of the bf16 receive buffer the given exchange fills."""
         return (self.off_x, self.off_y, self.off_dy, self.off_dx)[phase]
+
+    def landing_off(self, phase):
+        """Heap offset of the buffer peers store into for a dispatch-like exchange (the int8 landing buffer when
+        rows travel as int8, else the bf16 operand itself)."""
+        if self.q8:
+            return self.off_qx if phase == PH_DISPATCH else self.off_qdy
+        return self.off_of(phase)
 
     def expect(self, phase, arrivals):
         """Every flag of ``phase`` will receive ``arrivals`` more; returns the device address of the new
@@ -83,11 +109,14 @@ class _BufferSet:
         return self.want_dev.data_ptr() + 8 * phase
 
     def flag_off(self, phase):
-        return self.off_flags + phase * MAX_CHUNKS * self.W * 8
+        return self.off_flags + phase * self.flag_slots * 8
 
     def flag_ptr(self, phase, chunk=0):
         base = self.tr.segments[self.block.segment].local_base()
         return base + self.flag_off(phase) + chunk * self.W * 8
+
+    def local_ptr(self, off):
+        return self.block.local_ptr + (off - self.block.offset)
 
     def view(self, off, shape):
         return self.block.tensor(torch.bfloat16, shape, byte_offset=off - self.block.offset)
@@ -133,29 +162,75 @@ def _sm_count():
 
 def _fuse_send(world):
     """Whether the dispatch send runs inside the flag-gated GEMM launch (a copy warp in every CTA, on the
-    bulk-copy engine).
-    With peers it does: transfer and math then overlap in one kernel.  With one rank nothing crosses
-    NVLink and a separate copy kernel on the whole machine, run first, is the default; the environment
-    variable PLANMOE_FUSE_SEND=0/1 overrides either way."""
+    bulk-copy engine): the default, with or without peers.  PLANMOE_FUSE_SEND=0 selects the separate
+    slot-major copy kernel followed by the gated GEMM instead."""
     env = os.environ.get('PLANMOE_FUSE_SEND')
     if env is not None:
         return env not in ('0', '', 'false')
-    return world > 1
+    return True
 
 
-def _send_and_gemm(lib, bs, phase, src, slot_map, gates, K, E, C, W, rank, d, grid, gemm):
-    """Dispatch-style push of ``src`` plus the flag-gated GEMM that consumes it.  ``gemm(want_ptr, **copy)``
-    enqueues the GEMM gated on the arrival count stored at ``want_ptr``; ``grid`` is its CTA count."""
+# Role trace of the fused launches (PLANMOE_GEMM_TRACE=1): per CTA, when the copy role ran and how long the TMA
+# producer waited for rows; `last_trace()` summarises the most recent launch per exchange.
+_TRACE = {}
+
+
+def _trace_buffer(phase, device):
+    if os.environ.get('PLANMOE_GEMM_TRACE', '0') != '1':
+        return None
+    if phase not in _TRACE:
+        _TRACE[phase] = torch.zeros(256, 8, dtype=torch.int64, device=device)
+    return _TRACE[phase]
+
+
+def last_trace():
+    """{exchange: {'kernel_us', 'copy_us', 'copy_start_us', 'gate_wait_us'}} medians / maxima over the CTAs."""
+    out = {}
+    for phase, buf in _TRACE.items():
+        t = buf.cpu()
+        t = t[t[:, 4] > 0]
+        if t.numel() == 0:
+            continue
+        t0 = int(t[:, 0].min())
+        out[{PH_DISPATCH: 'dispatch', PH_COMBINE_BWD: 'combine_bwd'}.get(phase, str(phase))] = {
+            'kernel_us': (int(t[:, 4].max()) - t0) / 1e3,
+            'copy_end_us_max': (int(t[:, 2].max()) - t0) / 1e3,
+            'copy_end_us_median': (int(t[:, 2].median()) - t0) / 1e3,
+            'copy_begin_us_median': (int(t[:, 1].median()) - t0) / 1e3,
+            'gate_wait_us_median': float(t[:, 3].median()) / 1e3,
+            'gate_wait_us_max': float(t[:, 3].max()) / 1e3,
+            'ctas': int(t.size(0))}
+    return out
+
+
+def _send_and_gemm(lib, bs, phase, src, slot_map, gates, K, E, C, W, rank, d, gemm):
+    """Dispatch-style push of ``src`` plus the flag-gated GEMM that consumes it.  ``gemm(**gate_and_copy)``
+    enqueues the GEMM with the given gate / copy / de-quantiser options."""
     bases = bs.block.bases_ptr
-    if not _fuse_send(W):
+    Cc = C // d
+    fused = _fuse_send(W) and gates is None and src.size(1) * src.element_size() <= MAX_ROW_BYTES
+    if not fused:
+        assert not bs.q8, "int8 rows travel only with the fused send"
         ctas = 4 * _sm_count()
         lib.scatter_push(src, slot_map, gates, K, E, C, bases, bs.off_of(phase), bs.flag_off(phase), W, rank, d,
                          ctas, 0, d)
-        gemm(bs.expect(phase, ctas))
+        gemm(gate_flags_ptr=bs.flag_ptr(phase, 0), gate_rows=Cc, gate_want_ptr=bs.expect(phase, ctas))
+        return
+    nblk = (W * Cc + GATE_BLOCK - 1) // GATE_BLOCK
+    opts = dict(gate_mode=1, gate_nblk=nblk, gate_want_ptr=bs.expect(phase, 1), perm_w=W, perm_seg_rows=Cc,
+                heap_bases_ptr=bases, copy_x=src, copy_slot_map=slot_map, copy_K=K, copy_E_local=E // W, copy_C=C,
+                copy_chunks=d, copy_ctas=1, copy_data_off=bs.landing_off(phase), copy_flag_off=bs.flag_off(phase),
+                copy_nblk=nblk)
+    trace = _trace_buffer(phase, src.device)
+    if trace is not None:
+        opts['trace_ptr'] = trace.data_ptr()
+    if bs.q8:
+        ready = PH_DISPATCH_READY if phase == PH_DISPATCH else PH_COMBINE_BWD_READY
+        opts.update(gate_flags_ptr=bs.flag_ptr(ready, 0), dq_ptr=bs.local_ptr(bs.landing_off(phase)),
+                    dq_arrival_ptr=bs.flag_ptr(phase, 0), dq_ready_ptr=bs.flag_ptr(ready, 0))
     else:
-        gemm(bs.expect(phase, grid), heap_bases_ptr=bases, copy_x=src, copy_slot_map=slot_map, copy_gates=gates,
-             copy_K=K, copy_E_local=E // W, copy_C=C, copy_chunks=d, copy_ctas=grid,
-             copy_data_off=bs.off_of(phase), copy_flag_off=bs.flag_off(phase))
+        opts.update(gate_flags_ptr=bs.flag_ptr(phase, 0))
+    gemm(**opts)
 
 
 class _Lease:
@@ -210,7 +285,10 @@ class _FusedExperts(torch.autograd.Function):
         postscore = meta['postscore']
         # Buffer sets are keyed by the pipeline degree as well: the flags of a set are cumulative counters
         # that advance together, chunk by chunk, only while every use has the same number of chunks.
-        bs = st.acquire((E_l, W, C, M, O, d))
+        q8 = bool(meta.get('q8', False))
+        # ... and by the protocol of their flags: row counters per 128-row block (fused send) or one arrival per
+        # sender CTA (separate copy kernel) must not be mixed on the same counters
+        bs = st.acquire((E_l, W, C, M, O, d, q8, _fuse_send(W)))
         bases = bs.block.bases_ptr
         budget, status = tr.budget_ms, tr.status_ptr
         gates_f = gates.detach().contiguous()
@@ -223,28 +301,37 @@ class _FusedExperts(torch.autograd.Function):
         dact = torch.empty((d * E_l, R, H), dtype=x.dtype, device=x.device)
         h = torch.empty_like(dact)
 
-        def gemm1(want_ptr, **copy):
+        def gemm1(**gate):
             grouped_gemm(recv_x, False, w1, True, EPI_BIAS_ACT, act, bias=b1, aux=dact, out=h,
-                         gate_flags_ptr=bs.flag_ptr(PH_DISPATCH, 0), gate_rows=Cc, gate_want_ptr=want_ptr,
-                         chunk_groups=E_l, W=W, my_rank=rank, budget_ms=budget, status_ptr=status, **copy)
+                         chunk_groups=E_l, W=W, my_rank=rank, budget_ms=budget, status_ptr=status, **gate)
+        src = x
+        if q8:
+            # int8 wire: rows are quantised once per token (M bytes + a 16-byte scale trailer), the copy warps
+            # move them as they are, and the de-quantiser warps of the receiving launch expand them in front of
+            # the GEMM
+            with stage('fwd.quantise'):
+                src = lib.int8_rows_encode(x)
         with stage('fwd.dispatch+gemm1'):
-            _send_and_gemm(lib, bs, PH_DISPATCH, x, slot_map, None if postscore else gates_f, K, E, C, W, rank, d,
-                           lib.gemm_grid_ctas(d * E_l, R, H), gemm1)
+            _send_and_gemm(lib, bs, PH_DISPATCH, src, slot_map, None if postscore else gates_f, K, E, C, W, rank, d,
+                           gemm1)
         push_arrivals = lib.gemm_push_arrivals(E_l, R, O, Cc, rank)
+        rows_y = E * C                              # rows of a combine buffer
+        q8_push = dict(push_q8=1, push_scale_off=bs.off_y + rows_y * O) if q8 else {}
         # GEMM 2 over all chunks: the epilogue pushes rows to the token owners' combine buffers
         with stage('fwd.gemm2+combine_push'):
             grouped_gemm(h, False, w2, True, EPI_PUSH, 0, bias=b2,
                          heap_bases_ptr=bases, heap_bases_host=bs.bases_host, push_data_off=bs.off_y,
                          push_flag_off=bs.flag_off(PH_COMBINE), push_rows=Cc, push_C=C,
-                         chunk_groups=E_l, W=W, my_rank=rank, budget_ms=budget, status_ptr=status)
+                         chunk_groups=E_l, W=W, my_rank=rank, budget_ms=budget, status_ptr=status, **q8_push)
         want_y = bs.expect(PH_COMBINE, push_arrivals)
 
         # ---- combine: wait for every (chunk, expert rank) flag, gate-weighted sum over k ---------
         # flags of chunks 0..d-1 are consecutive: [d][W]
+        q8_gather = dict(q8_scales_ptr=bs.local_ptr(bs.off_y + rows_y * O), q8_group_rows=rows_y) if q8 else {}
         with stage('fwd.combine_wait+decode'):
-            out = lib.gather_wait(bs.block.local_ptr + (bs.off_y - bs.block.offset), x.dtype, O, idx, loc,
+            out = lib.gather_wait(bs.local_ptr(bs.off_y), x.dtype, O, idx, loc,
                                   gates_f if postscore else None, C, bs.flag_ptr(PH_COMBINE, 0), d * W, 0,
-                                  budget, status, want_y)
+                                  budget, status, want_y, **q8_gather)
 
         ctx.meta, ctx.bs = meta, bs
         ctx.save_for_backward(x, gates_f, w1, w2, dact, h)
@@ -265,10 +352,20 @@ class _FusedExperts(torch.autograd.Function):
         budget, status = tr.budget_ms, tr.status_ptr
         dout = dout.contiguous()
 
-        recv_y = bs.view(bs.off_y, (E * C, O))
+        q8 = bs.q8
+        rows_y = E * C
+        recv_y = None if q8 else bs.view(bs.off_y, (E * C, O))
         dgates = None
         send_src, send_gates, send_K = dout, (gates_f if postscore else None), K
-        if postscore and _fuse_send(W):
+        if q8:
+            # expert outputs are held as int8 rows: the gate gradient de-quantises them on the fly; the gate-weighted
+            # dY rows are quantised for the wire like the tokens were
+            with stage('bwd.gate_grad'):
+                dgates, scaled = lib.dispatch_gate_grad_q8(bs.local_ptr(bs.off_y), bs.local_ptr(bs.off_y + rows_y * O),
+                                                           rows_y, dout, idx, loc, gates_f, C, True)
+                send_src = lib.int8_rows_encode(scaled)
+            send_gates, send_K = None, 1
+        elif postscore and _fuse_send(W) and O * 2 <= MAX_ROW_BYTES:
             # The fused send moves rows with the bulk-copy engine, which cannot scale them: the gate-gradient
             # pass, which reads every dY row anyway, also writes the gate-weighted copies (row = token * K + k,
             # the owner code of the slot map), and the send then moves those as they are.
@@ -284,21 +381,21 @@ class _FusedExperts(torch.autograd.Function):
         recv_x = bs.view(bs.off_x, (d * E_l, R, M))
         dh = torch.empty_like(dact)
 
-        def dgrad2(want_ptr, **copy):
+        def dgrad2(**gate):
             # dH = (dY . W2^T) * act'
             grouped_gemm(recv_dy, False, w2, False, EPI_DACT, act, aux=dact, out=dh,
-                         gate_flags_ptr=bs.flag_ptr(PH_COMBINE_BWD, 0), gate_rows=Cc, gate_want_ptr=want_ptr,
-                         chunk_groups=E_l, W=W, my_rank=rank, budget_ms=budget, status_ptr=status, **copy)
+                         chunk_groups=E_l, W=W, my_rank=rank, budget_ms=budget, status_ptr=status, **gate)
         with stage('bwd.combine_bwd_send+dgrad2'):
             _send_and_gemm(lib, bs, PH_COMBINE_BWD, send_src, slot_map, send_gates, send_K, E, C, W, rank,
-                           d, lib.gemm_grid_ctas(d * E_l, R, H), dgrad2)
+                           d, dgrad2)
         push_arrivals = lib.gemm_push_arrivals(E_l, R, M, Cc, rank)
+        q8_push = dict(push_q8=1, push_scale_off=bs.off_dx + rows_y * M) if q8 else {}
         # dX slots = dH . W1^T, pushed back to the token owners
         with stage('bwd.dgrad1+dispatch_bwd_push'):
             grouped_gemm(dh, False, w1, False, EPI_PUSH, 0,
                          heap_bases_ptr=bases, heap_bases_host=bs.bases_host, push_data_off=bs.off_dx,
                          push_flag_off=bs.flag_off(PH_DISPATCH_BWD), push_rows=Cc, push_C=C,
-                         chunk_groups=E_l, W=W, my_rank=rank, budget_ms=budget, status_ptr=status)
+                         chunk_groups=E_l, W=W, my_rank=rank, budget_ms=budget, status_ptr=status, **q8_push)
         want_dx = bs.expect(PH_DISPATCH_BWD, push_arrivals)
 
         # ---- weight / bias gradients: contract over all chunks in one launch each ---------------
@@ -311,10 +408,11 @@ class _FusedExperts(torch.autograd.Function):
             db1 = lib.colsum(dh, d, True)
 
         # ---- dispatch backward: wait for the returned slots, gather (gate-weighted if pre-score)
+        q8_gather = dict(q8_scales_ptr=bs.local_ptr(bs.off_dx + rows_y * M), q8_group_rows=rows_y) if q8 else {}
         with stage('bwd.dispatch_bwd_wait+gather'):
-            dx = lib.gather_wait(bs.block.local_ptr + (bs.off_dx - bs.block.offset), dout.dtype, M, idx, loc,
+            dx = lib.gather_wait(bs.local_ptr(bs.off_dx), dout.dtype, M, idx, loc,
                                  None if postscore else gates_f, C, bs.flag_ptr(PH_DISPATCH_BWD, 0), d * W,
-                                 0, budget, status, want_dx)
+                                 0, budget, status, want_dx, **q8_gather)
         if not postscore and ctx.needs_input_grad[1]:
             recv_dx = bs.view(bs.off_dx, (E * C, M))
             dgates = lib.dispatch_gate_grad(recv_dx, x, idx, loc, C)
@@ -344,10 +442,10 @@ def forward(layer, x, gctx, top_k, capacity_factor, degree):
         gates, l_aux, idx, loc, slot_map = fused_gate(logits, top_k, capacity, layer.normalize_gate)
     ex = layer.experts
     meta = dict(state=st, idx=idx, loc=loc, slot_map=slot_map, E=E, C=capacity, degree=degree, K=top_k,
-                act=ACT_CODES[ex.act_name], postscore=layer.is_postscore)
+                act=ACT_CODES[ex.act_name], postscore=layer.is_postscore, q8=(layer.compress_name == 'int8'))
     y = _FusedExperts.apply(x.contiguous(), gates, ex.batched_fc1_w, ex.batched_fc1_bias,
                             ex.batched_fc2_w, ex.batched_fc2_bias, meta)
-    layer.last_stats = dict(capacity=capacity, degree=degree, path='fused')
+    layer.last_stats = dict(capacity=capacity, degree=degree, path='fused', wire=('int8' if meta['q8'] else 'bf16'))
     if getattr(layer, 'collect_stats', False):
         from ..utils import metrics
         layer.last_stats.update(metrics.routing_stats(idx, loc, E, capacity))

@@ -2,15 +2,16 @@
 world size the layer supports (1, 2, 4, 8) without a GPU:
 
   * the dispatch send (copy role of the GEMM kernel): every (chunk, destination, expert, slot) row is moved
-    exactly once, lands inside the receive buffer, and no two units write the same bytes;
-  * the flag gate of GEMM 1: the source ranks a 128-row CTA tile waits for are exactly the ranks whose rows
-    it reads;
+    exactly once, lands inside the receive buffer, no two items write the same bytes, and the row counts
+    the senders add to a destination's 128-row block flags sum to the block's size;
+  * the flag gate of GEMM 1 and the de-quantiser's unit list: every 128-row block a tile reads has a flag,
+    the segment-interleaved tile order is a permutation, and the units cover every row once, in tile order;
   * the push epilogue: destination rows are unique and inside the combine buffer, and the number of
     arrivals each (chunk, source) flag receives equals what the host helper ``gemm_push_arrivals`` tells
     the receiver to wait for.
 
-The formulas mirror ``csrc/kernels/gemm_tcgen05.cu`` (``copy_role``, the producer's gate, the push
-epilogue) and ``ops/fused_moe.py``."""
+The formulas mirror ``csrc/kernels/gemm_tcgen05.cu`` (``copy_role``, ``dequant_role``, ``permute_mt``, the
+producer's gate, the push epilogue) and ``ops/fused_moe.py``."""
 
 import itertools
 
@@ -19,57 +20,121 @@ import pytest
 from planmoe_b200.ops import native
 
 BM = 128            # accumulator rows per CTA
-SLOT = 4096         # bytes per bulk-copy unit
+GATE_BLOCK = 128    # rows per arrival flag
+COPY_BYTES, MIN_SLOT = 65536, 4096
 
 
-def _copy_units(W, my_rank, E_l, C, d, M, grid):
-    """(cta, chunk, dest, row, piece, dst_byte_offset, bytes) for every unit the copy role moves."""
-    Cc, row_bytes = C // d, M * 2
-    rows = E_l * Cc
-    pieces = (row_bytes + SLOT - 1) // SLOT
+def _copy_items(W, my_rank, E_l, C, d, M, grid, quant=False):
+    """(cta, dest, group, first row in the destination group, rows, [dst byte offset of each row]) per item."""
+    Cc = C // d
+    wire = M + 16 if quant else M * 2                        # bytes of a row, at the source and on the wire
+    slot = MIN_SLOT
+    while slot < wire:
+        slot *= 2
+    lanes = COPY_BYTES // slot // 2                          # rows per item: half of the slots (two alternating sets)
+    per_seg = (Cc + lanes - 1) // lanes
+    n_items = d * E_l * per_seg * W
     out = []
     for cta in range(grid):
-        my_rows = (rows - 1 - cta) // grid + 1 if cta < rows else 0
-        units = W * my_rows * pieces
-        for j in range(d):
-            for u in range(units):
-                piece = u % pieces
-                k = (u // pieces) % my_rows
-                rr = u // (pieces * my_rows)
-                r = (my_rank + 1 + rr + cta) % W
-                row = cta + k * grid
-                el, cc = divmod(row, Cc)
-                nbytes = min(SLOT, row_bytes - piece * SLOT)
-                dst = ((((j * E_l + el) * W + my_rank) * Cc + cc) * row_bytes) + piece * SLOT
-                out.append((cta, j, r, el, cc, piece, dst, nbytes))
-    return out
+        for item in range(cta, n_items, grid):
+            rr = item % W
+            t = item // W
+            sub, g = t % per_seg, t // per_seg
+            r = (my_rank + 1 + rr) % W
+            row0 = sub * lanes
+            nrows = min(lanes, Cc - row0)
+            dsts = [((g * W + my_rank) * Cc + row0 + i) * wire for i in range(nrows)]
+            out.append((cta, r, g, my_rank * Cc + row0, nrows, dsts))
+    return out, wire
 
 
+@pytest.mark.parametrize("quant", [False, True])
 @pytest.mark.parametrize("W,E_l,C,d,M", [(1, 2, 8192, 1, 2048), (2, 2, 4096, 4, 2048), (4, 2, 2048, 2, 2048),
                                         (8, 2, 1024, 4, 2048), (8, 8, 320, 1, 1024), (8, 1, 96, 2, 4096),
-                                        (4, 3, 40, 1, 72)])
-def test_dispatch_send_covers_every_slot_once(W, E_l, C, d, M):
+                                        (4, 3, 40, 1, 72), (2, 2, 260, 1, 8192)])
+def test_dispatch_send_covers_every_slot_once(W, E_l, C, d, M, quant):
+    if quant and M % 16:
+        pytest.skip("int8 rows need a multiple of 16 elements")
     grid = 148
-    Cc, row_bytes = C // d, M * 2
-    buf_bytes = d * E_l * W * Cc * row_bytes                 # receive buffer of one destination rank
-    for my_rank in {0, W - 1, W // 2}:
-        seen = {}
-        per_dest_chunk = {}
-        for cta, j, r, el, cc, piece, dst, nbytes in _copy_units(W, my_rank, E_l, C, d, M, grid):
-            assert 0 <= dst and dst + nbytes <= buf_bytes
-            key = (r, dst)
-            assert key not in seen, "two units write the same bytes"
-            seen[key] = nbytes
-            per_dest_chunk[(r, j)] = per_dest_chunk.get((r, j), 0) + nbytes
-        # every destination receives, per chunk, all of my rows for its experts
+    Cc = C // d
+    R = W * Cc
+    nblk = (R + GATE_BLOCK - 1) // GATE_BLOCK
+    flags = {}                                               # (dest, group, block) -> rows added by all senders
+    for my_rank in range(W):
+        items, wire = _copy_items(W, my_rank, E_l, C, d, M, grid, quant)
+        buf_bytes = d * E_l * W * Cc * wire                  # receive buffer of one destination rank
+        seen = set()
+        rows_to = {}
+        for cta, r, g, first, nrows, dsts in items:
+            for dst in dsts:
+                assert 0 <= dst and dst + wire <= buf_bytes
+                assert (r, dst) not in seen, "two items write the same bytes"
+                seen.add((r, dst))
+            rows_to[(r, g)] = rows_to.get((r, g), 0) + nrows
+            left, f = nrows, first                            # the signal: rows split over the blocks they touch
+            while left > 0:
+                blk = f // GATE_BLOCK
+                n = min(left, (blk + 1) * GATE_BLOCK - f)
+                assert blk < nblk
+                flags[(r, g, blk)] = flags.get((r, g, blk), 0) + n
+                f += n
+                left -= n
         for r in range(W):
-            for j in range(d):
-                assert per_dest_chunk.get((r, j), 0) == E_l * Cc * row_bytes, (r, j)
+            for g in range(d * E_l):
+                assert rows_to.get((r, g), 0) == Cc, (r, g)  # every destination gets all my rows of every group
+    for r in range(W):
+        for g in range(d * E_l):
+            for blk in range(nblk):
+                assert flags.get((r, g, blk), 0) == min(GATE_BLOCK, R - blk * GATE_BLOCK), (r, g, blk)
+
+
+def _permute_mt(mt_lin, perm_w, perm_q):
+    if perm_q <= 1:
+        return mt_lin
+    return (mt_lin % perm_w) * perm_q + mt_lin // perm_w
+
+
+@pytest.mark.parametrize("W,E_l,C,d,cg", [(1, 2, 8192, 1, 2), (2, 2, 4096, 4, 2), (4, 2, 2048, 2, 2), (8, 2, 1024, 4, 2),
+                                         (8, 2, 1024, 1, 2), (8, 2, 1024, 8, 2), (8, 8, 320, 1, 2), (2, 2, 48, 2, 1)])
+def test_tile_order_and_dequant_units_cover_every_block(W, E_l, C, d, cg):
+    Cc = C // d
+    R = W * Cc                                               # rows per (chunk, expert) group
+    tile_rows = BM * cg
+    mt_count = (R + tile_rows - 1) // tile_rows
+    perm_w, perm_q = 0, 0
+    if W > 1 and Cc > tile_rows and Cc % tile_rows == 0 and W * Cc == R:
+        perm_w, perm_q = W, Cc // tile_rows
+    order = [_permute_mt(i, perm_w, perm_q) for i in range(mt_count)]
+    assert sorted(order) == list(range(mt_count))            # a permutation of the m-tiles
+    if perm_q > 1:                                           # first tile of every source before any second tile
+        assert [mt // perm_q for mt in order[:W]] == list(range(W))
+    nblk = (R + GATE_BLOCK - 1) // GATE_BLOCK
+    # de-quantiser units: 32 rows each, listed in tile order; every row exactly once, inside a flagged block
+    units_per_block = GATE_BLOCK // 32
+    covered = []
+    for u in range(mt_count * cg * units_per_block):
+        sub = u % units_per_block
+        t = u // units_per_block
+        b = t % cg
+        mt = _permute_mt(t // cg, perm_w, perm_q)
+        blk = mt * cg + b
+        row0 = blk * GATE_BLOCK + sub * 32
+        if row0 >= R:
+            continue
+        assert blk < nblk
+        covered += list(range(row0, min(row0 + 32, R)))
+    assert sorted(covered) == list(range(R))
+    # the producer of a CTA tile waits for the one block its 128 rows lie in
+    for mt in range(mt_count):
+        for cr in range(cg):
+            m0 = mt * tile_rows + cr * BM
+            if m0 < R:
+                assert m0 // GATE_BLOCK < nblk and m0 % GATE_BLOCK == 0
 
 
 @pytest.mark.parametrize("W,E_l,C,d", [(1, 2, 8192, 1), (2, 2, 4096, 4), (4, 2, 2048, 2), (8, 2, 1024, 4),
                                       (8, 2, 1024, 8), (8, 8, 320, 1), (2, 2, 48, 2)])
-def test_gate_flags_cover_the_rows_a_tile_reads(W, E_l, C, d):
+def test_gate_flags_of_the_unfused_send_cover_the_rows_a_tile_reads(W, E_l, C, d):
     Cc = C // d
     R = W * Cc                                               # rows per (chunk, expert) group
     for m0 in range(0, R, BM):

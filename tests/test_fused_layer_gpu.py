@@ -60,6 +60,46 @@ def test_fused_layer_matches_fp32_reference(degree, postscore, fuse_send, monkey
         assert close(p.grad, r.grad, 5e-2), p.shape
 
 
+@pytest.mark.parametrize("degree", [1, 2])
+def test_fused_layer_int8_wire_matches_fp32_reference(degree):
+    """compress_name='int8' on the fused path: rows are quantised before the send, de-quantised in front of the
+    GEMMs by the de-quantiser warps, pushed back as int8 by the GEMM epilogues and de-quantised by the gathers."""
+    E, M, H, k, cf = 4, 256, 512, 2, 1.0
+    layer = _layer(E, M, H, k, cf, a2a_ffn_overlap_degree=degree, compress_name='int8')
+    layer.gates[0].wg.float()
+    torch.manual_seed(0)
+    x = torch.randn(2048, M, device='cuda').to(torch.bfloat16).requires_grad_(True)
+    y = layer(x)
+    assert layer.last_stats['path'] == 'fused' and layer.last_stats['wire'] == 'int8'
+    w = torch.linspace(-1, 1, y.numel(), device='cuda').view_as(y)
+    ((y.float() * w).sum() + y.l_aux.float()).backward()
+    from planmoe_b200.parallel import transport
+    transport.get_transport(layer.group).check()
+
+    ex = layer.experts
+    params = [layer.gates[0].wg.weight, ex.batched_fc1_w, ex.batched_fc1_bias, ex.batched_fc2_w, ex.batched_fc2_bias]
+    refp = [p.detach().float().cpu().requires_grad_(True) for p in params]
+    xr = x.detach().float().cpu().requires_grad_(True)
+    yr, l_aux = dense_moe_reference(xr, *refp, top_k=k, capacity_factor=cf, act=F.gelu, alignment=4 * degree)
+    ((yr * w.cpu()).sum() + l_aux).backward()
+
+    def err(a, b):
+        a, b = a.float().cpu(), b.float()
+        return ((a - b).abs().max() / (b.abs().max() + 1e-6)).item()
+
+    assert err(y, yr) < 6e-2, err(y, yr)
+    assert err(x.grad, xr.grad) < 0.15, err(x.grad, xr.grad)
+    for p, r in zip(params, refp):
+        assert err(p.grad, r.grad) < 0.15, (p.shape, err(p.grad, r.grad))
+    # and it really differs from the bf16 wire (the quantisation is not a no-op)
+    layer2 = _layer(E, M, H, k, cf, a2a_ffn_overlap_degree=degree)
+    layer2.load_state_dict(layer.state_dict())
+    layer2.gates[0].wg.float()
+    with torch.no_grad():
+        y2 = layer2(x.detach())
+    assert not torch.equal(y2, y.detach())
+
+
 def test_fused_layer_is_bit_reproducible_and_reuses_buffers():
     layer = _layer(2, 256, 256, 2, 1.0)
     x = torch.randn(1024, 256, device='cuda').to(torch.bfloat16)
