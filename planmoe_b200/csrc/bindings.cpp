@@ -204,6 +204,27 @@ std::vector<Tensor> dispatch_gate_grad_q8_op(int64_t disp_ptr, int64_t scales_pt
   return {out, want_scaled ? scaled : Tensor()};
 }
 
+// (rank [S] i32, perm [S] i32) of the batch-prioritised token order
+std::vector<Tensor> importance_order_op(const Tensor& logits) {
+  count_launch(2);
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.is_contiguous());
+  const int S = logits.size(0), E = logits.size(1);
+  c10::cuda::CUDAGuard guard(logits.device());
+  Tensor key = torch::empty({S}, logits.options().dtype(at::kFloat));
+  Tensor rank = torch::empty({S}, logits.options().dtype(at::kInt)), perm = torch::empty({S}, logits.options().dtype(at::kInt));
+  DISPATCH_FLOAT(logits, "importance_order", [&] {
+    launch_importance_order<scalar_t>(reinterpret_cast<const scalar_t*>(logits.data_ptr()), S, E, key.data_ptr<float>(),
+                                      rank.data_ptr<int>(), perm.data_ptr<int>(), cur_stream());
+  });
+  return {rank, perm};
+}
+void remap_slot_map_op(Tensor& slot_map, const Tensor& perm, int64_t K) {
+  count_launch(1);
+  TORCH_CHECK(slot_map.is_cuda() && slot_map.is_contiguous() && slot_map.scalar_type() == at::kInt && perm.scalar_type() == at::kInt);
+  c10::cuda::CUDAGuard guard(slot_map.device());
+  launch_remap_slot_map(slot_map.data_ptr<int>(), slot_map.numel(), perm.data_ptr<int>(), (int)K, cur_stream());
+}
+
 // ---- fused gate -------------------------------------------------------------------------------
 // returns (idx[K,S] i32, loc[K,S] i32, gates[K,S] f32, slot_map[E*C] i32, top1_count[E] i32, l_aux[1] f32)
 std::vector<Tensor> gate_forward_op(const Tensor& logits, int64_t K, int64_t C, bool normalize) {
@@ -569,20 +590,35 @@ Tensor lz_decode_op(const Tensor& payload, const Tensor& sizes, int64_t raw_byte
 }
 
 // ---- C++ extension points: run a registered comm / codec on tensors -----------------------------
-Tensor native_comm_all_to_all_op(const std::string& name, const Tensor& t, int64_t world_size, int64_t world_rank,
-                                 int64_t local_size, int64_t heap_bases_ptr) {
-  CommContext ctx;
-  ctx.world_size = world_size; ctx.world_rank = world_rank; ctx.local_size = local_size;
-  ctx.local_rank = local_size > 0 ? world_rank % local_size : 0;
-  ctx.heap_bases = reinterpret_cast<const unsigned long long*>(heap_bases_ptr);
-  auto comm = make_comm(name, ctx);
-  TORCH_CHECK(comm != nullptr, "no native comm registered under `", name, "`");
-  Tensor in = t.contiguous();
-  Tensor out = torch::empty_like(in);
-  cudaStream_t s = in.is_cuda() ? cur_stream() : nullptr;
-  comm->all_to_all(in.data_ptr(), out.data_ptr(), in.numel() * in.element_size(), s);
-  return out;
-}
+// A comm object registered in C++, kept alive across calls (it owns call counters and cached tables).
+struct NativeCommHandle {
+  std::unique_ptr<AbstractComm> comm;
+  NativeCommHandle(const std::string& name, int64_t world_size, int64_t world_rank, int64_t local_size,
+                   int64_t heap_bases_ptr, int64_t local_base, int64_t scratch_off, int64_t scratch_bytes,
+                   int64_t status_ptr, int64_t budget_ms) {
+    CommContext ctx;
+    ctx.world_size = world_size; ctx.world_rank = world_rank; ctx.local_size = local_size > 0 ? local_size : world_size;
+    ctx.local_rank = world_rank % ctx.local_size;
+    ctx.heap_bases = reinterpret_cast<const unsigned long long*>(heap_bases_ptr);
+    ctx.local_base = (unsigned long long)local_base;
+    ctx.scratch_off = (unsigned long long)scratch_off; ctx.scratch_bytes = (unsigned long long)scratch_bytes;
+    ctx.status = reinterpret_cast<int*>(status_ptr);
+    if (budget_ms > 0) ctx.budget_ns = (unsigned long long)budget_ms * 1000000ull;
+    comm = make_comm(name, ctx);
+    TORCH_CHECK(comm != nullptr, "no native comm registered under `", name, "`");
+  }
+  int64_t scratch_bytes_for(int64_t payload) const { return (int64_t)comm->scratch_bytes_for((size_t)payload); }
+  Tensor all_to_all(const Tensor& t) {
+    Tensor in = t.contiguous();
+    Tensor out = torch::empty_like(in);
+    cudaStream_t s = nullptr;
+    if (in.is_cuda()) { count_launch(2); s = cur_stream(); }
+    c10::cuda::OptionalCUDAGuard guard;
+    if (in.is_cuda()) guard.set_device(in.device());
+    comm->all_to_all(in.data_ptr(), out.data_ptr(), in.numel() * in.element_size(), s);
+    return out;
+  }
+};
 
 Tensor native_codec_roundtrip_op(const std::string& name, const Tensor& t, int64_t parts, bool decode, int64_t out_bytes) {
   auto codec = make_compressor(name);
@@ -636,6 +672,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("dispatch_gate_grad_scaled", &dispatch_gate_grad_scaled_op);
   m.def("dispatch_gate_grad_q8", &dispatch_gate_grad_q8_op);
   m.def("gate_forward", &gate_forward_op);
+  m.def("importance_order", &importance_order_op);
+  m.def("remap_slot_map", &remap_slot_map_op);
   m.def("gate_backward", &gate_backward_op);
   m.def("cumsum_sub_one", &cumsum_sub_one_op);
   m.def("int8_encode", &int8_encode_op);
@@ -652,7 +690,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("lz_decode", &lz_decode_op);
   m.def("native_comm_names", &comm_names);
   m.def("native_compressor_names", &compressor_names);
-  m.def("native_comm_all_to_all", &native_comm_all_to_all_op);
+  py::class_<NativeCommHandle>(m, "NativeCommHandle")
+      .def(py::init<const std::string&, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t>(),
+           py::arg("name"), py::arg("world_size") = 1, py::arg("world_rank") = 0, py::arg("local_size") = 0,
+           py::arg("heap_bases_ptr") = 0, py::arg("local_base") = 0, py::arg("scratch_off") = 0,
+           py::arg("scratch_bytes") = 0, py::arg("status_ptr") = 0, py::arg("budget_ms") = 0)
+      .def("scratch_bytes_for", &NativeCommHandle::scratch_bytes_for)
+      .def("all_to_all", &NativeCommHandle::all_to_all);
   m.def("native_codec_run", &native_codec_roundtrip_op);
   m.def("xfer", &xfer_op, py::arg("src_ptr"), py::arg("msgs"), py::arg("ctas_per_msg"), py::arg("heap_bases_ptr"),
         py::arg("flag_off"), py::arg("wait_flags_ptr"), py::arg("wait_idx"), py::arg("want"), py::arg("budget_ms"),

@@ -27,12 +27,15 @@
 namespace planmoe {
 
 // What a comm object knows about the job.  heap_bases: device array [world_size] of peer-mapped
-// heap base addresses (null in a one-rank world); scratch_off / scratch_bytes: a block of the heap
-// reserved for this comm object on every rank; flag_off: u64 flags [world_size] inside that heap.
+// heap base addresses (null in a one-rank world), rank r's copy of the heap starts at heap_bases[r];
+// local_base: this rank's own base as a host-visible number; scratch_off / scratch_bytes: a zero-initialised
+// block of the heap reserved for this comm object, at the same offset on every rank, to lay out as it likes
+// (staging buffers, u64 flags, message tables); status: host-mapped int32[8] that bounded waits report to;
+// budget_ns: how long a device-side wait may last.
 struct CommContext {
   const unsigned long long* heap_bases = nullptr;
   unsigned long long local_base = 0;
-  unsigned long long scratch_off = 0, scratch_bytes = 0, flag_off = 0;
+  unsigned long long scratch_off = 0, scratch_bytes = 0;
   int world_size = 1, world_rank = 0, local_size = 1, local_rank = 0;
   int* status = nullptr;
   unsigned long long budget_ns = 20000000000ull;
@@ -42,6 +45,9 @@ class AbstractComm {
  public:
   explicit AbstractComm(const CommContext& ctx) : ctx_(ctx) {}
   virtual ~AbstractComm() = default;
+  // Heap bytes an object of this class wants reserved for payloads of `payload_bytes` per call (asked on a
+  // throw-away instance before the real one is built with a block of that size).
+  virtual size_t scratch_bytes_for(size_t payload_bytes) const { return 2 * payload_bytes + (64u << 10); }
   // `in` holds world_size equal parts of bytes / world_size, part j for rank j; `out` receives the
   // parts of all source ranks in rank order.  Enqueue on `stream`; do not synchronise.
   virtual void all_to_all(const void* in, void* out, size_t bytes, cudaStream_t stream) = 0;

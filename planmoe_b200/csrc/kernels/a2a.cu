@@ -97,11 +97,12 @@ xfer_kernel(const unsigned char* __restrict__ src_base, const long long* __restr
   ok = __all_sync(0xffffffffu, ok);
 
   if (ok && flag_idx >= 0 && dest >= 0) {
+    // every lane's bulk stores have completed (wait_group above, then the warp vote): the data is in place, so
+    // the flag update needs no release or fence of its own
     if (lane == 0) {
-      __threadfence_system();
       unsigned long long* flags = reinterpret_cast<unsigned long long*>(
           reinterpret_cast<unsigned char*>(heap_bases[dest]) + flag_off);
-      red_release_sys_add(flags + flag_idx, 1ull);
+      red_relaxed_sys_add(flags + flag_idx, 1ull);
     }
   }
 }

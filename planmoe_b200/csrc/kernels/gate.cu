@@ -279,6 +279,65 @@ void launch_gate_backward(const T* logits, int S, int E, int K, bool normalize, 
 
 int gate_workspace_blocks(int S) { return (S + kGateThreads - 1) / kGateThreads; }
 
+// ---- batch-prioritised routing: the order in which tokens claim slots -------------------------------
+// The reference sorts tokens by the score of their best expert, highest first (importance = -max softmax
+// score, PlanMoE/impls/fast_dispatch.py:135-138,153-154), and scans locations in that order.  Here the order
+// comes from a counting rank: key[t] = max_e softmax(logits[t])[e] = 1 / sum_e exp(l[t][e] - max_e l[t]);
+// rank[t] = number of tokens that go before t (larger key, or the same key and a lower index), perm = rank^-1.
+// S^2 comparisons on fp32 keys staged through shared memory: exact, stable and free of sort libraries.
+template <class T>
+__global__ void __launch_bounds__(256)
+importance_key_kernel(const T* __restrict__ logits, int S, int E, float* __restrict__ key) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= S) return;
+  const T* row = logits + (size_t)t * E;
+  float mx = -INFINITY;
+  for (int e = 0; e < E; ++e) mx = fmaxf(mx, to_f32(row[e]));
+  float sum = 0.f;
+  for (int e = 0; e < E; ++e) sum += expf(to_f32(row[e]) - mx);
+  key[t] = 1.f / sum;
+}
+
+__global__ void __launch_bounds__(256)
+importance_rank_kernel(const float* __restrict__ key, int S, int* __restrict__ rank, int* __restrict__ perm) {
+  __shared__ float tile[1024];
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  const float mine = t < S ? key[t] : 0.f;
+  int before = 0;
+  for (int base = 0; base < S; base += 1024) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < 1024; i += blockDim.x) tile[i] = base + i < S ? key[base + i] : -INFINITY;
+    __syncthreads();
+    const int n = min(1024, S - base);
+    for (int i = 0; i < n; ++i) {
+      const float other = tile[i];
+      before += (other > mine || (other == mine && base + i < t)) ? 1 : 0;
+    }
+  }
+  if (t < S) { rank[t] = before; perm[before] = t; }
+}
+
+template <class T>
+void launch_importance_order(const T* logits, int S, int E, float* key, int* rank, int* perm, cudaStream_t stream) {
+  if (S <= 0) return;
+  importance_key_kernel<T><<<(S + 255) / 256, 256, 0, stream>>>(logits, S, E, key);
+  importance_rank_kernel<<<(S + 255) / 256, 256, 0, stream>>>(key, S, rank, perm);
+}
+template void launch_importance_order<float>(const float*, int, int, float*, int*, int*, cudaStream_t);
+template void launch_importance_order<__nv_bfloat16>(const __nv_bfloat16*, int, int, float*, int*, int*, cudaStream_t);
+template void launch_importance_order<__half>(const __half*, int, int, float*, int*, int*, cudaStream_t);
+
+// slot map of a permuted token order back to token ids: owner = position * K + k -> perm[position] * K + k
+__global__ void remap_slot_map_kernel(int* __restrict__ slot_map, long long n, const int* __restrict__ perm, int K) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int o = slot_map[i];
+  if (o >= 0) slot_map[i] = perm[o / K] * K + o % K;
+}
+void launch_remap_slot_map(int* slot_map, long long n, const int* perm, int K, cudaStream_t stream) {
+  if (n > 0) remap_slot_map_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(slot_map, n, perm, K);
+}
+
 #define INSTANTIATE(T)                                                                            \
   template void launch_gate_forward<T>(const T*, int, int, int, int, bool, float, int*, int*,     \
                                        float*, float*, int*, int*, float*, int*, int*, float*,    \

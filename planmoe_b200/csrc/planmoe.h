@@ -72,6 +72,11 @@ template <class T>
 void launch_gate_backward(const T* logits, int S, int E, int K, bool normalize, float eps,
                           const int* idx, const float* dgates, const float* dl_aux,
                           const int* top1_count, T* dlogits, cudaStream_t stream);
+// order of tokens for batch-prioritised routing: rank[t] = position of token t (best top score first, ties by index),
+// perm[position] = token; `key` is an fp32 [S] workspace
+template <class T>
+void launch_importance_order(const T* logits, int S, int E, float* key, int* rank, int* perm, cudaStream_t stream);
+void launch_remap_slot_map(int* slot_map, long long n, const int* perm, int K, cudaStream_t stream);
 int cumsum_tiles(int S);
 void launch_cumsum_sub_one(const int* x, int* out, int* tile_sum, int S, int E, cudaStream_t stream);
 

@@ -328,8 +328,6 @@ class MOELayer(torch.nn.Module):
         # the hierarchical algorithms exist on the generic path
         if comm_name not in ('naive', 'pipe'):
             return False
-        if not self.is_gshard_loss:
-            return False
         if getattr(gctx, 'gate_kind', None) not in ('top', 'cosine_top'):
             return False
         if self.num_global_experts > 64 or x.size(-1) % 64 != 0:

@@ -419,8 +419,36 @@ class _FusedExperts(torch.autograd.Function):
         return dx, dgates, dw1, db1, dw2, db2, None
 
 
+def _dynamic_capacity(lib, logits, top_k, normalize, group, align):
+    """Capacity for ``capacity_factor == 0``: the largest slot any expert hands out, over all ranks, plus one
+    (reference: PlanMoE/impls/fast_dispatch.py:183-184, including its one host read of the all-reduced value).
+    The value is rounded up to the next of a coarse ladder (steps of about 12 %) so that the buffer sets, which are
+    keyed by capacity, take few distinct sizes; a larger capacity only adds empty slots."""
+    with torch.no_grad():
+        _idx, loc0, _g, _m, _t, _l = lib.gate_forward(logits.detach(), top_k, 4, normalize)
+        peak = loc0.max().reshape(1).to(torch.int64)
+        import torch.distributed as dist
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+            dist.all_reduce(peak, op=dist.ReduceOp.MAX, group=group)
+        cap = int(peak.item()) + 1
+    step = max(align, 64)
+    ladder = step
+    while ladder < cap:
+        ladder = max(ladder + step, (int(ladder * 1.125) + step - 1) // step * step)
+    return ladder
+
+
 def forward(layer, x, gctx, top_k, capacity_factor, degree):
-    """Run the fused path for ``layer`` on tokens ``x [S, M]``; returns ``(y [S, O], l_aux)``."""
+    """Run the fused path for ``layer`` on tokens ``x [S, M]``; returns ``(y [S, O], l_aux)``.
+
+    Routing variants of the reference, all on the fused gate kernels: ``capacity_factor < 0`` uses its bound
+    ``top_k * int(-cf * ceil(S / E))`` as the capacity (the reference takes the smaller of that bound and the largest
+    slot in use, PlanMoE/impls/fast_dispatch.py:185-186; the same tokens are kept either way and no host read is
+    needed); ``capacity_factor == 0`` sizes the capacity to the largest slot in use (one host read, as in the
+    reference); batch-prioritised routing scans the slots in the order of the tokens' best scores (a counting-rank
+    kernel, then the same gate kernels on the reordered logits); the load-importance loss replaces the GShard loss
+    when ``is_gshard_loss`` is false (a few element-wise operations on the [S, E] scores)."""
+    lib = native.lib()
     if layer._fused is None:
         layer._fused = FusedState(layer)
     st = layer._fused
@@ -430,16 +458,38 @@ def forward(layer, x, gctx, top_k, capacity_factor, degree):
     assert degree <= MAX_CHUNKS and top_k <= MAX_TOP_K, "plan outside the fused kernels' limits"
 
     with torch.autocast('cuda', enabled=False), stage('fwd.gate_linear'):
-        logits = gctx(x)
+        clean = gctx(x)
+        logits = clean
         if layer.training and gctx.gate_noise > 0:
-            logits = logits + gctx.gate_noise * torch.randn_like(logits) / E
-    capacity = top_k * int(capacity_factor * ((S + E - 1) // E))
+            logits = clean + gctx.gate_noise * torch.randn_like(clean) / E
+        logits = logits.contiguous()
     align = 4 * layer.sharded_count * degree
+    per_expert = (S + E - 1) // E
+    if capacity_factor > 0:
+        capacity = top_k * int(capacity_factor * per_expert)
+    elif capacity_factor < 0:
+        capacity = top_k * int(-capacity_factor * per_expert)
+    else:
+        capacity = _dynamic_capacity(lib, logits, top_k, layer.normalize_gate, layer.group, align)
+    capacity = max(capacity, 1)
     if capacity % align:
         capacity += align - capacity % align
 
     with stage('fwd.gate_topk_scan'):
-        gates, l_aux, idx, loc, slot_map = fused_gate(logits, top_k, capacity, layer.normalize_gate)
+        if layer.batch_prioritized_routing:
+            rank, perm = lib.importance_order(logits.detach())
+            gates_p, l_aux, idx_p, loc_p, slot_map = fused_gate(logits.index_select(0, perm.long()), top_k, capacity,
+                                                                layer.normalize_gate)
+            pos = rank.long()
+            gates = gates_p.index_select(1, pos)
+            idx, loc = idx_p.index_select(1, pos).contiguous(), loc_p.index_select(1, pos).contiguous()
+            lib.remap_slot_map(slot_map, perm, top_k)
+        else:
+            gates, l_aux, idx, loc, slot_map = fused_gate(logits, top_k, capacity, layer.normalize_gate)
+    if not layer.is_gshard_loss:
+        from ..impls import losses
+        topk_logits = logits.float().gather(1, idx.t().long())
+        l_aux = losses.load_importance_loss(F.softmax(clean.float(), dim=1), topk_logits, E, gctx.gate_noise)
     ex = layer.experts
     meta = dict(state=st, idx=idx, loc=loc, slot_map=slot_map, E=E, C=capacity, degree=degree, K=top_k,
                 act=ACT_CODES[ex.act_name], postscore=layer.is_postscore, q8=(layer.compress_name == 'int8'))

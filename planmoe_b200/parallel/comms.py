@@ -219,17 +219,50 @@ def register_comm(name, factory):
 
 
 class NativeComm(AbstractComm):
-    """Bridge to an all-to-all algorithm registered in C++ (``planmoe::register_comm``)."""
+    """Bridge to an all-to-all algorithm registered in C++ (``planmoe::register_comm``; extension contract in
+    ``csrc/comm/abstract.h``).  The C++ object is kept alive across calls; on CUDA worlds it is given a block of
+    the symmetric heap (the same offset on every rank) that it lays out itself, the table of the peers' heap base
+    addresses, the status word and the wait budget, which is all a user algorithm needs to move data between
+    ranks with ``planmoe::launch_xfer`` or kernels of its own."""
+
+    _HANDLES = {}
 
     def __init__(self, name, group=None):
         super().__init__(group)
         self.name = name
 
-    def all_to_all(self, t):
+    def _handle(self, t):
         from ..ops import native
-        bases = self._transport().segments[0].bases_device_ptr() if self._use_transport(t) else 0
-        return native.lib().native_comm_all_to_all(self.name, t, self.world_size, self.world_rank,
-                                                   self.local_size, bases)
+        lib = native.lib()
+        nbytes = t.numel() * t.element_size()
+        ranks = tuple(dist.get_process_group_ranks(self.group)) if (self.group is not None and self.world_size > 1) else ()
+        key = (self.name, ranks, self.world_size, t.is_cuda and self.world_size > 1)
+        cur = NativeComm._HANDLES.get(key)
+        if cur is not None and cur[1] >= nbytes:
+            return cur[0]
+        if not (t.is_cuda and self.world_size > 1):
+            h = lib.NativeCommHandle(self.name, self.world_size, self.world_rank, self.local_size)
+            NativeComm._HANDLES[key] = (h, 1 << 62)
+            return h
+        tr = self._transport()
+        cap = 1 << 20
+        while cap < nbytes:
+            cap <<= 1
+        probe = lib.NativeCommHandle(self.name, self.world_size, self.world_rank, self.local_size)
+        blk = tr.alloc(probe.scratch_bytes_for(cap))             # collective: every rank asks for the same size
+        h = lib.NativeCommHandle(self.name, self.world_size, self.world_rank, self.local_size, blk.bases_ptr,
+                                 tr.segments[blk.segment].local_base(), blk.offset, blk.nbytes, tr.status_ptr,
+                                 tr.budget_ms)
+        NativeComm._HANDLES[key] = (h, cap)
+        return h
+
+    def all_to_all(self, t):
+        if C.TUTEL_SKIP_A2A:
+            return t
+        t = t.contiguous()
+        if self.world_size > 1 and not t.is_cuda:
+            return _gloo_a2a(t, self.group)                      # CPU worlds have no heap: the library collective
+        return self._handle(t).all_to_all(t)
 
 
 def get_comm(name, group=None):

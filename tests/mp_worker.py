@@ -13,6 +13,11 @@ import torch.nn.functional as F
 
 
 def _init():
+    if os.environ.get('PLANMOE_USER_COMM_SO'):           # an out-of-tree C++ comm to register before use
+        import ctypes
+        from planmoe_b200.ops import native
+        native.lib()
+        ctypes.CDLL(os.environ['PLANMOE_USER_COMM_SO'], mode=ctypes.RTLD_GLOBAL)
     backend = os.environ.get('MP_BACKEND', 'gloo')
     rank, world = int(os.environ['RANK']), int(os.environ['WORLD_SIZE'])
     if backend == 'nccl':
@@ -255,6 +260,23 @@ def gpu_a2a(algo='flat'):
         out = tr.all_to_all(x, algo)
         tr.check()
         assert torch.equal(out, ref), (algo, it, rank)
+    dist.barrier()
+
+
+def gpu_native_comm_a2a(comm='native_flat'):
+    """A C++ comm object against all_to_all_single: several sizes, buffers reused, sizes growing."""
+    rank, world, dev = _init()
+    from planmoe_b200.parallel import comms, transport
+    for it, nelem in enumerate([4096, 1 << 18, 4096, 3 << 18, 1 << 18]):
+        torch.manual_seed(rank * 100 + it)
+        x = torch.randn(world, nelem, device=dev).to(torch.bfloat16)
+        ref = torch.empty_like(x)
+        dist.all_to_all_single(ref, x)
+        c = comms.get_comm(comm)
+        assert isinstance(c, comms.NativeComm)
+        out = c.all_to_all(x)
+        transport.get_transport(None).check()
+        assert torch.equal(out, ref), (comm, it, rank)
     dist.barrier()
 
 

@@ -100,6 +100,70 @@ def test_fused_layer_int8_wire_matches_fp32_reference(degree):
     assert not torch.equal(y2, y.detach())
 
 
+@pytest.mark.parametrize("variant", ['cf_negative', 'cf_zero_dynamic', 'batch_prio', 'load_importance', 'fairseq_like'])
+def test_routing_variants_stay_on_the_fused_path(variant, monkeypatch):
+    """Dynamic / bounded capacity, batch-prioritised routing and the load-importance loss run on the fused kernels
+    and agree with the generic path (ATen routing of ``extract_critical``, torch.matmul experts)."""
+    E, M, H, k = 4, 256, 256, 2
+    kw, cf = {}, 1.0
+    if variant == 'cf_negative':
+        cf = -1.5
+    elif variant == 'cf_zero_dynamic':
+        cf = 0.0
+    elif variant == 'batch_prio':
+        kw['batch_prioritized_routing'] = True
+        cf = 0.5                                   # tight capacity: which tokens are dropped depends on the order
+    elif variant == 'load_importance':
+        kw['is_gshard_loss'] = False
+    elif variant == 'fairseq_like':
+        E, cf = 1, 0.0                             # one expert per GPU, dynamic capacity (the fairseq integration)
+    layer = _layer(E, M, H, k, cf, **kw)
+    layer.gates[0].wg.float()
+    if variant == 'load_importance':
+        layer.gates[0].gate_noise = 1.0            # the loss's load term needs a noise scale; eval mode adds no noise
+        layer.eval()
+    torch.manual_seed(3)
+    x0 = torch.randn(1536, M, device='cuda').to(torch.bfloat16)
+    w = torch.linspace(-1, 1, x0.numel(), device='cuda').view_as(x0)
+
+    def run(fused):
+        monkeypatch.setenv('PLANMOE_FUSED', '1' if fused else '0')
+        x = x0.clone().requires_grad_(True)
+        y = layer(x)
+        assert layer.last_stats['path'] == ('fused' if fused else 'generic')
+        ((y.float() * w).sum() + y.l_aux.float()).backward()
+        g = layer.gates[0].wg.weight.grad.clone()
+        layer.zero_grad()
+        return y.detach().float(), float(y.l_aux), x.grad.float(), g, layer.last_stats['capacity']
+
+    yf, lf, gxf, gwf, cap_f = run(True)
+    from planmoe_b200.parallel import transport
+    transport.get_transport(layer.group).check()
+    yg, lg, gxg, gwg, cap_g = run(False)
+    if variant in ('cf_zero_dynamic', 'fairseq_like'):
+        assert cap_f >= cap_g                      # the fused path rounds the dynamic capacity up, never down
+    close = lambda a, b, tol: ((a - b).abs().max() / (b.abs().max() + 1e-6)).item() < tol   # noqa: E731
+    assert close(yf, yg, 3e-2)
+    assert abs(lf - lg) < 1e-3 * max(1.0, abs(lg)), (lf, lg)
+    assert close(gxf, gxg, 4e-2)
+    assert close(gwf.float(), gwg.float(), 5e-2)
+
+
+def test_importance_order_kernel_matches_a_sort():
+    from planmoe_b200.ops import native
+    lib = native.lib()
+    torch.manual_seed(0)
+    logits = torch.randn(3000, 16, device='cuda')
+    logits[100] = logits[7]                         # a tie: the lower token index goes first
+    rank, perm = lib.importance_order(logits)
+    key = F.softmax(logits.double(), dim=1).max(dim=1).values
+    along = key[perm.long()]
+    assert bool((along[:-1] - along[1:] >= -1e-6).all())          # best top score first
+    pos = rank.tolist()
+    assert pos[7] + 1 == pos[100]                                   # equal keys: token order
+    assert rank[perm.long()].tolist() == list(range(3000))          # rank and perm are inverse permutations
+
+
 def test_fused_layer_is_bit_reproducible_and_reuses_buffers():
     layer = _layer(2, 256, 256, 2, 1.0)
     x = torch.randn(1024, 256, device='cuda').to(torch.bfloat16)
