@@ -77,8 +77,13 @@ extern "C" int planmoe_colsum_bf16_noalloc(const void* x, float* out, int groups
   if (need > (long long)PLANMOE_COLSUM_NOALLOC_MAX_FLOATS || slabs > 65535 || groups > 65535)
     return PLANMOE_NOALLOC_TOO_LARGE;
 
+  // An error left behind by earlier work of this thread is the caller's to handle: report it as such instead of
+  // launching and then mistaking it for a failure of this call.
+  cudaError_t e = cudaPeekAtLastError();
+  if (e != cudaSuccess) { t_last_cuda_error = (int)e; return PLANMOE_NOALLOC_PENDING_ERROR; }
+
   float* scratch = nullptr;
-  cudaError_t e = scratch_for_current_device(&scratch);
+  e = scratch_for_current_device(&scratch);
   if (e != cudaSuccess) { t_last_cuda_error = (int)e; return PLANMOE_NOALLOC_CUDA_ERROR; }
 
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);

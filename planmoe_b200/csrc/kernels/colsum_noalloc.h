@@ -39,6 +39,7 @@ enum {
   PLANMOE_NOALLOC_BAD_ARGUMENT = 1,   // null pointer, non-positive extent, odd N, misaligned x
   PLANMOE_NOALLOC_TOO_LARGE = 2,      // needs more scratch than the built-in array holds
   PLANMOE_NOALLOC_CUDA_ERROR = 3,     // symbol lookup or launch failed (see planmoe_colsum_noalloc_last_cuda_error)
+  PLANMOE_NOALLOC_PENDING_ERROR = 4,  // an earlier CUDA error of this thread was still pending: nothing was launched
 };
 
 // x: device pointer to bf16, element strides `row_stride` / `group_stride`; out: device pointer to

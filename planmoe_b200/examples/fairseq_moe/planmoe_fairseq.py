@@ -5,7 +5,8 @@ The reference patches fairseq (commit b5e7b25) so that every ``MOE``-th decoder 
 ``system.cache()`` and adds ``L_AUX_WT * sample_size * sum(l_aux)`` to the loss, and with
 ``NO_OVERFLOW=1`` zeroes non-finite gradients before the optimizer step
 (``PlanMoE/examples/fairseq_moe/fairseq_patch.diff:41-54,82-84,103-106,119-128``).
-These functions hold that logic; README.md next to this file shows where fairseq calls them.
+These functions hold that logic; ``planmoe_fairseq.diff`` next to this file is the patch that makes fairseq call
+them (``git apply`` it in a checkout of that commit).
 """
 
 import os
@@ -32,23 +33,51 @@ def build_ffn(layer_index, embed_dim, ffn_dim, activation_fn=None):
         scan_expert_func=lambda name, param: setattr(param, 'expert', True))
 
 
+def tag_layer_index(cfg, index):
+    """Record which decoder layer is being built (``TransformerDecoderBase`` builds them in a comprehension)."""
+    cfg.transformer_index = index
+    return cfg
+
+
+def build_ffn_for_layer(layer, cfg):
+    """The MoE FFN of a ``TransformerDecoderLayerBase`` under construction, or None for a dense layer.  The
+    experts' activation is the layer's activation dropout (and FFN layer norm), as in the dense branch."""
+    index = int(getattr(cfg, 'transformer_index', 0))
+    n = moe_every()
+    if n <= 0 or (index + 1) % n != 0:
+        return None
+    assert not getattr(layer, 'quant_noise', 0), "Unhandled quant_noise > 0.0 for MoE layer."
+
+    def act(x):
+        x = layer.activation_dropout_module(layer.activation_fn(x))
+        return x if layer.ffn_layernorm is None else layer.ffn_layernorm(x)
+    return build_ffn(index, layer.embed_dim, cfg.decoder.ffn_embed_dim, act)
+
+
 def ffn_forward(moe, x):
-    """Run the MoE FFN and record its auxiliary loss in the process-wide cache."""
+    """Run the MoE FFN and record (tokens, l_aux) in the process-wide cache for the loss."""
     from planmoe_b200 import system
     y = moe(x)
-    system.cache().set(id(moe), y.l_aux)
+    if y.l_aux is not None and y.l_aux.requires_grad:
+        system.cache().set(id(moe), (y.numel() // y.size(-1), y.l_aux))
     return y
 
 
-def add_aux_loss(loss, sample_size):
-    """``loss + L_AUX_WT * sample_size * sum(l_aux of all MoE layers)``; clears the cache."""
+def add_aux_loss(loss, sample_size=None):
+    """``loss + L_AUX_WT * sum(tokens * l_aux of every MoE layer)``; clears the cache.  With ``sample_size`` given,
+    that count weighs every layer instead of the layer's own token count."""
     from planmoe_b200 import system
-    weight = float(os.environ.get('L_AUX_WT', 0.01))
-    aux = [a for a in system.cache().get() if a is not None]
+    weight = float(os.environ.get('L_AUX_WT', 0.0))
+    entries = [a for a in system.cache().get() if a is not None]
     system.cache().reset()
-    if not aux:
+    if not entries or not weight:
         return loss
-    return loss + weight * sample_size * sum(a.float() for a in aux)
+    total = None
+    for entry in entries:
+        tokens, aux = entry if isinstance(entry, tuple) else (sample_size or 1, entry)
+        term = aux.float() * (weight * (sample_size if sample_size is not None else tokens))
+        total = term if total is None else total + term
+    return loss + total
 
 
 def sanitize_grads(parameters):

@@ -5,8 +5,8 @@ The reference ships this as a patch against Megatron-LM ``core_r0.9.0``
 ``--schemoe`` / ``--schemoe-overlap-degree`` / ``--schemoe-compress-name`` / ``--schemoe-comm-name``
 and, when enabled, every decoder layer's ``mlp`` becomes a ``moe_layer`` (top-k linear gate in fp32
 with gate noise 1.0, GELU FFN experts, ``param.allreduce = False`` on expert parameters so that the
-data-parallel reducer skips them).  Here the same logic is importable code; the three lines to add
-to Megatron are listed in README.md next to this file.
+data-parallel reducer skips them).  Here the same logic is importable code, and ``planmoe_megatron.diff`` next
+to this file is the patch that makes Megatron call it (``git apply`` it in a ``core_r0.9.0`` checkout).
 """
 
 import torch
@@ -56,3 +56,19 @@ def maybe_replace_mlp(layer, config, args, group=None):
     if getattr(args, 'schemoe', False):
         layer.mlp = PlanMoEMLP(config, args, group)
     return layer
+
+
+def wrap_model_provider(model_provider, args):
+    """Wraps Megatron's ``model_provider`` (called from ``pretrain``): the model is built as usual, then the ``mlp``
+    of every decoder layer is replaced by ``PlanMoEMLP``.  Its ``forward`` returns ``(output, None)`` like
+    Megatron's MLP, so ``TransformerLayer.forward`` needs no change."""
+    def provider(pre_process=True, post_process=True, **kwargs):
+        try:
+            model = model_provider(pre_process=pre_process, post_process=post_process, **kwargs)
+        except TypeError:
+            model = model_provider()
+        config = getattr(model, 'config', None)
+        for layer in model.decoder.layers:
+            maybe_replace_mlp(layer, config if config is not None else layer.config, args)
+        return model
+    return provider

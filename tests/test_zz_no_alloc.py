@@ -44,6 +44,25 @@ def test_noalloc_colsum_matches_regular_entry_point_twice():
         assert torch.allclose(out, x.float().sum(1), atol=1e-2, rtol=1e-3), trial
 
 
+def test_noalloc_colsum_padded_groups_and_second_stream():
+    """Groups with padding between them (a group stride larger than rows * N), launched on a side stream that an
+    event orders behind the producer of the input and in front of the consumer of the output."""
+    lib, fn = _symbol()
+    torch.cuda.set_device(0)
+    groups, rows, n, pad_rows = 3, 300, 128, 20
+    side = torch.cuda.Stream()
+    big = torch.randn(groups, rows + pad_rows, n, device='cuda').to(torch.bfloat16)
+    x = big[:, :rows]                                    # group stride (rows + pad_rows) * n, rows contiguous
+    out = torch.full((groups, n), float('nan'), device='cuda', dtype=torch.float32)
+    side.wait_stream(torch.cuda.current_stream())        # the input is ready
+    rc = fn(x.data_ptr(), out.data_ptr(), groups, rows, n, x.stride(1), x.stride(0), side.cuda_stream)
+    assert rc == 0, rc
+    torch.cuda.current_stream().wait_stream(side)        # the output is ready
+    ref = lib.colsum(x.contiguous())
+    torch.cuda.synchronize()
+    assert torch.allclose(out, ref, atol=1e-2, rtol=1e-3)
+
+
 def test_noalloc_colsum_rejects_oversize_and_bad_arguments():
     lib, fn = _symbol()
     x = torch.zeros(1, 256, 8, device='cuda', dtype=torch.bfloat16)
