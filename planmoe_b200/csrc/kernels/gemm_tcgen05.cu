@@ -278,6 +278,7 @@ struct Ctl {
   uint64_t acc_empty[kAccStages];
   uint64_t copy_full[kCopyMaxLanes];   // a row has landed in bulk-copy slot i
   uint32_t tmem_base;
+  int dq_next;                 // next de-quantiser unit of this CTA (claimed by whichever warp is free)
   volatile int abort;
   volatile int epi_abort[2];   // written by epilogue warps before a barrier, read after it
 };
@@ -534,7 +535,7 @@ __device__ __forceinline__ void copy_role(const KernelParams& p, uint8_t* cring,
 // ---------------------------------------------------------------------------------------------
 template <int CG>
 __device__ __forceinline__ void dequant_role(const KernelParams& p, __nv_bfloat16* a_base, long long a_row_stride,
-                                             long long a_group_stride, int mt_count) {
+                                             long long a_group_stride, int mt_count, Ctl* ctl) {
   const GemmArgs::DequantJob& d = p.dequant;
   const int lane = threadIdx.x & 31;
   const unsigned long long uses = p.gate_want_ptr != nullptr ? *p.gate_want_ptr : p.gate_want;
@@ -542,7 +543,14 @@ __device__ __forceinline__ void dequant_role(const KernelParams& p, __nv_bfloat1
   const long long n_units = (long long)p.groups * mt_count * CG * kUnitsPerBlock;
   const size_t q_row = (size_t)d.M + 16;
   const uint8_t* qbase = reinterpret_cast<const uint8_t*>(d.q);
-  for (long long u = blockIdx.x; u < n_units; u += gridDim.x) {
+  // The CTA's units (blockIdx.x, blockIdx.x + grid, ...) are claimed one at a time from a shared counter, in order:
+  // the de-quantiser warp starts at once, the copy warp joins when its sends are done.
+  while (true) {
+    int k = 0;
+    if (lane == 0) k = atomicAdd(&ctl->dq_next, 1);
+    k = __shfl_sync(0xffffffffu, k, 0);
+    const long long u = (long long)blockIdx.x + (long long)k * gridDim.x;
+    if (u >= n_units) break;
     const int sub = (int)(u % kUnitsPerBlock);
     long long t = u / kUnitsPerBlock;
     const int b = (int)(t % CG); t /= CG;
@@ -673,6 +681,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     for (int i = 0; i < kCopyMaxLanes; ++i) mbar_init(smem_u32(&ctl->copy_full[i]), 1);
     ctl->abort = 0;
+    ctl->dq_next = 0;
     ctl->epi_abort[0] = ctl->epi_abort[1] = 0;
     fence_barrier_init();
   }
@@ -796,13 +805,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         copy_role(p, cring, ctl);
         if (trace != nullptr && lane == 0) trace[2] = global_timer_ns();
       }
+      if constexpr (!A_MN) {
+        if (p.dequant.q != nullptr)              // sends done: help expanding the int8 rows that arrive
+          dequant_role<CG>(p, const_cast<__nv_bfloat16*>(reinterpret_cast<const __nv_bfloat16*>(p.a_ptr)), p.a_row_stride,
+                           p.a_group_stride, mt_count, ctl);
+      }
     }
   } else if (warp == 3 + kEpiWarps) {
     // ------------------------------------------------------------------ de-quantiser warp (int8 wire)
     if constexpr (COPY && !A_MN) {
       if (p.dequant.q != nullptr)
         dequant_role<CG>(p, const_cast<__nv_bfloat16*>(reinterpret_cast<const __nv_bfloat16*>(p.a_ptr)), p.a_row_stride,
-                         p.a_group_stride, mt_count);
+                         p.a_group_stride, mt_count, ctl);
       if (trace != nullptr && lane == 0) trace[5] = global_timer_ns();
     }
   } else {

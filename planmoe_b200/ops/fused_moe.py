@@ -90,6 +90,16 @@ class _BufferSet:
         self.want_views = [self.want_dev[i:i + 1] for i in range(N_PHASES)]
         self.bases_host = self.block.bases_host   # peers' base addresses, for tensor maps over their buffers
         self.held = False
+        if T.debug_guards():
+            # debug: receive buffers start as NaN (bf16) / 0xFF (int8 rows), so a slot that no sender wrote is
+            # visible in the first step's output; the flags behind them stay zero
+            data_bytes = self.off_flags - self.block.offset
+            raw = self.block.tensor(torch.uint8, (data_bytes,))
+            raw.fill_(0xFF)                            # 0xFFFF is a bf16 NaN
+            if tr.world > 1 and not tr.emulated:
+                torch.cuda.synchronize()
+                import torch.distributed as dist
+                dist.barrier(group=tr.group)           # nobody sends before every rank has finished poisoning
 
     def off_of(self, phase):
         """Heap offset of the bf16 receive buffer the given exchange fills."""

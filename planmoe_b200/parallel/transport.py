@@ -43,6 +43,17 @@ def default_budget_ms():
     return int(os.environ.get('PLANMOE_WAIT_BUDGET_MS', '20000'))
 
 
+def debug_guards():
+    """PLANMOE_DEBUG_GUARDS=1: every heap block is allocated between two guard bands filled with a canary pattern
+    that ``Transport.check()`` verifies, and the fused layer's receive buffers start out filled with NaN so that a
+    slot nobody wrote shows up in the output instead of reading as stale zeros.  Stands in for a memory checker."""
+    return os.environ.get('PLANMOE_DEBUG_GUARDS', '0') == '1'
+
+
+_GUARD_BYTES = 1024
+_CANARY = 0xA5
+
+
 class HeapBlock:
     """A block of the symmetric heap: same offset on every rank."""
     __slots__ = ('segment', 'offset', 'nbytes', 'transport')
@@ -96,6 +107,7 @@ class Transport:
         self.segment_bytes = int(os.environ.get('PLANMOE_HEAP_MB', '1024')) << 20
         self._a2a = None
         self._peers = None      # emulation: list of sibling transports
+        self._guards = []       # (segment, offset of the lower guard, inner bytes) of guarded blocks
 
     # -- heap -------------------------------------------------------------------------------
     def _new_segment(self, nbytes):
@@ -111,6 +123,26 @@ class Transport:
 
     def alloc(self, nbytes):
         """Collective: every rank must call with the same sizes in the same order."""
+        if debug_guards():
+            inner = (int(nbytes) + _ALIGN - 1) // _ALIGN * _ALIGN
+            outer = self._alloc_raw(inner + 2 * _GUARD_BYTES)
+            blk = HeapBlock(self, outer.segment, outer.offset + _GUARD_BYTES, inner)
+            for off in (outer.offset, outer.offset + _GUARD_BYTES + inner):
+                HeapBlock(self, outer.segment, off, _GUARD_BYTES).tensor(torch.uint8, (_GUARD_BYTES,)).fill_(_CANARY)
+            self._guards.append((outer.segment, outer.offset, inner))
+            return blk
+        return self._alloc_raw(nbytes)
+
+    def check_guards(self):
+        """Raise if a guard band around any heap block of this rank was overwritten (by any rank)."""
+        for seg, off, inner in self._guards:
+            for at, name in ((off, 'below'), (off + _GUARD_BYTES + inner, 'above')):
+                band = HeapBlock(self, seg, at, _GUARD_BYTES).tensor(torch.uint8, (_GUARD_BYTES,))
+                if not bool((band == _CANARY).all()):
+                    raise TransportError("rank %d: guard band %s heap block at offset %d (segment %d) was overwritten"
+                                         % (self.rank, name, off + _GUARD_BYTES, seg))
+
+    def _alloc_raw(self, nbytes):
         nbytes = (int(nbytes) + _ALIGN - 1) // _ALIGN * _ALIGN
         if self.emulated and self._peers is not None and self is not self._peers[0]:
             raise TransportError("emulated transports allocate through rank 0 (alloc_all)")
@@ -137,6 +169,8 @@ class Transport:
             self.status.clear()
             raise TransportError("rank %d: %s (details: %s)" % (
                 self.rank, STATUS_NAMES.get(st[0], 'error %d' % st[0]), st[1:4]))
+        if self._guards:
+            self.check_guards()
 
     # -- collectives --------------------------------------------------------------------------
     def all_to_all(self, t, algo='flat', var_len=None, heap_out=False):

@@ -264,14 +264,17 @@ def test_integration_helpers():
     assert out.shape == (2, 8, 32) and bias is None
     assert all(p.allreduce is False for p in layer.mlp.moe.experts.parameters())
     os.environ['MOE'] = '2'
+    os.environ['L_AUX_WT'] = '0.01'
     try:
         assert pf.build_ffn(0, 16, 32) is None
         moe = pf.build_ffn(1, 16, 32)
-        y = pf.ffn_forward(moe, torch.randn(6, 16))
+        moe.train()
+        y = pf.ffn_forward(moe, torch.randn(6, 16, requires_grad=True))
         total = pf.add_aux_loss(torch.tensor(1.0), sample_size=6)
         assert y.shape == (6, 16) and float(total) > 1.0
     finally:
         os.environ.pop('MOE')
+        os.environ.pop('L_AUX_WT')
     p = torch.nn.Parameter(torch.ones(3))
     p.grad = torch.tensor([1.0, float('inf'), float('nan')])
     os.environ['NO_OVERFLOW'] = '1'

@@ -164,6 +164,30 @@ def test_importance_order_kernel_matches_a_sort():
     assert rank[perm.long()].tolist() == list(range(3000))          # rank and perm are inverse permutations
 
 
+def test_debug_guards_and_poisoned_receive_buffers(monkeypatch):
+    """PLANMOE_DEBUG_GUARDS=1: heap blocks sit between canary bands and receive buffers start as NaN.  A correct
+    layer step leaves the canaries intact and produces finite numbers (every slot it reads was written); a write
+    just past a block, made from the host side through a view of the heap, is reported by check()."""
+    from planmoe_b200.parallel import transport
+    monkeypatch.setenv('PLANMOE_DEBUG_GUARDS', '1')
+    layer = _layer(2, 256, 256, 2, 1.0)
+    x = torch.randn(1024, 256, device='cuda').to(torch.bfloat16).requires_grad_(True)
+    for _ in range(3):
+        y = layer(x)
+        y.float().sum().backward()
+    tr = transport.get_transport(layer.group)
+    tr.check()
+    assert torch.isfinite(y.float()).all() and torch.isfinite(x.grad.float()).all()
+    blk = tr.alloc(4096)
+    from planmoe_b200.ops import native
+    past = native.lib().tensor_from_ptr(blk.local_ptr + blk.nbytes, 16, torch.cuda.current_device())
+    past.fill_(0)                                            # 16 bytes of the upper guard band
+    with pytest.raises(transport.TransportError, match='guard band'):
+        tr.check()
+    past.fill_(0xA5)
+    tr.check()
+
+
 def test_fused_layer_is_bit_reproducible_and_reuses_buffers():
     layer = _layer(2, 256, 256, 2, 1.0)
     x = torch.randn(1024, 256, device='cuda').to(torch.bfloat16)

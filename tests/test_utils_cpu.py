@@ -154,3 +154,34 @@ def test_pipeline_model_of_the_scheduler():
     order, pred = sc.rank_candidates({'fwd.dispatch': {'median_us': 80.}, 'fwd.gemm1': 60., 'fwd.gemm2': 40.,
                                       'fwd.combine_push': {'median_us': 80.}})
     assert order[0] in (4, 8) and set(order) == {1, 2, 4, 8}
+
+
+def test_checkpoint_reshards_sharded_experts_along_the_hidden_dim():
+    """Two experts on four ranks (two ranks per expert, hidden dim split) -> two ranks (whole experts) -> eight ranks
+    (four slices per expert) and back: every tensor survives, fc2's sliced bias included (odd output dim)."""
+    import torch
+    from planmoe_b200.utils import checkpoint as ck
+    E, M, H, O = 2, 6, 8, 5
+    torch.manual_seed(0)
+    full = {'gates.0.wg.weight': torch.randn(E, M),
+            'experts.batched_fc1_w': torch.randn(E, M, H), 'experts.batched_fc1_bias': torch.randn(E, H),
+            'experts.batched_fc2_w': torch.randn(E, H, O), 'experts.batched_fc2_bias': torch.randn(E, O)}
+    four = [ck.shard_expert_state(full, r, 4) for r in range(4)]
+    assert four[1]['experts.batched_fc1_w'].shape == (1, M, H // 2)
+    assert four[1]['experts.batched_fc2_w'].shape == (1, H // 2, O)
+    assert four[3]['experts.batched_fc2_bias'].shape == (1, 3)            # ceil(5 / 2), zero-padded
+    assert torch.equal(four[2]['experts.batched_fc1_bias'], full['experts.batched_fc1_bias'][1:2, :H // 2])
+    two = ck.reshard_state_dicts(four, 2, sharded_count=2)
+    for r in range(2):
+        for k in full:
+            want = full[k][r:r + 1] if k.startswith('experts.') else full[k]
+            assert torch.equal(two[r][k], want), (r, k)
+    eight = ck.reshard_state_dicts(four, 8, sharded_count=2)
+    assert eight[5]['experts.batched_fc1_w'].shape == (1, M, H // 4)
+    back = ck.reshard_state_dicts(eight, 4, sharded_count=4)
+    for r in range(4):
+        for k in full:
+            assert torch.equal(back[r][k], four[r][k]), (r, k)
+    import pytest
+    with pytest.raises(ValueError):
+        ck.shard_expert_state({'experts.something_else': torch.randn(2, 3)}, 0, 4)
