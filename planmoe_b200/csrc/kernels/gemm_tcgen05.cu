@@ -567,25 +567,29 @@ __device__ __forceinline__ void dequant_role(const KernelParams& p, __nv_bfloat1
                         p.status, 2000 + blk);
     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
     if (!ok) return;
-    // Two rows at a time, four 16-byte pieces per lane and row in flight (eight independent loads per lane), so
+    // Four rows at a time, four 16-byte pieces per lane and row in flight (sixteen independent loads per lane), so
     // that the warp streams instead of waiting for one load after the other.
+    constexpr int kRB = 4;
     const int pieces = d.M / 16;
-    for (int r = 0; r < nrows; r += 2) {
-      const bool two = r + 1 < nrows;
-      const uint8_t* src0 = qbase + ((size_t)g * p.M + row0 + r) * q_row;
-      const uint8_t* src1 = src0 + (two ? q_row : 0);
-      __nv_bfloat16* dst0 = a_base + (long long)g * a_group_stride + (long long)(row0 + r) * a_row_stride;
-      __nv_bfloat16* dst1 = dst0 + (two ? a_row_stride : 0);
-      const float2 sl0 = *reinterpret_cast<const float2*>(src0 + d.M);
-      const float2 sl1 = *reinterpret_cast<const float2*>(src1 + d.M);
+    for (int r = 0; r < nrows; r += kRB) {
+      const uint8_t* src[kRB];
+      __nv_bfloat16* dstp[kRB];
+      float2 sl[kRB];
+#pragma unroll
+      for (int b = 0; b < kRB; ++b) {
+        const int rr = min(r + b, nrows - 1);                    // rows past the end repeat the last one (not stored)
+        src[b] = qbase + ((size_t)g * p.M + row0 + rr) * q_row;
+        dstp[b] = a_base + (long long)g * a_group_stride + (long long)(row0 + rr) * a_row_stride;
+        sl[b] = *reinterpret_cast<const float2*>(src[b] + d.M);
+      }
       for (int v0 = 0; v0 < pieces; v0 += 128) {
-        uint4 raw[2][4];
+        uint4 raw[kRB][4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int v = v0 + i * 32 + lane;
           if (v < pieces) {
-            raw[0][i] = *reinterpret_cast<const uint4*>(src0 + (size_t)v * 16);
-            raw[1][i] = *reinterpret_cast<const uint4*>(src1 + (size_t)v * 16);
+#pragma unroll
+            for (int b = 0; b < kRB; ++b) raw[b][i] = *reinterpret_cast<const uint4*>(src[b] + (size_t)v * 16);
           }
         }
 #pragma unroll
@@ -593,21 +597,20 @@ __device__ __forceinline__ void dequant_role(const KernelParams& p, __nv_bfloat1
           const int v = v0 + i * 32 + lane;
           if (v >= pieces) continue;
 #pragma unroll
-          for (int rr = 0; rr < 2; ++rr) {
-            if (rr == 1 && !two) continue;
-            const float2 sl = rr == 0 ? sl0 : sl1;
-            const uint32_t w[4] = {raw[rr][i].x, raw[rr][i].y, raw[rr][i].z, raw[rr][i].w};
+          for (int b = 0; b < kRB; ++b) {
+            if (r + b >= nrows) continue;
+            const uint32_t w[4] = {raw[b][i].x, raw[b][i].y, raw[b][i].z, raw[b][i].w};
             uint32_t o[8];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              const float f0 = fmaf((float)(w[j] & 0xffu), sl.x, sl.y);
-              const float f1 = fmaf((float)((w[j] >> 8) & 0xffu), sl.x, sl.y);
-              const float f2 = fmaf((float)((w[j] >> 16) & 0xffu), sl.x, sl.y);
-              const float f3 = fmaf((float)(w[j] >> 24), sl.x, sl.y);
+              const float f0 = fmaf((float)(w[j] & 0xffu), sl[b].x, sl[b].y);
+              const float f1 = fmaf((float)((w[j] >> 8) & 0xffu), sl[b].x, sl[b].y);
+              const float f2 = fmaf((float)((w[j] >> 16) & 0xffu), sl[b].x, sl[b].y);
+              const float f3 = fmaf((float)(w[j] >> 24), sl[b].x, sl[b].y);
               o[2 * j] = pack_bf16(f0, f1);
               o[2 * j + 1] = pack_bf16(f2, f3);
             }
-            __nv_bfloat16* dst = (rr == 0 ? dst0 : dst1) + (size_t)v * 16;
+            __nv_bfloat16* dst = dstp[b] + (size_t)v * 16;
             reinterpret_cast<uint4*>(dst)[0] = make_uint4(o[0], o[1], o[2], o[3]);
             reinterpret_cast<uint4*>(dst)[1] = make_uint4(o[4], o[5], o[6], o[7]);
           }

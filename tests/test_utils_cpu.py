@@ -185,3 +185,29 @@ def test_checkpoint_reshards_sharded_experts_along_the_hidden_dim():
     import pytest
     with pytest.raises(ValueError):
         ck.shard_expert_state({'experts.something_else': torch.randn(2, 3)}, 0, 4)
+
+
+def test_config_object_resolves_kwargs_and_documents_every_switch():
+    import os
+    import re
+    import subprocess
+    import pytest
+    from planmoe_b200.utils import config as cf
+    cfg = cf.MoEConfig.from_kwargs(gate_type={'type': 'top', 'k': 2}, model_dim=16,
+                                   experts={'type': 'ffn', 'count_per_node': 2, 'hidden_size_per_expert': 8},
+                                   a2a_ffn_overlap_degree='auto', comm_name='pipe', pad_samples=True)
+    layer = cfg.build()
+    back = cf.MoEConfig.from_layer(layer)
+    assert back.comm_name == 'pipe' and back.a2a_ffn_overlap_degree == 'auto' and back.model_dim == 16
+    with pytest.raises(Exception, match='Unrecognized argument'):
+        cf.MoEConfig.from_kwargs(model_dim=16, bogus=1)
+    with pytest.raises(AssertionError):
+        cf.MoEConfig.from_kwargs(model_dim=16, a2a_ffn_overlap_degree=64)
+    # every PLANMOE_* switch that the sources read is in the documentation table
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run(['grep', '-rhoE', r"(environ\.get\(|getenv\()['\"]PLANMOE_[A-Z0-9_]+", os.path.join(root, 'planmoe_b200')],
+                         stdout=subprocess.PIPE, text=True).stdout
+    used = set(re.findall(r'PLANMOE_[A-Z0-9_]+', out))
+    missing = used - set(cf.ENV)
+    assert not missing, missing
+    assert 'PLANMOE_WAIT_BUDGET_MS' in cf.runtime_env()
