@@ -181,7 +181,8 @@ std::vector<Tensor> dispatch_gate_grad_scaled_op(const Tensor& disp, const Tenso
 
 // The same for expert outputs that arrived as uint8 rows with a (scale, low) pair per 128 columns and row (the int8
 // push epilogue's layout): `disp_ptr` uint8 [E * C, M], `scales_ptr` fp32 [M / 128][group_rows][2].  `gates` may be
-// absent (then no scaled copies are produced and the second result is empty).
+// absent (then no scaled copies are produced and the second result is empty).  The scaled copies come out as int8 wire
+// rows, uint8 [S * K, M + 16]: M quantised bytes + {scale, low, 0, 0}.
 std::vector<Tensor> dispatch_gate_grad_q8_op(int64_t disp_ptr, int64_t scales_ptr, int64_t group_rows, const Tensor& dy,
                                              const Tensor& idx, const Tensor& loc, const c10::optional<Tensor>& gates,
                                              int64_t C, bool want_scaled) {
@@ -190,16 +191,16 @@ std::vector<Tensor> dispatch_gate_grad_q8_op(int64_t disp_ptr, int64_t scales_pt
   const int K = idx.size(0), S = idx.size(1), M = dy.size(1);
   c10::cuda::CUDAGuard guard(dy.device());
   Tensor out = torch::empty({K, S}, dy.options().dtype(at::kFloat));
-  Tensor scaled;
+  Tensor scaled;       // int8 wire rows [S * K, M + 16] of gate * dy (rows of picks without a slot stay unwritten)
   if (want_scaled) {
     TORCH_CHECK(gates.has_value() && gates->defined(), "scaled copies need the gates");
-    scaled = torch::empty({(int64_t)S * K, (int64_t)M}, dy.options());
+    scaled = torch::empty({(int64_t)S * K, (int64_t)M + 16}, dy.options().dtype(at::kByte));
   }
   DISPATCH_FLOAT(dy, "dispatch_gate_grad_q8", [&] {
     launch_gate_grad<scalar_t>(reinterpret_cast<const scalar_t*>(disp_ptr), reinterpret_cast<const scalar_t*>(dy.data_ptr()),
                                idx.data_ptr<int>(), loc.data_ptr<int>(), out.data_ptr<float>(), opt_f32(gates),
-                               want_scaled ? reinterpret_cast<scalar_t*>(scaled.data_ptr()) : nullptr, K, S, M, C,
-                               cur_stream(), reinterpret_cast<const float*>(scales_ptr), group_rows);
+                               nullptr, K, S, M, C, cur_stream(), reinterpret_cast<const float*>(scales_ptr), group_rows,
+                               want_scaled ? scaled.data_ptr<uint8_t>() : nullptr);
   });
   return {out, want_scaled ? scaled : Tensor()};
 }

@@ -353,12 +353,25 @@ __global__ void __launch_bounds__(kRowThreads, 8)
 gate_grad_kernel(const T* __restrict__ disp, const T* __restrict__ dy, const int* __restrict__ idx,
                  const int* __restrict__ loc, float* __restrict__ dgates, const float* __restrict__ gates,
                  T* __restrict__ scaled, int K, int S, int M, int C, const float* __restrict__ disp_scales,
-                 long long group_rows) {
+                 long long group_rows, unsigned char* __restrict__ scaled_q) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int V = Vec16<T>::N;
   const int nvec = M / V;
   for (int t = blockIdx.x * kRowWarps + warp; t < S; t += gridDim.x * kRowWarps) {
     const T* b = dy + (size_t)t * M;
+    // int8 wire rows of the gate-weighted dy: gates are non-negative, so gate * dy quantises to the same bytes as
+    // dy itself with range and low scaled by the gate; the row's range is found once per token
+    float qlo = 0.f, qinv = 0.f, qrange = 0.f;
+    if (scaled_q != nullptr) {
+      float lo = INFINITY, hi = -INFINITY;
+      for (int v = lane; v < nvec; v += 32) {
+        Pack<T> pb = ld16(b + v * V);
+#pragma unroll
+        for (int i = 0; i < V; ++i) { const float f = to_f32(pb.v[i]); lo = fminf(lo, f); hi = fmaxf(hi, f); }
+      }
+      lo = warp_min(lo); hi = warp_max(hi);
+      qlo = lo; qrange = hi - lo; qinv = qrange > 0.f ? 255.f / qrange : 0.f;
+    }
     for (int k = 0; k < K; ++k) {
       const int e = idx[(size_t)k * S + t], l = loc[(size_t)k * S + t];
       float acc = 0.f;
@@ -371,10 +384,12 @@ gate_grad_kernel(const T* __restrict__ disp, const T* __restrict__ dy, const int
           const float2* sc = reinterpret_cast<const float2*>(disp_scales);
           const float gw = gates != nullptr ? gates[(size_t)k * S + t] : 1.f;
           T* o = scaled != nullptr ? scaled + ((size_t)t * K + k) * M : nullptr;
+          unsigned char* oq = scaled_q != nullptr ? scaled_q + ((size_t)t * K + k) * ((size_t)M + 16) : nullptr;
           for (int v = lane; v < M / 16; v += 32) {
             const float2 sl = sc[(size_t)(v >> 3) * group_rows + slot];
             const uint4 raw = *reinterpret_cast<const uint4*>(aq + (size_t)v * 16);
             const unsigned char* q = reinterpret_cast<const unsigned char*>(&raw);
+            alignas(16) unsigned char qo[16];
 #pragma unroll
             for (int h = 0; h < 16 / V; ++h) {
               Pack<T> pb = ld16(b + (size_t)v * 16 + h * V), po;
@@ -383,10 +398,14 @@ gate_grad_kernel(const T* __restrict__ disp, const T* __restrict__ dy, const int
                 const float fb = to_f32(pb.v[i]);
                 acc += fmaf(sl.x, (float)q[h * V + i], sl.y) * fb;
                 po.v[i] = from_f32<T>(gw * fb);
+                qo[h * V + i] = (unsigned char)fminf(fmaxf(rintf((fb - qlo) * qinv), 0.f), 255.f);
               }
               if (o != nullptr) st16(o + (size_t)v * 16 + h * V, po);
             }
+            if (oq != nullptr) reinterpret_cast<uint4*>(oq)[v] = *reinterpret_cast<uint4*>(qo);
           }
+          if (oq != nullptr && lane == 0)
+            *reinterpret_cast<float4*>(oq + M) = make_float4(gw * qrange * (1.f / 255.f), gw * qlo, 0.f, 0.f);
         } else if (scaled != nullptr) {
           const float gw = gates[(size_t)k * S + t];
           T* o = scaled + ((size_t)t * K + k) * M;
@@ -417,12 +436,12 @@ gate_grad_kernel(const T* __restrict__ disp, const T* __restrict__ dy, const int
 template <class T>
 void launch_gate_grad(const T* disp, const T* dy, const int* idx, const int* loc, float* dgates,
                       const float* gates, T* scaled, int K, int S, int M, int C, cudaStream_t stream,
-                      const float* disp_scales, long long group_rows) {
+                      const float* disp_scales, long long group_rows, unsigned char* scaled_q) {
   int ctas = (S + kRowWarps - 1) / kRowWarps;
   if (ctas > 148 * 8) ctas = 148 * 8;
   if (ctas < 1) ctas = 1;
   gate_grad_kernel<T><<<ctas, kRowThreads, 0, stream>>>(disp, dy, idx, loc, dgates, gates, scaled, K, S, M, C,
-                                                        disp_scales, group_rows);
+                                                        disp_scales, group_rows, scaled_q);
 }
 
 #define INSTANTIATE(T)                                                                             \
@@ -432,7 +451,7 @@ void launch_gate_grad(const T* disp, const T* dy, const int* idx, const int* loc
                                       const float*, T*, int, int, int, int, const WaitArgs*,       \
                                       cudaStream_t, long long);                                    \
   template void launch_gate_grad<T>(const T*, const T*, const int*, const int*, float*, const float*, \
-                                    T*, int, int, int, int, cudaStream_t, const float*, long long);
+                                    T*, int, int, int, int, cudaStream_t, const float*, long long, unsigned char*);
 INSTANTIATE(float)
 INSTANTIATE(__nv_bfloat16)
 INSTANTIATE(__half)

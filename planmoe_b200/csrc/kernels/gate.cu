@@ -298,10 +298,13 @@ importance_key_kernel(const T* __restrict__ logits, int S, int E, float* __restr
   key[t] = 1.f / sum;
 }
 
+// 32 tokens per CTA, eight threads per token: each thread counts over an eighth of every key tile, the eight
+// counts are added by shuffles.  S / 32 CTAs keep the whole machine busy for a few thousand tokens.
 __global__ void __launch_bounds__(256)
 importance_rank_kernel(const float* __restrict__ key, int S, int* __restrict__ rank, int* __restrict__ perm) {
   __shared__ float tile[1024];
-  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  const int part = threadIdx.x & 7;
+  const int t = blockIdx.x * 32 + (threadIdx.x >> 3);
   const float mine = t < S ? key[t] : 0.f;
   int before = 0;
   for (int base = 0; base < S; base += 1024) {
@@ -309,19 +312,22 @@ importance_rank_kernel(const float* __restrict__ key, int S, int* __restrict__ r
     for (int i = threadIdx.x; i < 1024; i += blockDim.x) tile[i] = base + i < S ? key[base + i] : -INFINITY;
     __syncthreads();
     const int n = min(1024, S - base);
-    for (int i = 0; i < n; ++i) {
+    for (int i = part; i < n; i += 8) {
       const float other = tile[i];
       before += (other > mine || (other == mine && base + i < t)) ? 1 : 0;
     }
   }
-  if (t < S) { rank[t] = before; perm[before] = t; }
+  before += __shfl_xor_sync(0xffffffffu, before, 1);
+  before += __shfl_xor_sync(0xffffffffu, before, 2);
+  before += __shfl_xor_sync(0xffffffffu, before, 4);
+  if (part == 0 && t < S) { rank[t] = before; perm[before] = t; }
 }
 
 template <class T>
 void launch_importance_order(const T* logits, int S, int E, float* key, int* rank, int* perm, cudaStream_t stream) {
   if (S <= 0) return;
   importance_key_kernel<T><<<(S + 255) / 256, 256, 0, stream>>>(logits, S, E, key);
-  importance_rank_kernel<<<(S + 255) / 256, 256, 0, stream>>>(key, S, rank, perm);
+  importance_rank_kernel<<<(S + 31) / 32, 256, 0, stream>>>(key, S, rank, perm);
 }
 template void launch_importance_order<float>(const float*, int, int, float*, int*, int*, cudaStream_t);
 template void launch_importance_order<__nv_bfloat16>(const __nv_bfloat16*, int, int, float*, int*, int*, cudaStream_t);

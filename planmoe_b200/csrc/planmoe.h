@@ -55,11 +55,12 @@ void launch_gather_rows(const void* disp, const float* scale_bias, const int* id
                         const float* gates, T* out, int K, int S, int M, int C, const WaitArgs* wait,
                         cudaStream_t stream, long long group_rows = 0);
 // `gates` / `scaled` optional: also write scaled[t * K + k] = gates[k][t] * dy[t]
-// disp_scales != null: disp holds uint8 rows with fp32 (scale, low) per (128-column group, row), [M / 128][E * C]
+// disp_scales != null: disp holds uint8 rows with fp32 (scale, low) per (128-column group, row), [M / 128][E * C];
+// scaled_q (int8 mode only): the gate-weighted dy rows as int8 wire rows [S * K][M + 16] instead of `scaled`
 template <class T>
 void launch_gate_grad(const T* disp, const T* dy, const int* idx, const int* loc, float* dgates,
                       const float* gates, T* scaled, int K, int S, int M, int C, cudaStream_t stream,
-                      const float* disp_scales = nullptr, long long group_rows = 0);
+                      const float* disp_scales = nullptr, long long group_rows = 0, unsigned char* scaled_q = nullptr);
 
 // ---- kernels/gate.cu -------------------------------------------------------------------------
 int gate_workspace_blocks(int S);

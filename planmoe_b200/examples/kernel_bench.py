@@ -6,7 +6,8 @@
 Cases: gemm_fwd (K-major x MN-major, bias+GELU epilogue), gemm_push (same GEMM, rows stored into the
 symmetric heap with flags), gemm_dgrad (K x K, activation-backward
 epilogue), gemm_wgrad (MN x MN), cublas (torch.bmm of the forward shape, for comparison), scatter
-(dispatch), gather (combine), gate (fused gate), int8 (encode + decode), all.  Shapes are the
+(dispatch), gather (combine), gate (fused gate), int8 (encode + decode), misc (the small kernels: wire-row int8
+encoder, batch-prioritised order, slot-map build / remap, cumsum, flag wait, delay, allocation-free column sum), all.  Shapes are the
 per-rank shapes of the pre_test layer: 2 experts x 8192 rows, model_dim = hidden = 2048
 (``--small`` quarters the rows so that a profiler capture stays short).  Between timed
 iterations a 256 MiB buffer is written to flush L2.  One JSON line per case.
@@ -146,6 +147,37 @@ def main():
     if want('colsum'):
         ms, best = timed(lambda: lib.colsum(dy), args.iters, flush)
         report('colsum', ms, best, bytes_=dy.numel() * 2.0)
+    if want('misc'):
+        import ctypes
+        ms, best = timed(lambda: lib.int8_rows_encode(tok), args.iters, flush)
+        report('int8_rows_encode', ms, best, bytes_=tok.numel() * 3.0)
+        ms, best = timed(lambda: lib.importance_order(logits), args.iters, flush)
+        report('importance_order', ms, best)
+        rank, perm = lib.importance_order(logits)
+        sm2 = smap.clone()
+        ms, best = timed(lambda: lib.remap_slot_map(sm2, perm, K), args.iters, flush)
+        report('remap_slot_map', ms, best)
+        ms, best = timed(lambda: lib.build_slot_map(idx, loc, E, C), args.iters, flush)
+        report('build_slot_map', ms, best)
+        mask = (torch.rand(S, 16, device=dev) > 0.5).int()
+        ms, best = timed(lambda: lib.cumsum_sub_one(mask), args.iters, flush)
+        report('cumsum_sub_one', ms, best)
+        flags = torch.ones(64, dtype=torch.int64, device=dev)
+        st = gemm._status_word()
+        ms, best = timed(lambda: lib.wait_flags(flags.data_ptr(), 64, 1, 100, st.device_ptr()), args.iters, flush)
+        report('wait_flags(all set)', ms, best)
+        ms, best = timed(lambda: lib.delay(20000), args.iters, flush)
+        report('delay(20us)', ms, best)
+        fn = ctypes.CDLL(lib.__file__).planmoe_colsum_bf16_noalloc
+        fn.restype = ctypes.c_int
+        fn.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_int, ctypes.c_longlong,
+                       ctypes.c_longlong, ctypes.c_void_p]
+        small = dy[:, :2048].contiguous()
+        res = torch.empty(G, H, device=dev)
+        stream = torch.cuda.current_stream().cuda_stream
+        ms, best = timed(lambda: fn(small.data_ptr(), res.data_ptr(), G, small.size(1), H, small.stride(1), small.stride(0),
+                                    stream), args.iters, flush)
+        report('colsum_noalloc', ms, best, bytes_=small.numel() * 2.0)
 
 
 if __name__ == '__main__':

@@ -371,9 +371,8 @@ class _FusedExperts(torch.autograd.Function):
             # expert outputs are held as int8 rows: the gate gradient de-quantises them on the fly; the gate-weighted
             # dY rows are quantised for the wire like the tokens were
             with stage('bwd.gate_grad'):
-                dgates, scaled = lib.dispatch_gate_grad_q8(bs.local_ptr(bs.off_y), bs.local_ptr(bs.off_y + rows_y * O),
-                                                           rows_y, dout, idx, loc, gates_f, C, True)
-                send_src = lib.int8_rows_encode(scaled)
+                dgates, send_src = lib.dispatch_gate_grad_q8(bs.local_ptr(bs.off_y), bs.local_ptr(bs.off_y + rows_y * O),
+                                                             rows_y, dout, idx, loc, gates_f, C, True)
             send_gates, send_K = None, 1
         elif postscore and _fuse_send(W) and O * 2 <= MAX_ROW_BYTES:
             # The fused send moves rows with the bulk-copy engine, which cannot scale them: the gate-gradient
