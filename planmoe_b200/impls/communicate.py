@@ -45,7 +45,6 @@ def barrier(group=None):
         dist.barrier(group=group)
 
 
-TUTEL_GROUPING_CACHE = {}
 TUTEL_SKIP_A2A = int(os.environ.get('SKIP_A2A', 0)) > 0
 
 
@@ -58,18 +57,91 @@ class ParallelPropStorage:
             self.model_rank, self.model_size))
 
 
-def _rendezvous(backend):
-    """Initialise the default process group from torchrun or OpenMPI environment."""
-    if _dist_ready():
-        return
-    env = os.environ
-    if 'LOCAL_RANK' not in env and 'OMPI_COMM_WORLD_SIZE' in env:
-        dist.init_process_group(
-            backend=backend,
-            init_method='tcp://%s:%s' % (env['MASTER_ADDR'], env.get('MASTER_PORT', '23456')),
-            rank=int(env['OMPI_COMM_WORLD_RANK']), world_size=int(env['OMPI_COMM_WORLD_SIZE']))
-    else:
-        dist.init_process_group(backend=backend)
+def grid_of(world, rank, group_count):
+    """Pure arithmetic of the (data, model) grid: ranks are laid out row-major as ``[group_count][model_size]``.
+
+    Returns ``(group_count, model_size, data_rank, model_rank, rows, cols)`` where ``rows[d]`` lists the ranks of
+    model group ``d`` (contiguous) and ``cols[m]`` those of data group ``m`` (strided).  A negative ``group_count``
+    asks for model groups of ``-group_count`` ranks.
+    """
+    if group_count < 0:
+        group_count = world // -group_count
+    assert group_count > 0 and world % group_count == 0, \
+        "Expected to evenly divide devices into %d groups, while the world size of current " \
+        "session is %d." % (group_count, world)
+    model_size = world // group_count
+    rows = [list(range(d * model_size, (d + 1) * model_size)) for d in range(group_count)]
+    cols = [list(range(m, world, model_size)) for m in range(model_size)]
+    data_rank, model_rank = divmod(rank, model_size)
+    return group_count, model_size, data_rank, model_rank, rows, cols
+
+
+class _World:
+    """What this process knows about the job: the one backend it was told to use, its place in the launch
+    (torchrun or OpenMPI variables) and every grid it has already built."""
+
+    def __init__(self):
+        self.backend = None
+        self.grids = {}
+
+    def fix_backend(self, asked):
+        if asked:
+            if self.backend is None:
+                self.backend = asked
+            assert self.backend == asked, \
+                "Only 1 backend type is allowed, get: %s v.s. %s" % (self.backend, asked)
+        return self.backend
+
+    @staticmethod
+    def launch_slot():
+        """(rank, world, local_rank) as the launcher exported them, or None outside a launcher."""
+        env = os.environ
+        if 'LOCAL_RANK' in env:
+            return int(env.get('RANK', 0)), int(env.get('WORLD_SIZE', 1)), int(env['LOCAL_RANK'])
+        if 'OMPI_COMM_WORLD_SIZE' in env:
+            return (int(env['OMPI_COMM_WORLD_RANK']), int(env['OMPI_COMM_WORLD_SIZE']),
+                    int(env.get('OMPI_COMM_WORLD_LOCAL_RANK', 0)))
+        return None
+
+    def connect(self, backend):
+        """Bring the default process group up when asked to and not up yet; tell whether one exists."""
+        if _dist_ready() or not backend:
+            return _dist_ready()
+        env, slot = os.environ, self.launch_slot()
+        try:
+            if slot is not None and 'LOCAL_RANK' not in env:          # OpenMPI: no env:// variables exported
+                dist.init_process_group(
+                    backend=backend, rank=slot[0], world_size=slot[1],
+                    init_method='tcp://%s:%s' % (env['MASTER_ADDR'], env.get('MASTER_PORT', '23456')))
+            else:
+                dist.init_process_group(backend=backend)
+        except ValueError:                                            # env:// without its variables: a lone process
+            return False
+        return True
+
+    def device_for(self, backend, local_rank):
+        if backend is None:
+            return None
+        if backend == 'gloo':
+            return torch.device('cpu')
+        if backend == 'nccl':
+            dev = torch.device('cuda', min(local_rank, max(torch.cuda.device_count(), 1) - 1))
+            if torch.cuda.is_available():
+                torch.cuda.set_device(dev)
+            return dev
+        raise Exception('Unsupported backend type: %s' % backend)
+
+
+_WORLD = _World()
+
+
+def _pick_group(memberships, mine, whole_world):
+    """Every rank must call ``new_group`` for every membership list, in the same order; keep the one that
+    contains this rank.  A single list covering the world is the default group itself."""
+    if len(memberships) == 1:
+        return whole_world
+    made = [dist.new_group(ranks=r) for r in memberships]
+    return made[mine]
 
 
 def create_groups_from_world(group_count, include_init=None):
@@ -77,76 +149,30 @@ def create_groups_from_world(group_count, include_init=None):
     data groups.  ``group_count < 0`` means "groups of size -group_count".
 
     ``include_init`` names the backend ('nccl' | 'gloo') and also initialises the default
-    process group when it is not up yet.
+    process group when it is not up yet.  Results are cached per requested ``group_count``.
     """
-    backend = TUTEL_GROUPING_CACHE.get('', include_init)
-    if include_init:
-        assert backend == include_init, \
-            "Only 1 backend type is allowed, get: %s v.s. %s" % (backend, include_init)
-        TUTEL_GROUPING_CACHE[''] = backend
-    if group_count in TUTEL_GROUPING_CACHE:
-        return TUTEL_GROUPING_CACHE[group_count]
+    backend = _WORLD.fix_backend(include_init)
+    if group_count in _WORLD.grids:
+        return _WORLD.grids[group_count]
 
-    env = os.environ
-    is_distributed = True
-    try:
-        if include_init:
-            _rendezvous(backend)
-        if not _dist_ready():
-            raise ValueError("no process group")
-        if 'LOCAL_RANK' not in env and 'OMPI_COMM_WORLD_LOCAL_RANK' in env:
-            local_rank = int(env['OMPI_COMM_WORLD_LOCAL_RANK'])
-        else:
-            local_rank = int(env.get('LOCAL_RANK', 0))
-        world, rank = dist.get_world_size(), dist.get_rank()
-    except ValueError:
-        world, rank, local_rank, is_distributed = 1, 0, 0, False
-
-    requested = group_count
-    if group_count < 0:
-        group_count = world // -group_count
-    assert group_count > 0 and world % group_count == 0, \
-        "Expected to evenly divide devices into %d groups, while the world size of current " \
-        "session is %d." % (group_count, world)
-
-    model_size = world // group_count
-    model_rank, data_rank = rank % model_size, rank // model_size
-
-    model_group = data_group = global_group = None
-    if is_distributed:
-        model_group = data_group = global_group = dist.group.WORLD
-        if model_size != world:
-            for g in range(group_count):
-                ranks = list(range(g * model_size, (g + 1) * model_size))
-                pg = dist.new_group(ranks=ranks)
-                if g == data_rank:
-                    model_group = pg
-        if group_count != world:
-            for m in range(model_size):
-                ranks = list(range(m, world, model_size))
-                pg = dist.new_group(ranks=ranks)
-                if m == model_rank:
-                    data_group = pg
+    live = _WORLD.connect(include_init)
+    slot = _WORLD.launch_slot()
+    world, rank = (dist.get_world_size(), dist.get_rank()) if live else (1, 0)
+    local_rank = slot[2] if (live and slot is not None) else 0
+    groups, model_size, data_rank, model_rank, rows, cols = grid_of(world, rank, group_count)
 
     res = ParallelPropStorage()
+    res.is_distributed = live
     res.global_size, res.global_rank = world, rank
-    res.group_count, res.data_rank = group_count, data_rank
+    res.group_count, res.data_rank = groups, data_rank
     res.model_size, res.model_rank = model_size, model_rank
-    if backend == 'nccl':
-        ndev = max(torch.cuda.device_count(), 1)
-        res.local_device = torch.device('cuda', min(local_rank, ndev - 1))
-        if torch.cuda.is_available():
-            torch.cuda.set_device(res.local_device)
-    elif backend == 'gloo':
-        res.local_device = torch.device('cpu')
-    elif backend is None:
-        res.local_device = None
-    else:
-        raise Exception('Unsupported backend type: %s' % backend)
-    res.data_group, res.model_group, res.global_group = data_group, model_group, global_group
-    res.is_distributed = is_distributed
-    res.dist_print = (lambda *a: print(*a)) if rank == 0 else (lambda *a: None)
-    TUTEL_GROUPING_CACHE[requested] = res
+    res.local_device = _WORLD.device_for(backend, local_rank)
+    whole = dist.group.WORLD if live else None
+    res.global_group = whole
+    res.model_group = _pick_group(rows, data_rank, whole) if live else None
+    res.data_group = _pick_group(cols, model_rank, whole) if live else None
+    res.dist_print = print if rank == 0 else (lambda *a, **k: None)
+    _WORLD.grids[group_count] = res
     return res
 
 

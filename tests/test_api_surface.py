@@ -283,3 +283,17 @@ def test_integration_helpers():
     finally:
         os.environ.pop('NO_OVERFLOW')
     assert p.grad.tolist() == [1.0, 0.0, 0.0]
+
+
+def test_grid_of_rows_and_columns():
+    from planmoe_b200.impls.communicate import grid_of
+    g, m, d, r, rows, cols = grid_of(8, 5, 2)
+    assert (g, m, d, r) == (2, 4, 1, 1)
+    assert rows == [[0, 1, 2, 3], [4, 5, 6, 7]] and cols == [[0, 4], [1, 5], [2, 6], [3, 7]]
+    assert 5 in rows[d] and 5 in cols[r]
+    g, m, d, r, rows, cols = grid_of(8, 3, -2)            # model groups of two ranks
+    assert (g, m, d, r) == (4, 2, 1, 1) and rows[1] == [2, 3] and cols[1] == [1, 3, 5, 7]
+    assert grid_of(1, 0, 1)[:4] == (1, 1, 0, 0)
+    import pytest
+    with pytest.raises(AssertionError):
+        grid_of(6, 0, 4)
