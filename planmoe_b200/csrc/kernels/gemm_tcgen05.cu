@@ -302,6 +302,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, Ctl* ct
   return true;
 }
 
+constexpr int kTraceSlots = 32;                    // u64 words of role trace per CTA
+constexpr int kTraceTiles = 12;                    // per-tile gate waits recorded in slots 8 .. 31
+
 __device__ __forceinline__ float rcp_approx(float x) {
   float r;
   asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
@@ -667,7 +670,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   Ctl* ctl = reinterpret_cast<Ctl*>(smem + G::kSmemRing + kSmemStaging + G::kCopyArea + kSmemBias + G::kScaleArea);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  unsigned long long* trace = p.trace != nullptr ? p.trace + (size_t)blockIdx.x * 8 : nullptr;
+  unsigned long long* trace = p.trace != nullptr ? p.trace + (size_t)blockIdx.x * kTraceSlots : nullptr;
   if (trace != nullptr && threadIdx.x == 0) trace[0] = global_timer_ns();
 
   const int mt_count = (p.M + BM * CG - 1) / (BM * CG);
@@ -704,6 +707,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       unsigned long long gate_wait_ns = 0;
+      int traced_tiles = 0;
       const unsigned long long gate_want = p.gate_want_ptr != nullptr ? *p.gate_want_ptr : p.gate_want;
       for (int tile = unit; tile < tiles && ok; tile += nunits) {
         const int nt = tile % nt_count;
@@ -729,7 +733,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
           if (!ok) { ctl->abort = 1; break; }
           fence_proxy_async();   // peers' generic-proxy stores -> this thread's async-proxy loads
-          if (trace != nullptr) gate_wait_ns += global_timer_ns() - tw0;
+          if (trace != nullptr) {
+            const unsigned long long tw1 = global_timer_ns();
+            gate_wait_ns += tw1 - tw0;
+            if (traced_tiles < kTraceTiles) {        // when this CTA asked for the tile's rows and when it had them
+              trace[8 + 2 * traced_tiles] = tw0;
+              trace[9 + 2 * traced_tiles] = tw1;
+              ++traced_tiles;
+            }
+          }
         }
         for (int kb = 0; kb < kb_total; ++kb) {
           ok = mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1u, ctl, p.budget_ns, p.status, 0, stage);
@@ -833,6 +845,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int etid = threadIdx.x - 64;            // 0..255
     uint32_t acc = 0, acc_phase = 0, iter = 0;
     bool ok = true;
+    long long epi_acc_clk = 0, epi_stage_clk = 0;  // trace: SM clocks spent waiting for the accumulator / the staging tile
+    const long long epi_t0 = trace != nullptr ? clock64() : 0ll;
     for (int tile = unit; tile < tiles && ok; tile += nunits) {
       const int nt = tile % nt_count;
       const int mt = permute_mt(p, (tile / nt_count) % mt_count);
@@ -858,8 +872,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
       // All epilogue warps take the same exit decision: a warp that timed out raises the flag of
       // this iteration's parity before the barrier, everyone reads it after the barrier.
+      const long long tq0 = trace != nullptr ? clock64() : 0ll;
       bool got = mbar_wait(smem_u32(&ctl->acc_full[acc]), acc_phase, ctl, p.budget_ns, p.status, 2, acc);
       got = __all_sync(0xffffffffu, got);
+      if (trace != nullptr) epi_acc_clk += clock64() - tq0;
       if (!got && lane == 0) ctl->epi_abort[iter & 1] = 1;
       epi_bar_sync();                              // also: previous tile's readers of bias_s are done
       if (ctl->epi_abort[iter & 1]) { ok = false; break; }
@@ -908,8 +924,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const int tile_row = m0 + q * 32;            // first row of this warp's 32-row slice
       auto stage_free = [&]() {
         if (p.tma_out) {
+          const long long ts0 = trace != nullptr ? clock64() : 0ll;
           if (lane == 0) bulk_wait_read_all();
           __syncwarp();
+          if (trace != nullptr) epi_stage_clk += clock64() - ts0;
         }
       };
       auto tma_out = [&](const CUtensorMap* map, int col, int row, int grp) {
@@ -1149,6 +1167,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
     }
     if (p.tma_out && lane == 0) bulk_wait_all();   // no bulk store of mine is in flight at teardown
+    if (trace != nullptr && ewarp == 0 && lane == 0) {
+      trace[6] = (unsigned long long)epi_acc_clk;
+      trace[7] = ((unsigned long long)(clock64() - epi_t0) << 32) | (unsigned long long)(epi_stage_clk & 0xffffffffll);
+    }
   }
 
   // ---------------------------------------------------------------------- teardown

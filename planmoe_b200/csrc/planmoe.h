@@ -165,8 +165,10 @@ struct GemmArgs {
   // flag [chunk * W + my_rank].  One launch then covers all pipeline chunks.
   int chunk_groups;
   unsigned long long budget_ns; int* status;
-  // Optional role trace, device u64 [grid][8] (ns of %globaltimer): [0] kernel entry, [1] / [2] copy role begin / end,
-  // [3] time the TMA producer spent waiting on gate flags, [4] kernel exit, [5] de-quantiser role end.
+  // Optional role trace, device u64 [grid][32] (ns of %globaltimer): [0] kernel entry, [1] / [2] copy role begin / end,
+  // [3] time the TMA producer spent waiting on gate flags, [4] kernel exit, [5] de-quantiser role end; in SM clocks,
+  // from the first epilogue warp: [6] waiting for accumulators, [7] (whole tile loop << 32) | waiting for staging tiles;
+  // [8 + 2i] / [9 + 2i]: when the TMA producer began / ended waiting for the rows of its i-th tile (i < 12).
   unsigned long long* trace;
   int max_ctas;                    // 0 = one per SM
   int cta_group;                   // 0 = automatic (gemm_cta_group), 1, or 2 (two-CTA clusters, 256 x 256 tiles)

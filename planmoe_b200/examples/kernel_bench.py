@@ -59,6 +59,8 @@ def main():
     ap.add_argument('--case', default='all')
     ap.add_argument('--iters', type=int, default=10)
     ap.add_argument('--small', action='store_true')
+    ap.add_argument('--trace', action='store_true',
+                    help='GEMM cases: one extra launch with the role trace; prints where the first epilogue warp waited')
     args = ap.parse_args()
     lib = native.lib()
     hbm, tf, how = peaks()
@@ -87,13 +89,33 @@ def main():
     cases = args.case.split(',')
     want = lambda c: 'all' in cases or c in cases  # noqa: E731
 
+    def traced(name, fn):
+        """fn(trace_ptr=...) launches one GEMM; report the epilogue's waits as fractions of its tile loop."""
+        if not args.trace:
+            return
+        tb = torch.zeros(296, 32, dtype=torch.int64, device=dev)
+        fn(trace_ptr=tb.data_ptr())
+        torch.cuda.synchronize()
+        t = tb[tb[:, 4] > 0]
+        loop = (t[:, 7] >> 32).float()
+        stage = (t[:, 7] & 0xffffffff).float()
+        acc = t[:, 6].float()
+        print(json.dumps({'case': name + '_trace', 'ctas': int(t.size(0)),
+                          'kernel_us_max': round(float((t[:, 4] - t[:, 0]).max()) / 1e3, 1),
+                          'epi_loop_mclk_mean': round(float(loop.mean()) / 1e6, 4),
+                          'wait_acc_frac': round(float((acc / loop).mean()), 3),
+                          'wait_staging_frac': round(float((stage / loop).mean()), 3)}), flush=True)
+
     if want('gemm_fwd'):
         ms, best = timed(lambda: gemm.grouped_gemm(x, False, w1, True, gemm.EPI_BIAS_ACT, 2, bias=b1, aux=pre, out=out),
                          args.iters, flush)
         report('gemm_fwd', ms, best, flops)
+        traced('gemm_fwd', lambda **kw: gemm.grouped_gemm(x, False, w1, True, gemm.EPI_BIAS_ACT, 2, bias=b1, aux=pre,
+                                                          out=out, **kw))
     if want('gemm_plain'):
         ms, best = timed(lambda: gemm.grouped_gemm(x, False, w1, True, out=out), args.iters, flush)
         report('gemm_plain', ms, best, flops)
+        traced('gemm_plain', lambda **kw: gemm.grouped_gemm(x, False, w1, True, out=out, **kw))
     if want('gemm_push'):
         # push epilogue with this rank's own heap as the destination (one rank: no NVLink traffic)
         from planmoe_b200.parallel import transport
@@ -109,9 +131,11 @@ def main():
         ms, best = timed(lambda: gemm.grouped_gemm(dy, False, w1, False, gemm.EPI_DACT, 2, aux=pre, out=out),
                          args.iters, flush)
         report('gemm_dgrad', ms, best, flops)
+        traced('gemm_dgrad', lambda **kw: gemm.grouped_gemm(dy, False, w1, False, gemm.EPI_DACT, 2, aux=pre, out=out, **kw))
     if want('gemm_wgrad'):
         ms, best = timed(lambda: gemm.grouped_gemm(x, True, dy, True), args.iters, flush)
         report('gemm_wgrad', ms, best, flops)
+        traced('gemm_wgrad', lambda **kw: gemm.grouped_gemm(x, True, dy, True, **kw))
     if want('cublas'):
         ms, best = timed(lambda: torch.bmm(x, w1, out=out), args.iters, flush)
         report('cublas_bmm', ms, best, flops)

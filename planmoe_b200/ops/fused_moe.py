@@ -189,7 +189,7 @@ def _trace_buffer(phase, device):
     if os.environ.get('PLANMOE_GEMM_TRACE', '0') != '1':
         return None
     if phase not in _TRACE:
-        _TRACE[phase] = torch.zeros(256, 8, dtype=torch.int64, device=device)
+        _TRACE[phase] = torch.zeros(256, 32, dtype=torch.int64, device=device)
     return _TRACE[phase]
 
 
@@ -209,6 +209,13 @@ def last_trace():
             'copy_begin_us_median': (int(t[:, 1].median()) - t0) / 1e3,
             'gate_wait_us_median': float(t[:, 3].median()) / 1e3,
             'gate_wait_us_max': float(t[:, 3].max()) / 1e3,
+            # per tile of a CTA's loop: when (after kernel entry) the producer asked for the rows, how long it waited
+            'tile_ask_us_median': [round((int(t[:, 8 + 2 * i][t[:, 8 + 2 * i] > 0].median()) - t0) / 1e3, 1)
+                                   for i in range(12) if bool((t[:, 8 + 2 * i] > 0).any())],
+            'tile_wait_us_median': [round(float((t[:, 9 + 2 * i] - t[:, 8 + 2 * i])[t[:, 8 + 2 * i] > 0].median()) / 1e3, 1)
+                                    for i in range(12) if bool((t[:, 8 + 2 * i] > 0).any())],
+            'tile_wait_us_max': [round(float((t[:, 9 + 2 * i] - t[:, 8 + 2 * i])[t[:, 8 + 2 * i] > 0].max()) / 1e3, 1)
+                                 for i in range(12) if bool((t[:, 8 + 2 * i] > 0).any())],
             'ctas': int(t.size(0))}
     return out
 
@@ -504,7 +511,9 @@ def forward(layer, x, gctx, top_k, capacity_factor, degree):
                 act=ACT_CODES[ex.act_name], postscore=layer.is_postscore, q8=(layer.compress_name == 'int8'))
     y = _FusedExperts.apply(x.contiguous(), gates, ex.batched_fc1_w, ex.batched_fc1_bias,
                             ex.batched_fc2_w, ex.batched_fc2_bias, meta)
-    layer.last_stats = dict(capacity=capacity, degree=degree, path='fused', wire=('int8' if meta['q8'] else 'bf16'))
+    # both 'naive' and 'pipe' run as the flat push of the copy role / push epilogue: say so instead of echoing the name
+    layer.last_stats = dict(capacity=capacity, degree=degree, path='fused', comm='flat-push',
+                            wire=('int8' if meta['q8'] else 'bf16'))
     if getattr(layer, 'collect_stats', False):
         from ..utils import metrics
         layer.last_stats.update(metrics.routing_stats(idx, loc, E, capacity))
