@@ -90,69 +90,31 @@ int8_decode_kernel(const unsigned char* __restrict__ q, const float* __restrict_
 template <class T>
 __global__ void __launch_bounds__(256)
 int8_rows_encode_kernel(const T* __restrict__ x, unsigned char* __restrict__ out, int R, int M) {
-  // One warp per row.  Rows of up to 32 lanes x kHold 16-element pieces stay in registers between the min / max
-  // pass and the quantisation, so the input is read once; longer rows are read a second time.
-  constexpr int kHold = 4;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int V = Vec16<T>::N;
-  constexpr int PV = 16 / V;                     // 16-byte input vectors per 16-element piece
   const size_t out_stride = (size_t)M + 16;
-  const int pieces = M / 16;
-  const bool held = pieces <= 32 * kHold;
   for (int r = blockIdx.x * 8 + warp; r < R; r += gridDim.x * 8) {
     const T* src = x + (size_t)r * M;
-    Pack<T> keep[kHold][PV];
     float lo = INFINITY, hi = -INFINITY;
-    if (held) {
+    for (int v = lane; v < M / V; v += 32) {
+      Pack<T> p = ld16(src + v * V);
 #pragma unroll
-      for (int i = 0; i < kHold; ++i) {
-        const int v = i * 32 + lane;
-        if (v < pieces) {
-#pragma unroll
-          for (int h = 0; h < PV; ++h) {
-            keep[i][h] = ld16(src + (size_t)v * 16 + h * V);
-#pragma unroll
-            for (int e = 0; e < V; ++e) { float f = to_f32(keep[i][h].v[e]); lo = fminf(lo, f); hi = fmaxf(hi, f); }
-          }
-        }
-      }
-    } else {
-      for (int v = lane; v < M / V; v += 32) {
-        Pack<T> p = ld16(src + v * V);
-#pragma unroll
-        for (int e = 0; e < V; ++e) { float f = to_f32(p.v[e]); lo = fminf(lo, f); hi = fmaxf(hi, f); }
-      }
+      for (int i = 0; i < V; ++i) { float f = to_f32(p.v[i]); lo = fminf(lo, f); hi = fmaxf(hi, f); }
     }
     lo = warp_min(lo); hi = warp_max(hi);
     const float range = hi - lo;
     const float inv = range > 0.f ? 255.f / range : 0.f;
     unsigned char* dst = out + (size_t)r * out_stride;
-    if (held) {
+    for (int v = lane; v < M / 16; v += 32) {
+      alignas(16) unsigned char o[16];
 #pragma unroll
-      for (int i = 0; i < kHold; ++i) {
-        const int v = i * 32 + lane;
-        if (v < pieces) {
-          alignas(16) unsigned char o[16];
+      for (int h = 0; h < 16 / V; ++h) {
+        Pack<T> p = ld16(src + (size_t)v * 16 + h * V);
 #pragma unroll
-          for (int h = 0; h < PV; ++h)
-#pragma unroll
-            for (int e = 0; e < V; ++e)
-              o[h * V + e] = (unsigned char)fminf(fmaxf(rintf((to_f32(keep[i][h].v[e]) - lo) * inv), 0.f), 255.f);
-          reinterpret_cast<uint4*>(dst)[v] = *reinterpret_cast<uint4*>(o);
-        }
+        for (int i = 0; i < V; ++i)
+          o[h * V + i] = (unsigned char)fminf(fmaxf(rintf((to_f32(p.v[i]) - lo) * inv), 0.f), 255.f);
       }
-    } else {
-      for (int v = lane; v < pieces; v += 32) {
-        alignas(16) unsigned char o[16];
-#pragma unroll
-        for (int h = 0; h < PV; ++h) {
-          Pack<T> p = ld16(src + (size_t)v * 16 + h * V);
-#pragma unroll
-          for (int e = 0; e < V; ++e)
-            o[h * V + e] = (unsigned char)fminf(fmaxf(rintf((to_f32(p.v[e]) - lo) * inv), 0.f), 255.f);
-        }
-        reinterpret_cast<uint4*>(dst)[v] = *reinterpret_cast<uint4*>(o);
-      }
+      reinterpret_cast<uint4*>(dst)[v] = *reinterpret_cast<uint4*>(o);
     }
     if (lane == 0) *reinterpret_cast<float4*>(dst + M) = make_float4(range * (1.f / 255.f), lo, 0.f, 0.f);
   }
