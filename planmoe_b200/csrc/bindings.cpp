@@ -439,24 +439,56 @@ Tensor grouped_gemm_op(const Tensor& A, bool a_mn, const Tensor& B, bool b_mn, c
 }
 
 // fp32 column sums [groups / fold, N] of a bf16 [groups, rows, N] tensor; with `as_bf16` the result is
-// returned in bf16 (written by the same kernel).
-Tensor colsum_op(const Tensor& x, int64_t fold, bool as_bf16) {
-  count_launch(2);
+// returned in bf16 (written by the same kernel).  One launch (plus the memset of its counters).
+static void colsum_check(const Tensor& x, int64_t fold) {
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 3 && x.stride(2) == 1);
-  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(fold >= 1 && x.size(0) % fold == 0, "colsum: groups must be a multiple of fold");
+  TORCH_CHECK(x.size(2) % 8 == 0 && x.stride(1) % 8 == 0 && x.stride(0) % 8 == 0, "colsum needs 16-byte aligned rows");
+}
+
+// scratch of one job: [out][partials][counters]; fills `j`, returns the buffer
+static Tensor colsum_job(const Tensor& x, int64_t fold, bool as_bf16, ColsumJob& j, Tensor& ob) {
   const int groups = x.size(0), N = x.size(2);
-  const int64_t rows = x.size(1);
-  TORCH_CHECK(fold >= 1 && groups % fold == 0, "colsum: groups must be a multiple of fold");
-  TORCH_CHECK(N % 8 == 0 && x.stride(1) % 8 == 0 && x.stride(0) % 8 == 0, "colsum needs 16-byte aligned rows");
-  const int64_t slabs = colsum_slabs(rows);
-  const int64_t out_groups = groups / fold;
-  Tensor buf = torch::empty({out_groups * N + (int64_t)groups * N * slabs}, x.options().dtype(at::kFloat));
-  Tensor ob;
+  const int64_t rows = x.size(1), slabs = colsum_slabs(rows), out_groups = groups / fold;
+  const int64_t counters = out_groups * colsum_colblocks(N);
+  Tensor buf = torch::empty({out_groups * N + (int64_t)groups * N * slabs + counters}, x.options().dtype(at::kFloat));
   if (as_bf16) ob = torch::empty({out_groups, (int64_t)N}, x.options());
-  launch_colsum_bf16(x.data_ptr(), buf.data_ptr<float>(), groups, rows, N, x.stride(1), x.stride(0), (int)fold,
-                     as_bf16 ? ob.data_ptr() : nullptr, cur_stream());
+  j.x = x.data_ptr(); j.out = buf.data_ptr<float>(); j.out_bf16 = as_bf16 ? ob.data_ptr() : nullptr;
+  j.partial = j.out + out_groups * N;
+  j.counters = reinterpret_cast<unsigned*>(j.partial + (int64_t)groups * N * slabs);
+  j.rows = rows; j.row_stride = x.stride(1); j.group_stride = x.stride(0);
+  j.N = N; j.groups = groups; j.fold = (int)fold;
+  return buf;
+}
+
+Tensor colsum_op(const Tensor& x, int64_t fold, bool as_bf16) {
+  count_launch(1);
+  colsum_check(x, fold);
+  c10::cuda::CUDAGuard guard(x.device());
+  ColsumJob j{};
+  Tensor ob;
+  Tensor buf = colsum_job(x, fold, as_bf16, j, ob);
+  launch_colsum_jobs(&j, 1, cur_stream());
   if (as_bf16) return ob;
-  return buf.narrow(0, 0, out_groups * N).view({out_groups, (int64_t)N});
+  const int64_t out_groups = x.size(0) / fold;
+  return buf.narrow(0, 0, out_groups * x.size(2)).view({out_groups, x.size(2)});
+}
+
+// Column sums of two tensors in one launch (the two bias gradients of the expert FFN).
+std::vector<Tensor> colsum2_op(const Tensor& xa, const Tensor& xb, int64_t fold, bool as_bf16) {
+  count_launch(1);
+  colsum_check(xa, fold);
+  colsum_check(xb, fold);
+  TORCH_CHECK(xa.device() == xb.device());
+  c10::cuda::CUDAGuard guard(xa.device());
+  ColsumJob j[2] = {};
+  Tensor oa, ob;
+  Tensor ba = colsum_job(xa, fold, as_bf16, j[0], oa);
+  Tensor bb = colsum_job(xb, fold, as_bf16, j[1], ob);
+  launch_colsum_jobs(j, 2, cur_stream());
+  if (as_bf16) return {oa, ob};
+  const int64_t ga = xa.size(0) / fold, gb = xb.size(0) / fold;
+  return {ba.narrow(0, 0, ga * xa.size(2)).view({ga, xa.size(2)}), bb.narrow(0, 0, gb * xb.size(2)).view({gb, xb.size(2)})};
 }
 
 // rows [R, M] -> uint8 [R, M + 16]: M quantised bytes + {scale, low, 0, 0} (the wire rows of the fused send)
@@ -681,6 +713,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("int8_decode", &int8_decode_op);
   m.def("int8_rows_encode", &int8_rows_encode_op);
   m.def("colsum", &colsum_op, py::arg("x"), py::arg("fold") = 1, py::arg("as_bf16") = false);
+  m.def("colsum2", &colsum2_op, py::arg("xa"), py::arg("xb"), py::arg("fold") = 1, py::arg("as_bf16") = false);
   m.def("scatter_push", &scatter_push_op);
   m.def("gather_wait", &gather_wait_op, py::arg("disp_ptr"), py::arg("dtype"), py::arg("M"), py::arg("idx"), py::arg("loc"),
         py::arg("gates"), py::arg("C"), py::arg("flags_ptr"), py::arg("n_flags"), py::arg("want"), py::arg("budget_ms"),

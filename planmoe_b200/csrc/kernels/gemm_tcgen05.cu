@@ -53,6 +53,7 @@
 // (PlanMoE/impls/communicate.py:604-623).
 
 #include "planmoe.h"
+#include <algorithm>
 #include "kernels/common.cuh"
 
 #include <cuda.h>
@@ -1511,33 +1512,48 @@ cudaError_t launch_grouped_gemm(const GemmArgs& a, cudaStream_t stream) {
 
 // ---------------------------------------------------------------------------------------------
 // Column sums (bias gradients): fp32 [groups / fold][N] = sum over rows (and over `fold` leading
-// group blocks, the pipeline chunks) of bf16 [groups][rows][N].
-// Two-stage and deterministic.  Stage 1: a CTA of 8 row lanes x 32 column threads reduces a slab of
-// 128 rows x 256 columns with 16-byte loads (8 columns per thread), combines the row lanes through
-// shared memory and writes one fp32 partial row.  Stage 2 adds the partials in slab order.
+// group blocks, the pipeline chunks) of bf16 [groups][rows][N]; up to two tensors per launch.
+// One launch, deterministic.  A CTA of 8 row lanes x 32 column threads reduces a slab of 128 rows x 256
+// columns with 16-byte loads (8 columns per thread), combines the row lanes through shared memory and
+// writes one fp32 partial row; it then counts itself in on the (output group, column block) it
+// contributes to, and the CTA that arrives last adds that block's partials in slab order, so the result
+// does not depend on which CTA that was.
 // ---------------------------------------------------------------------------------------------
 namespace {
 constexpr int kColsumSlab = 128;
 constexpr int kColsumCols = 256;
 
+struct ColsumJobs {
+  ColsumJob j[2];
+  int z0[3];                                       // job i owns blockIdx.z in [z0[i], z0[i + 1])
+  int n;
+};
+
 __global__ void __launch_bounds__(256)
-colsum_partial_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ partial, long long rows, int N,
-                      long long row_stride, long long group_stride, int slabs) {
+colsum_kernel(const ColsumJobs jobs) {
   __shared__ float red[8][kColsumCols + 8];
+  __shared__ int last_s;
+  const int ji = (jobs.n > 1 && (int)blockIdx.z >= jobs.z0[1]) ? 1 : 0;
+  const ColsumJob& J = jobs.j[ji];
+  const int g = (int)blockIdx.z - jobs.z0[ji];
+  const int slab = blockIdx.y, cb = blockIdx.x;
+  const int slabs = (int)((J.rows + kColsumSlab - 1) / kColsumSlab);
+  const int colblocks = (J.N + kColsumCols - 1) / kColsumCols;
+  if (slab >= slabs || cb >= colblocks) return;    // the grid is sized for the larger job
   const int ct = threadIdx.x & 31, rl = threadIdx.x >> 5;
-  const int col0 = blockIdx.x * kColsumCols;
+  const int col0 = cb * kColsumCols;
   const int col = col0 + ct * 8;
-  const int slab = blockIdx.y, g = blockIdx.z;
+  const int N = J.N;
   const long long r0 = (long long)slab * kColsumSlab;
-  const long long r1 = r0 + kColsumSlab < rows ? r0 + kColsumSlab : rows;
+  const long long r1 = r0 + kColsumSlab < J.rows ? r0 + kColsumSlab : J.rows;
   float a[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) a[i] = 0.f;
   if (col < N) {
-    const __nv_bfloat16* base = x + (long long)g * group_stride + col;
+    const __nv_bfloat16* base = reinterpret_cast<const __nv_bfloat16*>(J.x) + (long long)g * J.group_stride + col;
 #pragma unroll 4
     for (long long r = r0 + rl; r < r1; r += 8) {
-      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(base + r * row_stride));
+      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(base + r * J.row_stride));
       const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -1554,58 +1570,82 @@ colsum_partial_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ p
     float acc = 0.f;
 #pragma unroll
     for (int l = 0; l < 8; ++l) acc += red[l][c];
-    partial[((long long)g * slabs + slab) * N + col0 + c] = acc;
+    J.partial[((long long)g * slabs + slab) * N + col0 + c] = acc;
   }
-}
 
-__global__ void __launch_bounds__(256)
-colsum_final_kernel(const float* __restrict__ partial, float* __restrict__ out, __nv_bfloat16* __restrict__ out_bf16,
-                    int N, int slabs, int fold, int out_groups) {
-  // 32 columns x 8 slab lanes per CTA: lane l adds partials l, l + 8, ... (independent loads in flight),
-  // the eight lane sums are then added in lane order, so the result does not depend on timing.
-  __shared__ float red[8][33];
-  const int ct = threadIdx.x & 31, sl = threadIdx.x >> 5;
-  const int col = blockIdx.x * 32 + ct;
-  const int e = blockIdx.y;
-  float acc = 0.f;
+  // count in; the last CTA of this (output group, column block) finishes the sum
+  const int out_groups = J.groups / J.fold;
+  const int e = g % out_groups;
+  const int total = J.fold * slabs;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) last_s = (atomicAdd(J.counters + e * colblocks + cb, 1u) == (unsigned)(total - 1)) ? 1 : 0;
+  __syncthreads();
+  if (!last_s) return;
+  __threadfence();
+#pragma unroll
+  for (int i = 0; i < 8; ++i) a[i] = 0.f;
   if (col < N) {
-    const int total = fold * slabs;
 #pragma unroll 4
-    for (int i = sl; i < total; i += 8) {
-      const int j = i / slabs, s = i - j * slabs;
-      acc += partial[((long long)(j * out_groups + e) * slabs + s) * N + col];
+    for (int i = rl; i < total; i += 8) {          // partial i = (fold block j, slab s); lanes take every eighth
+      const int j = i / slabs, s2 = i - j * slabs;
+      const float4* pp = reinterpret_cast<const float4*>(J.partial + ((long long)(j * out_groups + e) * slabs + s2) * N + col);
+      const float4 p0 = __ldcg(pp), p1 = __ldcg(pp + 1);
+      a[0] += p0.x; a[1] += p0.y; a[2] += p0.z; a[3] += p0.w;
+      a[4] += p1.x; a[5] += p1.y; a[6] += p1.z; a[7] += p1.w;
     }
   }
-  red[sl][ct] = acc;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) red[rl][ct * 8 + i] = a[i];
   __syncthreads();
-  if (sl == 0 && col < N) {
+  if (col0 + c < N) {
     float r = 0.f;
 #pragma unroll
-    for (int l = 0; l < 8; ++l) r += red[l][ct];
-    out[(long long)e * N + col] = r;
-    if (out_bf16 != nullptr) out_bf16[(long long)e * N + col] = __float2bfloat16_rn(r);
+    for (int l = 0; l < 8; ++l) r += red[l][c];    // lane order: independent of timing
+    J.out[(long long)e * N + col0 + c] = r;
+    if (J.out_bf16 != nullptr)
+      reinterpret_cast<__nv_bfloat16*>(J.out_bf16)[(long long)e * N + col0 + c] = __float2bfloat16_rn(r);
   }
 }
 }  // namespace
 
 int colsum_slabs(long long rows) { return (int)((rows + kColsumSlab - 1) / kColsumSlab); }
+int colsum_colblocks(int N) { return (N + kColsumCols - 1) / kColsumCols; }
 
-// `out` must have room for (groups / fold) * N floats followed by groups * colsum_slabs(rows) * N floats of
-// scratch.  N must be a multiple of 8 and rows of x 16-byte aligned.  groups = fold * (groups / fold):
-// group j * (groups / fold) + e is summed into output row e.  `out_bf16` (optional) receives the same sums
-// rounded to bf16.
+// One launch for one or two jobs.  Each job's `counters` ((groups / fold) * colsum_colblocks(N) words) are
+// zeroed here, in stream order, ahead of the kernel.
+void launch_colsum_jobs(const ColsumJob* jobs, int n, cudaStream_t stream) {
+  ColsumJobs js{};
+  js.n = n;
+  int z = 0, max_slabs = 1, max_cb = 1;
+  for (int i = 0; i < n; ++i) {
+    js.j[i] = jobs[i];
+    if (js.j[i].fold < 1) js.j[i].fold = 1;
+    js.z0[i] = z;
+    z += jobs[i].groups;
+    max_slabs = std::max(max_slabs, colsum_slabs(jobs[i].rows));
+    max_cb = std::max(max_cb, colsum_colblocks(jobs[i].N));
+    cudaMemsetAsync(jobs[i].counters, 0,
+                    sizeof(unsigned) * (size_t)(jobs[i].groups / js.j[i].fold) * colsum_colblocks(jobs[i].N), stream);
+  }
+  js.z0[n] = z;
+  colsum_kernel<<<dim3(max_cb, max_slabs, z), 256, 0, stream>>>(js);
+}
+
+// `out` must have room for (groups / fold) * N floats, then groups * colsum_slabs(rows) * N floats of scratch,
+// then (groups / fold) * colsum_colblocks(N) counters.  N must be a multiple of 8 and rows of x 16-byte
+// aligned.  groups = fold * (groups / fold): group j * (groups / fold) + e is summed into output row e.
+// `out_bf16` (optional) receives the same sums rounded to bf16.
 void launch_colsum_bf16(const void* x, float* out, int groups, long long rows, int N, long long row_stride,
                         long long group_stride, int fold, void* out_bf16, cudaStream_t stream) {
   if (fold < 1) fold = 1;
-  const int out_groups = groups / fold;
-  const int slabs = colsum_slabs(rows);
-  float* partial = out + (long long)out_groups * N;
-  dim3 g1((N + kColsumCols - 1) / kColsumCols, slabs, groups);
-  colsum_partial_kernel<<<g1, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), partial, rows, N,
-                                              row_stride, group_stride, slabs);
-  dim3 g2((N + 31) / 32, out_groups);
-  colsum_final_kernel<<<g2, 256, 0, stream>>>(partial, out, reinterpret_cast<__nv_bfloat16*>(out_bf16), N, slabs, fold,
-                                            out_groups);
+  ColsumJob j{};
+  j.x = x; j.out = out; j.out_bf16 = out_bf16;
+  j.partial = out + (long long)(groups / fold) * N;
+  j.counters = reinterpret_cast<unsigned*>(j.partial + (long long)groups * colsum_slabs(rows) * N);
+  j.rows = rows; j.row_stride = row_stride; j.group_stride = group_stride;
+  j.N = N; j.groups = groups; j.fold = fold;
+  launch_colsum_jobs(&j, 1, stream);
 }
 
 }  // namespace planmoe

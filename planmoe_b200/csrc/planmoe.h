@@ -208,10 +208,20 @@ int gemm_push_arrivals(int groups, int M, int N, int push_rows, int s);
 
 // Column sums of a bf16 [groups][rows][N] tensor -> fp32 [groups / fold][N] (bias gradients); the `fold`
 // leading blocks of groups (pipeline chunks) are added together.  `out` = (groups / fold) * N results
-// followed by groups * colsum_slabs(rows) * N floats of scratch; `out_bf16` optionally gets bf16 copies.
+// followed by groups * colsum_slabs(rows) * N floats of scratch and (groups / fold) * colsum_colblocks(N) counter
+// words; `out_bf16` optionally gets bf16 copies.
 int colsum_slabs(long long rows);
 void launch_colsum_bf16(const void* x, float* out, int groups, long long rows, int N,
                         long long row_stride, long long group_stride, int fold, void* out_bf16,
                         cudaStream_t stream);
+// One or two column-sum jobs in a single launch (see launch_colsum_bf16 for the meaning of the fields).
+// `partial`: groups * colsum_slabs(rows) * N floats; `counters`: (groups / fold) * colsum_colblocks(N) words.
+struct ColsumJob {
+  const void* x; float* out; void* out_bf16; float* partial; unsigned* counters;
+  long long rows, row_stride, group_stride;
+  int N, groups, fold;
+};
+int colsum_colblocks(int N);
+void launch_colsum_jobs(const ColsumJob* jobs, int n, cudaStream_t stream);
 
 }  // namespace planmoe

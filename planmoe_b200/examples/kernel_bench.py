@@ -171,6 +171,8 @@ def main():
     if want('colsum'):
         ms, best = timed(lambda: lib.colsum(dy), args.iters, flush)
         report('colsum', ms, best, bytes_=dy.numel() * 2.0)
+        ms, best = timed(lambda: lib.colsum2(dy, x, 1, True), args.iters, flush)
+        report('colsum2 (both bias gradients)', ms, best, bytes_=(dy.numel() + x.numel()) * 2.0)
     if want('misc'):
         import ctypes
         ms, best = timed(lambda: lib.int8_rows_encode(tok), args.iters, flush)

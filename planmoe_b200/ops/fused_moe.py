@@ -420,8 +420,7 @@ class _FusedExperts(torch.autograd.Function):
         with stage('bwd.wgrad1'):
             dw1 = grouped_gemm(recv_x.view(d, E_l, R, M), True, dh.view(d, E_l, R, H), True, EPI_STORE)
         with stage('bwd.bias_grads'):
-            db2 = lib.colsum(recv_dy, d, True)
-            db1 = lib.colsum(dh, d, True)
+            db2, db1 = lib.colsum2(recv_dy, dh, d, True)
 
         # ---- dispatch backward: wait for the returned slots, gather (gate-weighted if pre-score)
         q8_gather = dict(q8_scales_ptr=bs.local_ptr(bs.off_dx + rows_y * M), q8_group_rows=rows_y) if q8 else {}

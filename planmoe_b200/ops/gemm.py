@@ -94,8 +94,7 @@ class _ExpertFFN(torch.autograd.Function):
         # dW2 = H^T . dY, dW1 = X^T . dH_pre      contraction over rows: both operands MN-major
         dw2 = grouped_gemm(h, True, dy, True, EPI_STORE)
         dw1 = grouped_gemm(x, True, dh, True, EPI_STORE)
-        db2 = lib.colsum(dy, 1, True)
-        db1 = lib.colsum(dh, 1, True)
+        db2, db1 = lib.colsum2(dy, dh, 1, True)
         return dx, dw1, db1, dw2, db2, None
 
 

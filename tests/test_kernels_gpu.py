@@ -129,6 +129,13 @@ def test_colsum():
     ob = _lib().colsum(x, 3, True)
     assert ob.dtype == torch.bfloat16 and torch.equal(ob, out.to(torch.bfloat16))
     assert torch.equal(_lib().colsum(x, 3), out)            # fixed summation order
+    # two tensors of different shapes in one launch give what two launches give
+    xa, xb = _rand(4, 700, 264), _rand(4, 300, 520)
+    oa, ob2 = _lib().colsum2(xa, xb, 2)
+    assert torch.equal(oa, _lib().colsum(xa, 2)) and torch.equal(ob2, _lib().colsum(xb, 2))
+    assert torch.allclose(ob2, xb.float().sum(1).view(2, 2, 520).sum(0), atol=2e-2, rtol=1e-3)
+    ha, hb = _lib().colsum2(xa, xb, 2, True)
+    assert torch.equal(ha, oa.to(torch.bfloat16)) and torch.equal(hb, ob2.to(torch.bfloat16))
 
 
 def test_expert_ffn_forward_backward():
