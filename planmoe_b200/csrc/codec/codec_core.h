@@ -29,30 +29,63 @@ namespace codec {
 // ------------------------------------------------------------------------------------------------
 // bit stream over a small word array (LSB first)
 // ------------------------------------------------------------------------------------------------
+// Bits are collected in a 64-bit register and leave for the word array 32 at a time, so the array is touched
+// once per word, not once per bit.
 struct BitWriter {
-  uint32_t* w;
-  int pos;          // bit position
+  uint32_t* w;      // cleared by the caller
+  int widx;         // next word to write
+  uint64_t acc;     // pending bits, LSB first
+  int nacc;         // number of pending bits (< 32 between calls)
+  PM_HD void spill() {
+    if (nacc >= 32) {
+      w[widx++] = (uint32_t)acc;
+      acc >>= 32;
+      nacc -= 32;
+    }
+  }
   PM_HD void put(uint32_t bit) {
-    if (bit) w[pos >> 5] |= (1u << (pos & 31));
-    ++pos;
+    acc |= (uint64_t)(bit & 1u) << nacc;
+    ++nacc;
+    spill();
   }
   // writes the low n bits of x (n <= 16), returns x >> n
   PM_HD uint32_t put_bits(uint32_t x, int n) {
-    for (int i = 0; i < n; ++i) { put(x & 1u); x >>= 1; }
-    return x;
+    acc |= (uint64_t)(x & ((1u << n) - 1u)) << nacc;
+    nacc += n;
+    spill();
+    return x >> n;
+  }
+  PM_HD void flush() {
+    if (nacc > 0) w[widx] = (uint32_t)acc;
   }
 };
 struct BitReader {
   const uint32_t* w;
-  int pos;
+  int widx;         // next word to fetch
+  int nwords;       // words available
+  uint64_t acc;     // fetched bits not yet consumed, LSB first
+  int nacc;
+  PM_HD void fill(int need) {
+    if (nacc < need) {
+      const uint32_t next = widx < nwords ? w[widx] : 0u;
+      ++widx;
+      acc |= (uint64_t)next << nacc;
+      nacc += 32;
+    }
+  }
   PM_HD uint32_t get() {
-    const uint32_t b = (w[pos >> 5] >> (pos & 31)) & 1u;
-    ++pos;
+    fill(1);
+    const uint32_t b = (uint32_t)acc & 1u;
+    acc >>= 1;
+    --nacc;
     return b;
   }
-  PM_HD uint32_t get_bits(int n) {
-    uint32_t x = 0;
-    for (int i = 0; i < n; ++i) x |= get() << i;
+  PM_HD uint32_t get_bits(int n) {          // n <= 16
+    if (n == 0) return 0u;
+    fill(n);
+    const uint32_t x = (uint32_t)acc & ((1u << n) - 1u);
+    acc >>= n;
+    nacc -= n;
     return x;
   }
 };
@@ -115,7 +148,7 @@ PM_HD float zfp_ldexp(float x, int e) {
 
 // Encode 16 floats (row-major 4x4) into `words` (cleared by the caller), maxbits = 16 * rate.
 PM_HD void zfp_encode_block(const float* f, uint32_t* words, int maxbits) {
-  BitWriter bw{words, 0};
+  BitWriter bw{words, 0, 0ull, 0};
   float amax = 0.f;
   for (int i = 0; i < 16; ++i) { const float a = f[i] < 0 ? -f[i] : f[i]; if (a > amax) amax = a; }
   if (!(amax > 0.f) || !(amax < 3.0e38f)) { return; }          // all-zero (or non-finite) block: bit 0 = 0
@@ -139,10 +172,11 @@ PM_HD void zfp_encode_block(const float* f, uint32_t* words, int maxbits) {
     for (; n < 16 && bits && (bits--, bw.put(!!x), !!x); x >>= 1, n++)
       for (; n < 15 && bits && (bits--, bw.put(x & 1u), !(x & 1u)); x >>= 1, n++) {}
   }
+  bw.flush();
 }
 
 PM_HD void zfp_decode_block(const uint32_t* words, float* f, int maxbits) {
-  BitReader br{words, 0};
+  BitReader br{words, 0, maxbits / 32, 0ull, 0};
   if (!br.get()) {
     for (int i = 0; i < 16; ++i) f[i] = 0.f;
     return;

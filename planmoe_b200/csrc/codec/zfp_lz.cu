@@ -11,6 +11,7 @@
 
 #include "codec/codecs.h"
 #include "codec/codec_core.h"
+#include <cstddef>
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -56,8 +57,20 @@ __host__ __device__ inline void zfp_block_io(bool encode, const void* x_in, void
   float f[16];
   uint32_t* dst = reinterpret_cast<uint32_t*>(stream + b * (long long)(2 * rate));
   if (encode) {
+#pragma unroll
     for (int r = 0; r < 4; ++r) {
       const long long row = yb * 4 + r;
+#if defined(__CUDA_ARCH__)
+      if (elem == 1 && row < rows) {              // bf16: the block's four values of this row in one 8-byte load
+        const uint2 raw = *reinterpret_cast<const uint2*>(
+            reinterpret_cast<const __nv_bfloat16*>(x_in) + (slice * rows + row) * M + xb * 4);
+        f[r * 4 + 0] = __uint_as_float(raw.x << 16);
+        f[r * 4 + 1] = __uint_as_float(raw.x & 0xffff0000u);
+        f[r * 4 + 2] = __uint_as_float(raw.y << 16);
+        f[r * 4 + 3] = __uint_as_float(raw.y & 0xffff0000u);
+        continue;
+      }
+#endif
       for (int c = 0; c < 4; ++c)
         f[r * 4 + c] = row < rows ? load_elem(x_in, elem, (slice * rows + row) * M + xb * 4 + c) : 0.f;
     }
@@ -67,9 +80,21 @@ __host__ __device__ inline void zfp_block_io(bool encode, const void* x_in, void
   } else {
     for (int i = 0; i < words_n; ++i) words[i] = dst[i];
     zfp_decode_block(words, f, 16 * rate);
+#pragma unroll
     for (int r = 0; r < 4; ++r) {
       const long long row = yb * 4 + r;
       if (row >= rows) break;
+#if defined(__CUDA_ARCH__)
+      if (elem == 1) {                            // bf16: one 8-byte store per row of the block
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(f[r * 4 + 0], f[r * 4 + 1]);
+        const __nv_bfloat162 hi = __floats2bfloat162_rn(f[r * 4 + 2], f[r * 4 + 3]);
+        uint2 raw;
+        raw.x = *reinterpret_cast<const uint32_t*>(&lo);
+        raw.y = *reinterpret_cast<const uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(x_out) + (slice * rows + row) * M + xb * 4) = raw;
+        continue;
+      }
+#endif
       for (int c = 0; c < 4; ++c) store_elem(x_out, elem, (slice * rows + row) * M + xb * 4 + c, f[r * 4 + c]);
     }
   }
@@ -150,11 +175,15 @@ struct LzEncSmem {
   Sym in[kLzBlockBytes / sizeof(Sym)];
   uint8_t best[kLzMaxSym];                        // match length at p (0 = literal)
   uint8_t dist[kLzMaxSym];                        // p - candidate
-  uint16_t jump[2][kLzMaxSym];                    // pointer doubling, double buffered
   uint8_t mark[kLzMaxSym];                        // p starts a token
   uint32_t flagw[kLzMaxSym / 32];                 // one bit per token: 1 = match
+  uint16_t jump[2][kLzMaxSym];                    // pointer doubling, double buffered
   uint8_t data[kLzBlockBytes];                    // token payload
+  // jump[1] and data (4 KiB, adjacent) are first written in steps 2 and 4; step 1 uses them as its candidate masks
+  __device__ uint32_t* eq() { return reinterpret_cast<uint32_t*>(&jump[1][0]); }
 };
+static_assert(offsetof(LzEncSmem<uint16_t>, data) == offsetof(LzEncSmem<uint16_t>, jump) + 2 * kLzMaxSym * 2, "eq() layout");
+static_assert(offsetof(LzEncSmem<uint16_t>, jump) % 4 == 0 && kLzWindow == 32, "eq() holds one bit per window distance");
 
 template <class Sym>
 __device__ __forceinline__ void lz_encode_block_warp(const Sym* __restrict__ g_in, int nsym, uint8_t* __restrict__ out,
@@ -164,24 +193,54 @@ __device__ __forceinline__ void lz_encode_block_warp(const Sym* __restrict__ g_i
   for (int i = lane; i < kLzMaxSym / 32; i += 32) sm.flagw[i] = 0u;
   __syncwarp();
 
-  // 1. longest match per position
+  // 1. longest match per position.  eq[q] has bit d-1 set when in[q - d] == in[q] (d = 1 .. 32): a candidate at
+  // distance d matches L symbols from p exactly when eq[p] & eq[p + 1] & ... & eq[p + L - 1] keeps bit d-1, so the
+  // longest match is found by and-ing masks until nothing survives, and the first candidate of maximal length
+  // (the serial coder's choice) is the largest surviving distance.
+  uint32_t* eq = sm.eq();
   for (int p = lane; p < nsym; p += 32) {
-    int best = 0, bestc = 0;
-    const int w0 = p - kLzWindow < 0 ? 0 : p - kLzWindow;
-    const int lim = nsym - p < kLzMaxMatch ? nsym - p : kLzMaxMatch;
-    const Sym first = sm.in[p];
-    for (int c = w0; c < p; ++c) {
-      if (sm.in[c] != first) continue;
-      int len = 1;
-      while (len < lim && sm.in[c + len] == sm.in[p + len]) ++len;
-      if (len > best) { best = len; bestc = c; }
+    const Sym v = sm.in[p];
+    uint32_t m = 0u;
+    const int dmax = p < kLzWindow ? p : kLzWindow;
+#pragma unroll 8
+    for (int d = 1; d <= dmax; ++d) m |= (sm.in[p - d] == v ? 1u : 0u) << (d - 1);
+    eq[p] = m;
+  }
+  __syncwarp();
+  int best_r[kLzMaxSym / 32], dist_r[kLzMaxSym / 32];   // eq aliases jump[1] / data: results wait in registers
+#pragma unroll
+  for (int k = 0; k < kLzMaxSym / 32; ++k) {
+    const int p = k * 32 + lane;
+    int best = 0, d = 0;
+    if (p < nsym) {
+      const int lim = nsym - p < kLzMaxMatch ? nsym - p : kLzMaxMatch;
+      uint32_t m = eq[p];
+      if (m != 0u) {
+        best = 1;
+        while (best < lim) {
+          const uint32_t m2 = m & eq[p + best];
+          if (m2 == 0u) break;
+          m = m2;
+          ++best;
+        }
+        d = 32 - __clz(m);
+      }
     }
-    const bool match = best >= min_match && best > 0;
-    sm.best[p] = (uint8_t)(match ? best : 0);
-    sm.dist[p] = (uint8_t)(p - bestc);
-    const int nx = p + (match ? best : 1);
-    sm.jump[0][p] = (uint16_t)(nx < nsym ? nx : nsym);
-    sm.mark[p] = p == 0 ? 1 : 0;
+    best_r[k] = best; dist_r[k] = d;
+  }
+  __syncwarp();                                   // every lane is done reading eq
+#pragma unroll
+  for (int k = 0; k < kLzMaxSym / 32; ++k) {
+    const int p = k * 32 + lane;
+    if (p < nsym) {
+      const int best = best_r[k];
+      const bool match = best >= min_match && best > 0;
+      sm.best[p] = (uint8_t)(match ? best : 0);
+      sm.dist[p] = (uint8_t)dist_r[k];
+      const int nx = p + (match ? best : 1);
+      sm.jump[0][p] = (uint16_t)(nx < nsym ? nx : nsym);
+      sm.mark[p] = p == 0 ? 1 : 0;
+    }
   }
   __syncwarp();
 
