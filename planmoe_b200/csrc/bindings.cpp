@@ -439,7 +439,7 @@ Tensor grouped_gemm_op(const Tensor& A, bool a_mn, const Tensor& B, bool b_mn, c
 }
 
 // fp32 column sums [groups / fold, N] of a bf16 [groups, rows, N] tensor; with `as_bf16` the result is
-// returned in bf16 (written by the same kernel).  One launch (plus the memset of its counters).
+// returned in bf16 (written by the same kernel).  Two launches: partial sums, then their sum.
 static void colsum_check(const Tensor& x, int64_t fold) {
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 3 && x.stride(2) == 1);
   TORCH_CHECK(fold >= 1 && x.size(0) % fold == 0, "colsum: groups must be a multiple of fold");
@@ -462,7 +462,7 @@ static Tensor colsum_job(const Tensor& x, int64_t fold, bool as_bf16, ColsumJob&
 }
 
 Tensor colsum_op(const Tensor& x, int64_t fold, bool as_bf16) {
-  count_launch(1);
+  count_launch(2);
   colsum_check(x, fold);
   c10::cuda::CUDAGuard guard(x.device());
   ColsumJob j{};
@@ -474,9 +474,9 @@ Tensor colsum_op(const Tensor& x, int64_t fold, bool as_bf16) {
   return buf.narrow(0, 0, out_groups * x.size(2)).view({out_groups, x.size(2)});
 }
 
-// Column sums of two tensors in one launch (the two bias gradients of the expert FFN).
+// Column sums of two tensors in the same two launches (the two bias gradients of the expert FFN).
 std::vector<Tensor> colsum2_op(const Tensor& xa, const Tensor& xb, int64_t fold, bool as_bf16) {
-  count_launch(1);
+  count_launch(2);
   colsum_check(xa, fold);
   colsum_check(xb, fold);
   TORCH_CHECK(xa.device() == xb.device());

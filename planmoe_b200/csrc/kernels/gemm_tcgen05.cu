@@ -1513,11 +1513,11 @@ cudaError_t launch_grouped_gemm(const GemmArgs& a, cudaStream_t stream) {
 // ---------------------------------------------------------------------------------------------
 // Column sums (bias gradients): fp32 [groups / fold][N] = sum over rows (and over `fold` leading
 // group blocks, the pipeline chunks) of bf16 [groups][rows][N]; up to two tensors per launch.
-// One launch, deterministic.  A CTA of 8 row lanes x 32 column threads reduces a slab of 128 rows x 256
-// columns with 16-byte loads (8 columns per thread), combines the row lanes through shared memory and
-// writes one fp32 partial row; it then counts itself in on the (output group, column block) it
-// contributes to, and the CTA that arrives last adds that block's partials in slab order, so the result
-// does not depend on which CTA that was.
+// Two stages, deterministic, each one launch for all tensors.  Stage 1: a CTA of 8 row lanes x 32 column threads
+// reduces a slab of 128 rows x 256 columns with 16-byte loads (8 columns per thread), combines the row lanes
+// through shared memory and writes one fp32 partial row.  Stage 2 adds the partials in slab order.  (A
+// single-launch form in which the last CTA to arrive finished the sum measured slower: the fence and the
+// atomic that every CTA needs before it may leave cost more than the second launch.)
 // ---------------------------------------------------------------------------------------------
 namespace {
 constexpr int kColsumSlab = 128;
@@ -1532,7 +1532,6 @@ struct ColsumJobs {
 __global__ void __launch_bounds__(256)
 colsum_kernel(const ColsumJobs jobs) {
   __shared__ float red[8][kColsumCols + 8];
-  __shared__ int last_s;
   const int ji = (jobs.n > 1 && (int)blockIdx.z >= jobs.z0[1]) ? 1 : 0;
   const ColsumJob& J = jobs.j[ji];
   const int g = (int)blockIdx.z - jobs.z0[ji];
@@ -1572,39 +1571,40 @@ colsum_kernel(const ColsumJobs jobs) {
     for (int l = 0; l < 8; ++l) acc += red[l][c];
     J.partial[((long long)g * slabs + slab) * N + col0 + c] = acc;
   }
+}
 
-  // count in; the last CTA of this (output group, column block) finishes the sum
+// Stage 2 for every job of the launch: 32 columns x 8 slab lanes per CTA; lane l adds partials l, l + 8, ...
+// (independent loads in flight), the eight lane sums are then added in lane order, so the result does not
+// depend on timing.
+__global__ void __launch_bounds__(256)
+colsum_final_kernel(const ColsumJobs jobs) {
+  __shared__ float red[8][33];
+  const int ji = (jobs.n > 1 && (int)blockIdx.y >= jobs.z0[1]) ? 1 : 0;
+  const ColsumJob& J = jobs.j[ji];
+  const int e = (int)blockIdx.y - jobs.z0[ji];
+  const int N = J.N;
+  const int ct = threadIdx.x & 31, sl = threadIdx.x >> 5;
+  const int col = blockIdx.x * 32 + ct;
+  if ((int)blockIdx.x * 32 >= N) return;           // the grid is sized for the wider job
+  const int slabs = (int)((J.rows + kColsumSlab - 1) / kColsumSlab);
   const int out_groups = J.groups / J.fold;
-  const int e = g % out_groups;
-  const int total = J.fold * slabs;
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) last_s = (atomicAdd(J.counters + e * colblocks + cb, 1u) == (unsigned)(total - 1)) ? 1 : 0;
-  __syncthreads();
-  if (!last_s) return;
-  __threadfence();
-#pragma unroll
-  for (int i = 0; i < 8; ++i) a[i] = 0.f;
+  float acc = 0.f;
   if (col < N) {
+    const int total = J.fold * slabs;
 #pragma unroll 4
-    for (int i = rl; i < total; i += 8) {          // partial i = (fold block j, slab s); lanes take every eighth
-      const int j = i / slabs, s2 = i - j * slabs;
-      const float4* pp = reinterpret_cast<const float4*>(J.partial + ((long long)(j * out_groups + e) * slabs + s2) * N + col);
-      const float4 p0 = __ldcg(pp), p1 = __ldcg(pp + 1);
-      a[0] += p0.x; a[1] += p0.y; a[2] += p0.z; a[3] += p0.w;
-      a[4] += p1.x; a[5] += p1.y; a[6] += p1.z; a[7] += p1.w;
+    for (int i = sl; i < total; i += 8) {
+      const int j = i / slabs, s = i - j * slabs;
+      acc += J.partial[((long long)(j * out_groups + e) * slabs + s) * N + col];
     }
   }
-#pragma unroll
-  for (int i = 0; i < 8; ++i) red[rl][ct * 8 + i] = a[i];
+  red[sl][ct] = acc;
   __syncthreads();
-  if (col0 + c < N) {
+  if (sl == 0 && col < N) {
     float r = 0.f;
 #pragma unroll
-    for (int l = 0; l < 8; ++l) r += red[l][c];    // lane order: independent of timing
-    J.out[(long long)e * N + col0 + c] = r;
-    if (J.out_bf16 != nullptr)
-      reinterpret_cast<__nv_bfloat16*>(J.out_bf16)[(long long)e * N + col0 + c] = __float2bfloat16_rn(r);
+    for (int l = 0; l < 8; ++l) r += red[l][ct];
+    J.out[(long long)e * N + col] = r;
+    if (J.out_bf16 != nullptr) reinterpret_cast<__nv_bfloat16*>(J.out_bf16)[(long long)e * N + col] = __float2bfloat16_rn(r);
   }
 }
 }  // namespace
@@ -1612,28 +1612,31 @@ colsum_kernel(const ColsumJobs jobs) {
 int colsum_slabs(long long rows) { return (int)((rows + kColsumSlab - 1) / kColsumSlab); }
 int colsum_colblocks(int N) { return (N + kColsumCols - 1) / kColsumCols; }
 
-// One launch for one or two jobs.  Each job's `counters` ((groups / fold) * colsum_colblocks(N) words) are
-// zeroed here, in stream order, ahead of the kernel.
+// Two launches (partial sums, then their sum in slab order) for one or two jobs.
 void launch_colsum_jobs(const ColsumJob* jobs, int n, cudaStream_t stream) {
-  ColsumJobs js{};
-  js.n = n;
-  int z = 0, max_slabs = 1, max_cb = 1;
+  ColsumJobs js{}, jf{};
+  js.n = jf.n = n;
+  int z = 0, zo = 0, max_slabs = 1, max_cb = 1, max_n = 0;
   for (int i = 0; i < n; ++i) {
     js.j[i] = jobs[i];
     if (js.j[i].fold < 1) js.j[i].fold = 1;
+    jf.j[i] = js.j[i];
     js.z0[i] = z;
+    jf.z0[i] = zo;
     z += jobs[i].groups;
+    zo += jobs[i].groups / js.j[i].fold;
     max_slabs = std::max(max_slabs, colsum_slabs(jobs[i].rows));
     max_cb = std::max(max_cb, colsum_colblocks(jobs[i].N));
-    cudaMemsetAsync(jobs[i].counters, 0,
-                    sizeof(unsigned) * (size_t)(jobs[i].groups / js.j[i].fold) * colsum_colblocks(jobs[i].N), stream);
+    max_n = std::max(max_n, jobs[i].N);
   }
   js.z0[n] = z;
+  jf.z0[n] = zo;
   colsum_kernel<<<dim3(max_cb, max_slabs, z), 256, 0, stream>>>(js);
+  colsum_final_kernel<<<dim3((max_n + 31) / 32, zo), 256, 0, stream>>>(jf);
 }
 
 // `out` must have room for (groups / fold) * N floats, then groups * colsum_slabs(rows) * N floats of scratch,
-// then (groups / fold) * colsum_colblocks(N) counters.  N must be a multiple of 8 and rows of x 16-byte
+// then (groups / fold) * colsum_colblocks(N) unused words.  N must be a multiple of 8 and rows of x 16-byte
 // aligned.  groups = fold * (groups / fold): group j * (groups / fold) + e is summed into output row e.
 // `out_bf16` (optional) receives the same sums rounded to bf16.
 void launch_colsum_bf16(const void* x, float* out, int groups, long long rows, int N, long long row_stride,
