@@ -162,28 +162,39 @@ __host__ __device__ inline void lz_decode_one(const uint8_t* packed, uint8_t* ra
 // Warp-parallel block coder.  One warp codes one 2 KiB block and produces exactly the bytes of the
 // serial coder lz_encode_block (the CPU twin, which the tests compare against):
 //   1. every lane finds, for its positions p = lane, lane + 32, ..., the longest match in the 32-symbol
-//      window (first candidate of maximal length), as the serial coder would if a token started at p;
-//   2. the token starts are the positions reachable from 0 by next(p) = p + (match ? length : 1); they are
-//      marked with ten rounds of pointer doubling (2^10 >= symbols per block);
-//   3. token ordinals and data offsets come from a warp scan over contiguous 32-position segments;
-//   4. flags and data are assembled in shared memory and copied to the block's slot.
+//      window (first candidate of maximal length), as the serial coder would if a token started at p, from
+//      per-position candidate bit masks;
+//   2. the token starts are the positions reachable from 0 by next(p) = p + (match ? length : 1): each lane
+//      owns a segment of 32 positions, computes where a walk from each of them leaves the segment, the exits
+//      are chained from position 0 to give every segment its entry, and each lane walks its own segment;
+//   3. token ordinals and data offsets come from a warp scan over the per-segment counts of that walk;
+//   4. a second walk assembles flags and data in shared memory, which are then copied to the block's slot.
 constexpr int kLzWarps = 4;                       // blocks coded per CTA
 constexpr int kLzMaxSym = kLzBlockBytes / 2;      // symbols per block with 16-bit symbols
+
+constexpr int kLzInfoWords = 32 * 33;             // position p lives at word (p % 32) * 33 + p / 32 (see lz_tp)
 
 template <class Sym>
 struct LzEncSmem {
   Sym in[kLzBlockBytes / sizeof(Sym)];
-  uint8_t best[kLzMaxSym];                        // match length at p (0 = literal)
-  uint8_t dist[kLzMaxSym];                        // p - candidate
-  uint8_t mark[kLzMaxSym];                        // p starts a token
+  // One word per position, written at the end of step 1: bits 0-10 next(p) = p + (match ? length : 1), bit 31
+  // match; a match has its length in bits 11-16 and its distance in bits 17-22, a 16-bit literal its symbol in
+  // bits 11-26.
+  uint32_t info[kLzInfoWords];
   uint32_t flagw[kLzMaxSym / 32];                 // one bit per token: 1 = match
-  uint16_t jump[2][kLzMaxSym];                    // pointer doubling, double buffered
-  uint8_t data[kLzBlockBytes];                    // token payload
-  // jump[1] and data (4 KiB, adjacent) are first written in steps 2 and 4; step 1 uses them as its candidate masks
-  __device__ uint32_t* eq() { return reinterpret_cast<uint32_t*>(&jump[1][0]); }
+  // step 1: candidate masks eq[1024]; afterwards: exit positions (u16 [kLzInfoWords]) and the token payload
+  uint32_t scratch[(kLzInfoWords * 2 + kLzBlockBytes + 3) / 4];
+  __device__ uint32_t* eq() { return scratch; }
+  __device__ uint16_t* exits() { return reinterpret_cast<uint16_t*>(scratch); }
+  __device__ uint8_t* data() { return reinterpret_cast<uint8_t*>(scratch) + kLzInfoWords * 2; }
 };
-static_assert(offsetof(LzEncSmem<uint16_t>, data) == offsetof(LzEncSmem<uint16_t>, jump) + 2 * kLzMaxSym * 2, "eq() layout");
-static_assert(offsetof(LzEncSmem<uint16_t>, jump) % 4 == 0 && kLzWindow == 32, "eq() holds one bit per window distance");
+static_assert(kLzWindow == 32 && kLzMaxMatch <= 32 && kLzMaxSym <= 1024, "lz encoder: masks, info fields and segments");
+static_assert(sizeof(LzEncSmem<uint16_t>::scratch) >= kLzMaxSym * 4, "eq() needs one word per position");
+
+// Positions are handed to lanes in two ways: strided (p = k * 32 + lane, steps 1) and in segments of 32 consecutive
+// positions per lane (steps 2-4).  This index keeps both conflict-free or nearly so: strided writes hit 32 banks,
+// and lanes walking their segments in lock-step (same offset) do too.
+__device__ __forceinline__ int lz_tp(int p) { return (p & 31) * 33 + (p >> 5); }
 
 template <class Sym>
 __device__ __forceinline__ void lz_encode_block_warp(const Sym* __restrict__ g_in, int nsym, uint8_t* __restrict__ out,
@@ -207,14 +218,15 @@ __device__ __forceinline__ void lz_encode_block_warp(const Sym* __restrict__ g_i
     eq[p] = m;
   }
   __syncwarp();
-  int best_r[kLzMaxSym / 32], dist_r[kLzMaxSym / 32];   // eq aliases jump[1] / data: results wait in registers
+  uint32_t info_r[kLzMaxSym / 32];                  // eq shares its memory with later steps: results wait in registers
 #pragma unroll
   for (int k = 0; k < kLzMaxSym / 32; ++k) {
     const int p = k * 32 + lane;
-    int best = 0, d = 0;
+    uint32_t w = 0u;
     if (p < nsym) {
       const int lim = nsym - p < kLzMaxMatch ? nsym - p : kLzMaxMatch;
       uint32_t m = eq[p];
+      int best = 0;
       if (m != 0u) {
         best = 1;
         while (best < lim) {
@@ -223,45 +235,55 @@ __device__ __forceinline__ void lz_encode_block_warp(const Sym* __restrict__ g_i
           m = m2;
           ++best;
         }
-        d = 32 - __clz(m);
+      }
+      if (best >= min_match && best > 0) {
+        w = 0x80000000u | (uint32_t)(p + best) | ((uint32_t)best << 11) | ((uint32_t)(32 - __clz(m)) << 17);
+      } else {
+        w = (uint32_t)(p + 1);
+        if (sizeof(Sym) == 2) w |= (uint32_t)sm.in[p] << 11;
       }
     }
-    best_r[k] = best; dist_r[k] = d;
+    info_r[k] = w;
   }
   __syncwarp();                                   // every lane is done reading eq
 #pragma unroll
   for (int k = 0; k < kLzMaxSym / 32; ++k) {
     const int p = k * 32 + lane;
-    if (p < nsym) {
-      const int best = best_r[k];
-      const bool match = best >= min_match && best > 0;
-      sm.best[p] = (uint8_t)(match ? best : 0);
-      sm.dist[p] = (uint8_t)dist_r[k];
-      const int nx = p + (match ? best : 1);
-      sm.jump[0][p] = (uint16_t)(nx < nsym ? nx : nsym);
-      sm.mark[p] = p == 0 ? 1 : 0;
-    }
+    if (p < nsym) sm.info[lz_tp(p)] = info_r[k];
   }
   __syncwarp();
 
-  // 2. token starts = positions reachable from 0
-  int cur = 0;
-  for (int hop = 1; hop < nsym; hop <<= 1) {
-    for (int p = lane; p < nsym; p += 32) {
-      const int j = sm.jump[cur][p];
-      if (sm.mark[p] && j < nsym) sm.mark[j] = 1;
-      sm.jump[cur ^ 1][p] = (uint16_t)(j < nsym ? sm.jump[cur][j] : nsym);
+  // 2. token starts = positions reachable from 0 by next().  Lane l owns the segment [32 l, 32 l + 32).  (a) Going
+  // backwards through its segment every lane finds, for each position, where a walk from there leaves the
+  // segment; (b) following these exits from position 0, segment by segment, gives every segment its entry
+  // point (a jump is at most 32 long, so a walk enters each segment it does not end in); (c) each lane then
+  // walks its segment from its entry.
+  const int p0 = lane * 32, p1 = p0 + 32 < nsym ? p0 + 32 : nsym;
+  uint16_t* exits = sm.exits();
+  for (int o = p1 - p0 - 1; o >= 0; --o) {
+    const int nx = (int)(sm.info[o * 33 + lane] & 0x7ffu);
+    exits[o * 33 + lane] = (uint16_t)(nx >= p1 ? nx : exits[(nx & 31) * 33 + lane]);
+  }
+  __syncwarp();
+  int entry = -1;
+  {
+    int e = 0;
+    for (int l = 0; l < 32 && e < nsym; ++l) {
+      const int end = (l + 1) * 32 < nsym ? (l + 1) * 32 : nsym;
+      if (e < end) {
+        if (l == lane) entry = e;
+        e = exits[(e & 31) * 33 + l];
+      }
     }
-    __syncwarp();
-    cur ^= 1;
   }
 
-  // 3. ordinals and data offsets: lane owns positions [lane * seg, lane * seg + seg)
-  const int seg = (nsym + 31) / 32;
-  const int p0 = lane * seg, p1 = p0 + seg < nsym ? p0 + seg : nsym;
+  // 3. ordinals and data offsets from a first walk
   int ntok_l = 0, bytes_l = 0;
-  for (int p = p0; p < p1; ++p) {
-    if (sm.mark[p]) { ++ntok_l; bytes_l += sm.best[p] ? 2 : (int)sizeof(Sym); }
+  for (int p = entry; p >= 0 && p < p1;) {
+    const uint32_t w = sm.info[(p & 31) * 33 + lane];
+    ++ntok_l;
+    bytes_l += (w >> 31) ? 2 : (int)sizeof(Sym);
+    p = (int)(w & 0x7ffu);
   }
   int tok_incl = ntok_l, byt_incl = bytes_l;
 #pragma unroll
@@ -274,19 +296,20 @@ __device__ __forceinline__ void lz_encode_block_warp(const Sym* __restrict__ g_i
   const int dbytes = __shfl_sync(0xffffffffu, byt_incl, 31);
   int t = tok_incl - ntok_l, dpos = byt_incl - bytes_l;
 
-  // 4. flags + data
-  for (int p = p0; p < p1; ++p) {
-    if (!sm.mark[p]) continue;
-    if (sm.best[p]) {
+  // 4. flags + data from a second walk
+  uint8_t* data = sm.data();
+  for (int p = entry; p >= 0 && p < p1; ++t) {
+    const uint32_t w = sm.info[(p & 31) * 33 + lane];
+    if (w >> 31) {
       atomicOr(&sm.flagw[t >> 5], 1u << (t & 31));
-      sm.data[dpos++] = sm.best[p];
-      sm.data[dpos++] = sm.dist[p];
+      data[dpos++] = (uint8_t)((w >> 11) & 63u);
+      data[dpos++] = (uint8_t)((w >> 17) & 63u);
     } else {
-      const uint32_t v = (uint32_t)sm.in[p];
+      const uint32_t v = sizeof(Sym) == 2 ? ((w >> 11) & 0xffffu) : (uint32_t)sm.in[p];
 #pragma unroll
-      for (unsigned b = 0; b < sizeof(Sym); ++b) sm.data[dpos++] = (uint8_t)(v >> (8 * b));
+      for (unsigned b = 0; b < sizeof(Sym); ++b) data[dpos++] = (uint8_t)(v >> (8 * b));
     }
-    ++t;
+    p = (int)(w & 0x7ffu);
   }
   __syncwarp();
   const int flag_bytes = (ntok + 7) >> 3;
@@ -298,7 +321,7 @@ __device__ __forceinline__ void lz_encode_block_warp(const Sym* __restrict__ g_i
   const uint8_t* fb = reinterpret_cast<const uint8_t*>(sm.flagw);
   for (int i = lane; i < flag_bytes; i += 32) out[2 + i] = fb[i];
   uint8_t* od = out + 2 + flag_bytes;
-  for (int i = lane; i < dbytes; i += 32) od[i] = sm.data[i];
+  for (int i = lane; i < dbytes; i += 32) od[i] = data[i];
   __syncwarp();
 }
 
