@@ -59,6 +59,8 @@ def main():
     ap.add_argument('--case', default='all')
     ap.add_argument('--iters', type=int, default=10)
     ap.add_argument('--small', action='store_true')
+    ap.add_argument('--act', type=int, default=2, help='activation of the gemm_fwd / gemm_dgrad epilogues: 0 identity, 1 ReLU, 2 GELU, 3 SiLU')
+    ap.add_argument('--no-aux', action='store_true', help='gemm_fwd without the saved-derivative output')
     ap.add_argument('--trace', action='store_true',
                     help='GEMM cases: one extra launch with the role trace; prints where the first epilogue warp waited')
     args = ap.parse_args()
@@ -107,10 +109,10 @@ def main():
                           'wait_staging_frac': round(float((stage / loop).mean()), 3)}), flush=True)
 
     if want('gemm_fwd'):
-        ms, best = timed(lambda: gemm.grouped_gemm(x, False, w1, True, gemm.EPI_BIAS_ACT, 2, bias=b1, aux=pre, out=out),
+        ms, best = timed(lambda: gemm.grouped_gemm(x, False, w1, True, gemm.EPI_BIAS_ACT, args.act, bias=b1, aux=None if args.no_aux else pre, out=out),
                          args.iters, flush)
-        report('gemm_fwd', ms, best, flops)
-        traced('gemm_fwd', lambda **kw: gemm.grouped_gemm(x, False, w1, True, gemm.EPI_BIAS_ACT, 2, bias=b1, aux=pre,
+        report('gemm_fwd' if args.act == 2 else 'gemm_fwd_act%d' % args.act, ms, best, flops)
+        traced('gemm_fwd', lambda **kw: gemm.grouped_gemm(x, False, w1, True, gemm.EPI_BIAS_ACT, args.act, bias=b1, aux=None if args.no_aux else pre,
                                                           out=out, **kw))
     if want('gemm_plain'):
         ms, best = timed(lambda: gemm.grouped_gemm(x, False, w1, True, out=out), args.iters, flush)

@@ -453,6 +453,25 @@ def _dynamic_capacity(lib, logits, top_k, normalize, group, align):
     return ladder
 
 
+def check_routing_bounds(idx, loc, slot_map, S, E, capacity, top_k):
+    """Bounds assertions on every index tensor the fused kernels address memory with (PLANMOE_DEBUG_GUARDS=1; costs
+    host synchronisations).  ``idx [K, S]``: expert of each pick; ``loc [K, S]``: its slot (>= capacity = dropped);
+    ``slot_map [E * capacity]``: owning pick ``token * K + k`` of each slot or -1.  Checked: ranges, that every kept
+    pick owns exactly the slot that points back at it, and that no slot has two owners."""
+    K = top_k
+    assert idx.shape == (K, S) and loc.shape == (K, S) and slot_map.numel() == E * capacity, "routing tensor shapes"
+    assert int(idx.min()) >= 0 and int(idx.max()) < E, "expert index out of range"
+    assert int(loc.min()) >= 0, "negative slot"
+    assert int(slot_map.min()) >= -1 and int(slot_map.max()) < S * K, "slot map entry out of range"
+    kept = loc < capacity
+    tok = torch.arange(S, device=idx.device).unsqueeze(0).expand(K, S)
+    kk = torch.arange(K, device=idx.device).unsqueeze(1).expand(K, S)
+    slots = (idx.long() * capacity + loc.long())[kept]
+    owners = (tok * K + kk)[kept]
+    assert torch.equal(slot_map.long()[slots], owners), "a kept pick does not own its slot"
+    assert int((slot_map >= 0).sum()) == int(kept.sum()), "slot map has owners that no pick claims"
+
+
 def forward(layer, x, gctx, top_k, capacity_factor, degree):
     """Run the fused path for ``layer`` on tokens ``x [S, M]``; returns ``(y [S, O], l_aux)``.
 
@@ -505,6 +524,8 @@ def forward(layer, x, gctx, top_k, capacity_factor, degree):
         from ..impls import losses
         topk_logits = logits.float().gather(1, idx.t().long())
         l_aux = losses.load_importance_loss(F.softmax(clean.float(), dim=1), topk_logits, E, gctx.gate_noise)
+    if T.debug_guards():
+        check_routing_bounds(idx, loc, slot_map, S, E, capacity, top_k)
     ex = layer.experts
     meta = dict(state=st, idx=idx, loc=loc, slot_map=slot_map, E=E, C=capacity, degree=degree, K=top_k,
                 act=ACT_CODES[ex.act_name], postscore=layer.is_postscore, q8=(layer.compress_name == 'int8'))

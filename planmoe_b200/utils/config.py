@@ -50,7 +50,7 @@ ENV = {
                                'error and returns'),
     'PLANMOE_HEAP_MB': ('1024', 'size of a symmetric-heap segment'),
     'PLANMOE_DEBUG_GUARDS': ('0', '1: canary bands around heap blocks (checked by Transport.check) and NaN-filled receive '
-                             'buffers'),
+                             'buffers; host-side range and ownership assertions on the routing tensors'),
     'PLANMOE_PLAN_CACHE': ('~/.cache/planmoe_b200/plans.json', 'where the adaptive scheduler stores frozen plans'),
     'PLANMOE_PLAN_CACHE_DISABLE': ('0', '1: always calibrate'),
     'PLANMOE_STAGE_TIMERS': ('0', '1: CUDA events + NVTX ranges around every stage of the fused layer'),

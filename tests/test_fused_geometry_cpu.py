@@ -178,3 +178,23 @@ def test_push_epilogue_rows_and_arrivals(W, E_l, C, d, N):
         if Cc % 32 == 0:
             for m0 in range(0, R, 32):
                 assert m0 // Cc == (m0 + 31) // Cc
+
+
+def test_routing_bounds_check_accepts_consistent_and_rejects_corrupt():
+    import pytest
+    import torch
+    from planmoe_b200.ops.fused_moe import check_routing_bounds
+    S, E, C, K = 6, 2, 3, 1
+    idx = torch.tensor([[0, 1, 0, 0, 1, 0]], dtype=torch.int32)
+    loc = torch.tensor([[0, 0, 1, 2, 1, 3]], dtype=torch.int32)          # the last pick is dropped (slot 3 >= C)
+    slot_map = torch.tensor([0, 2, 3, 1, 4, -1], dtype=torch.int32)      # expert 0: tokens 0, 2, 3; expert 1: 1, 4, empty
+    check_routing_bounds(idx, loc, slot_map, S, E, C, K)
+    bad = slot_map.clone(); bad[5] = 5                                   # an owner nobody claims
+    with pytest.raises(AssertionError):
+        check_routing_bounds(idx, loc, bad, S, E, C, K)
+    bad = idx.clone(); bad[0, 2] = 2                                     # expert out of range
+    with pytest.raises(AssertionError):
+        check_routing_bounds(bad, loc, slot_map, S, E, C, K)
+    bad = slot_map.clone(); bad[1] = 3; bad[2] = 2                       # two picks swapped: they no longer own their slots
+    with pytest.raises(AssertionError):
+        check_routing_bounds(idx, loc, bad, S, E, C, K)
