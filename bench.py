@@ -14,14 +14,14 @@ under the same timing protocol (eager loop, one event pair per step, L2 flushed 
 
 For N > 1 launch one process per GPU with ``python -m torch.distributed.run --nproc-per-node N``.
 Rank 0 prints ONE JSON line.  ``value`` is whole-job tokens/s from CUDA-event timing of exactly
-K steps (max over ranks).  By default the step (forward + backward + SGD) is captured once as a
-two-step CUDA graph and the K steps are K/2 replays inside one event bracket; a step touches about
-0.6 GB, several times the L2, so no step finds its inputs cached.  The K-step bracket is repeated ``--repeats`` times and the median bracket is
+K steps (max over ranks).  By default the two steps of the layer's buffer cycle (forward + backward +
+SGD each) are captured once as two CUDA graphs and the K steps are K replays inside one event bracket;
+a step touches about 0.6 GB, several times the L2, so no step finds its inputs cached.  The K-step bracket is repeated ``--repeats`` times and the median bracket is
 reported (``spread`` holds every bracket).  ``--no-graph`` (and any run in
 which capture fails) times the eager loop instead, one event pair per step with a 256 MiB L2 flush
 between steps outside the brackets.  ``e2e`` repeats the measurement through the public API
-including, every step, the pinned-host -> device copy of the step's input (on a copy stream, one
-step or graph replay ahead) and a device -> host read of the loss.
+including, every step, the pinned-host -> device copy of the step's input (on a copy stream, up to
+two steps ahead) and a device -> host read of the loss.
 """
 
 import argparse
@@ -418,7 +418,8 @@ def run(args, world, rank, local_rank):
                 turn[0] += 1
                 return loss.detach().float().reshape(1)
             lc0 = launch_count()
-            graphed = GraphedSteps(graph_step, unroll=2, warmup=2)
+            # one graph per step of the two-step cycle, so that the end-to-end loop can feed steps one by one
+            graphed = GraphedSteps(graph_step, unroll=2, warmup=2, split=True)
             launches_per_step = (launch_count() - lc0) // (2 * 2 + 2)      # warm-up steps + the captured pair
         except Exception as exc:                                            # capture not possible: eager loop
             print('bench.py: CUDA-graph capture failed (%s); timing the eager loop' % (exc,), file=sys.stderr)
@@ -445,7 +446,7 @@ def run(args, world, rank, local_rank):
         barrier()
         host_t0 = time.perf_counter()
         if graphed is not None:
-            # K steps = K // 2 replays of the two-step graph (+ one eager step if K is odd), one event bracket
+            # K steps = K // 2 replays of the two graphs of the cycle (+ one eager step if K is odd), one event bracket
             # around all of them.  The working set of a step (about 0.6 GB of activations, receive buffers and
             # weights) is several times the 126 MB L2, so no step finds its inputs cached.
             t_s, t_e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -484,55 +485,63 @@ def run(args, world, rank, local_rank):
     copy_stream = torch.cuda.Stream(device=device)
     cur = torch.cuda.current_stream()
     losses_read = 0
+    # context for the end-to-end number (outside its timed region): what one input copy costs on this box while
+    # every rank copies at once and nothing else runs
+    probe = torch.empty_like(x_dev)
+    barrier()
+    p_s, p_e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    p_s.record()
+    probe.copy_(host_x, non_blocking=True)
+    p_e.record()
+    p_e.synchronize()
+    h2d_alone_ms = p_s.elapsed_time(p_e)
+    del probe
     e2e_s = torch.cuda.Event(enable_timing=True)
     e2e_e = torch.cuda.Event(enable_timing=True)
     if graphed is not None:
-        # Graph mode: a replay runs two steps on two static inputs.  The inputs of the next replays are copied
-        # host -> device into a ring of staging pairs on the copy stream (up to two replays ahead) while this replay
-        # computes, moved into the static inputs by two device copies right before the replay, and the two losses of
-        # a replay are copied to pinned host memory behind it and read one replay later.
+        # Graph mode: step i replays graph i & 1 on static input i & 1.  The inputs of the next steps are copied
+        # host -> device into a ring of staging buffers on the copy stream (up to two steps ahead) while this step
+        # computes, moved into the static input by a device copy right before the replay, and the loss of a step
+        # is copied to pinned host memory behind it and read one step later.
         depth = 3
-        stage_pairs = [[torch.empty_like(x_dev), torch.empty_like(x_dev)] for _ in range(depth)]
-        pair_ready = [torch.cuda.Event() for _ in range(depth)]
-        pair_free = [torch.cuda.Event() for _ in range(depth)]
-        loss_pair = [torch.zeros(2, dtype=torch.float32).pin_memory() for _ in range(2)]
-        pair_done = [torch.cuda.Event() for _ in range(2)]
+        stage_bufs = [torch.empty_like(x_dev) for _ in range(depth)]
+        buf_ready = [torch.cuda.Event() for _ in range(depth)]
+        buf_free = [torch.cuda.Event() for _ in range(depth)]
+        loss_host = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(2)]
+        loss_done = [torch.cuda.Event() for _ in range(2)]
 
-        def prefetch_pair(r):
-            b = r % depth
+        def prefetch_step(i):
+            b = i % depth
             with torch.cuda.stream(copy_stream):
-                copy_stream.wait_event(pair_free[b])
-                stage_pairs[b][0].copy_(host_x, non_blocking=True)
-                stage_pairs[b][1].copy_(host_x, non_blocking=True)
-                pair_ready[b].record(copy_stream)
+                copy_stream.wait_event(buf_free[b])
+                stage_bufs[b].copy_(host_x, non_blocking=True)
+                buf_ready[b].record(copy_stream)
 
-        n_rep = args.steps // 2
+        n_graph = args.steps - (args.steps & 1)          # the cycle has two steps: an odd last step runs eagerly
         for b in range(depth):
-            pair_free[b].record(cur)
+            buf_free[b].record(cur)
         barrier()
         e2e_s.record()
-        for r in range(min(depth - 1, n_rep)):
-            prefetch_pair(r)
-        for r in range(n_rep):
-            b = r % depth
-            cur.wait_event(pair_ready[b])
-            x_static[0].copy_(stage_pairs[b][0], non_blocking=True)
-            x_static[1].copy_(stage_pairs[b][1], non_blocking=True)
-            pair_free[b].record(cur)
-            if r + depth - 1 < n_rep:
-                prefetch_pair(r + depth - 1)
-            outs = graphed.replay()
-            loss_pair[r & 1][0:1].copy_(outs[0], non_blocking=True)
-            loss_pair[r & 1][1:2].copy_(outs[1], non_blocking=True)
-            pair_done[r & 1].record(cur)
-            if r > 0:
-                pair_done[(r - 1) & 1].synchronize()
-                _ = float(loss_pair[(r - 1) & 1][0]) + float(loss_pair[(r - 1) & 1][1])
-                losses_read += 2
-        if n_rep:
-            pair_done[(n_rep - 1) & 1].synchronize()
-            _ = float(loss_pair[(n_rep - 1) & 1][0]) + float(loss_pair[(n_rep - 1) & 1][1])
-            losses_read += 2
+        for i in range(min(depth - 1, n_graph)):
+            prefetch_step(i)
+        for i in range(n_graph):
+            b = i % depth
+            cur.wait_event(buf_ready[b])
+            x_static[i & 1].copy_(stage_bufs[b], non_blocking=True)
+            buf_free[b].record(cur)
+            if i + depth - 1 < n_graph:
+                prefetch_step(i + depth - 1)
+            out = graphed.replay_one(i & 1)
+            loss_host[i & 1].copy_(out, non_blocking=True)
+            loss_done[i & 1].record(cur)
+            if i > 0:
+                loss_done[(i - 1) & 1].synchronize()
+                _ = float(loss_host[(i - 1) & 1][0])
+                losses_read += 1
+        if n_graph:
+            loss_done[(n_graph - 1) & 1].synchronize()
+            _ = float(loss_host[(n_graph - 1) & 1][0])
+            losses_read += 1
         if args.steps & 1:                             # odd K: one more step, eagerly
             x_in = host_x.to(device, non_blocking=True)
             loss = step(x_in)
@@ -622,7 +631,9 @@ def run(args, world, rank, local_rank):
                        'reported': 'median bracket of K steps, max over ranks per bracket'},
             'e2e': {'value': tokens / (e2e_ms / 1e3), 'unit': 'tokens/s',
                     'h2d_bytes_per_step': host_x.numel() * host_x.element_size(),
-                    'd2h_bytes_per_step': host_loss.numel() * host_loss.element_size()},
+                    'd2h_bytes_per_step': host_loss.numel() * host_loss.element_size(),
+                    'ms_per_step': round(e2e_ms / args.steps, 5),
+                    'h2d_copy_alone_ms': round(h2d_alone_ms, 4)},
             'gpu_launches': int(launches),
             'host_enqueue_ms_per_step': round(host_ms, 4),
             'cpu_affinity': affinity_cpus,

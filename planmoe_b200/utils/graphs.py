@@ -28,11 +28,17 @@ import torch
 
 
 class GraphedSteps:
-    def __init__(self, step_fn, unroll=2, warmup=3):
-        """``step_fn()`` runs one step on static inputs and returns a tensor (the loss) or None."""
+    def __init__(self, step_fn, unroll=2, warmup=3, split=False):
+        """``step_fn()`` runs one step on static inputs and returns a tensor (the loss) or None.
+
+        ``split=True`` captures every one of the ``unroll`` steps as a graph of its own (one shared memory pool;
+        replay them in capture order, cyclically): ``replay_one(i)`` then runs a single step, so a caller that
+        feeds each step its own input can overlap the copy for step i + 1 with step i."""
         assert unroll >= 1
         self.unroll = unroll
+        self.split = bool(split)
         self.outputs = []
+        self.graphs = []
         gc.collect()
         prev = torch.cuda.current_stream()
         side = torch.cuda.Stream()
@@ -42,36 +48,50 @@ class GraphedSteps:
                 step_fn()
         prev.wait_stream(side)
         torch.cuda.synchronize()
-        self.graph = torch.cuda.CUDAGraph()
-        ctx = torch.cuda.graph(self.graph, stream=side)
-        began = False
-        try:
-            ctx.__enter__()
-            began = True
-            for _ in range(unroll):
-                self.outputs.append(step_fn())
-            ctx.__exit__(None, None, None)
-        except BaseException:
-            # torch.cuda.graph does not unwind when ending the capture fails: do it here
-            if began:
-                try:
-                    self.graph.capture_end()
-                except Exception:
-                    pass
-                try:
-                    torch._C._cuda_endAllocateToPool(torch.cuda.current_device(), self.graph.pool())
-                except Exception:
-                    pass
-            torch.cuda.set_stream(prev)
+        n_graphs = unroll if self.split else 1
+        per_graph = 1 if self.split else unroll
+        for gi in range(n_graphs):
+            graph = torch.cuda.CUDAGraph()
+            kw = {'pool': self.graphs[0].pool()} if self.graphs else {}
+            ctx = torch.cuda.graph(graph, stream=side, **kw)
+            began = False
             try:
-                torch.cuda.synchronize()
-            except Exception:
-                pass
-            self.outputs = []
-            raise
+                ctx.__enter__()
+                began = True
+                for _ in range(per_graph):
+                    self.outputs.append(step_fn())
+                ctx.__exit__(None, None, None)
+            except BaseException:
+                # torch.cuda.graph does not unwind when ending the capture fails: do it here
+                if began:
+                    try:
+                        graph.capture_end()
+                    except Exception:
+                        pass
+                    try:
+                        torch._C._cuda_endAllocateToPool(torch.cuda.current_device(), graph.pool())
+                    except Exception:
+                        pass
+                torch.cuda.set_stream(prev)
+                try:
+                    torch.cuda.synchronize()
+                except Exception:
+                    pass
+                self.outputs = []
+                self.graphs = []
+                raise
+            self.graphs.append(graph)
+        self.graph = self.graphs[0]
 
     def replay(self):
         """Run ``unroll`` steps; returns the list of per-step outputs (static tensors, overwritten by the
         next replay)."""
-        self.graph.replay()
+        for g in self.graphs:
+            g.replay()
         return self.outputs
+
+    def replay_one(self, i):
+        """Split mode: run step ``i`` of the cycle (call with i = 0, 1, ..., unroll - 1, 0, ... in that order)."""
+        assert self.split, "replay_one needs split=True"
+        self.graphs[i].replay()
+        return self.outputs[i]

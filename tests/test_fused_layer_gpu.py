@@ -222,9 +222,10 @@ def test_fused_layer_survives_degree_changes():
         assert torch.equal(y, outs[0])
 
 
-def test_fused_layer_replays_under_cuda_graph():
-    """Two training steps (forward + backward + SGD) captured in one CUDA graph and replayed give the same
-    parameters as the same number of eager steps."""
+@pytest.mark.parametrize('split', [False, True])
+def test_fused_layer_replays_under_cuda_graph(split):
+    """Two training steps (forward + backward + SGD) captured in one CUDA graph, or in one graph each, and replayed
+    give the same parameters as the same number of eager steps."""
     from planmoe_b200.parallel import transport
     from planmoe_b200.utils.graphs import GraphedSteps
 
@@ -249,9 +250,9 @@ def test_fused_layer_replays_under_cuda_graph():
     for _ in range(warm * unroll + replays * unroll):     # the capture pass itself executes nothing
         one_step(layer_e, opt_e)
     layer_g, opt_g = make()
-    g = GraphedSteps(lambda: one_step(layer_g, opt_g), unroll=unroll, warmup=warm)     # warm-up + the captured pair
+    g = GraphedSteps(lambda: one_step(layer_g, opt_g), unroll=unroll, warmup=warm, split=split)
     for _ in range(replays):
-        outs = g.replay()
+        outs = [g.replay_one(0), g.replay_one(1)] if split else g.replay()
     torch.cuda.synchronize()
     transport.get_transport(layer_g.group).check()
     assert torch.isfinite(outs[-1]).all()
