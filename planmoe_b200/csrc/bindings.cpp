@@ -318,7 +318,7 @@ struct GemmOpts {
   c10::optional<Tensor> bias, aux, out;
   // flag gate
   int64_t gate_flags_ptr = 0, gate_rows = 0, gate_want = 0, gate_want_ptr = 0;
-  int64_t gate_mode = 0, gate_nblk = 0, perm_w = 0, perm_seg_rows = 0;
+  int64_t gate_mode = 0, gate_nblk = 0, perm_w = 0, perm_seg_rows = 0, perm_local_first = 0;
   // push
   int64_t heap_bases_ptr = 0, push_data_off = 0, push_flag_off = 0, push_rows = 0, push_C = 0, push_c0 = 0,
           push_chunk = 0, W = 1, my_rank = 0, chunk_groups = 0, push_q8 = 0, push_scale_off = 0;
@@ -392,7 +392,7 @@ Tensor grouped_gemm_op(const Tensor& A, bool a_mn, const Tensor& B, bool b_mn, c
   g.gate_flags = reinterpret_cast<const unsigned long long*>(o.gate_flags_ptr);
   g.gate_rows = o.gate_rows; g.gate_want = o.gate_want;
   g.gate_want_ptr = reinterpret_cast<const unsigned long long*>(o.gate_want_ptr);
-  g.gate_mode = o.gate_mode; g.gate_nblk = o.gate_nblk; g.perm_w = o.perm_w; g.perm_seg_rows = o.perm_seg_rows;
+  g.gate_mode = o.gate_mode; g.gate_nblk = o.gate_nblk; g.perm_w = o.perm_w; g.perm_seg_rows = o.perm_seg_rows; g.perm_local_first = (int)o.perm_local_first;
   g.heap_bases = reinterpret_cast<const unsigned long long*>(o.heap_bases_ptr);
   g.push_data_off = o.push_data_off; g.push_flag_off = o.push_flag_off; g.push_rows = o.push_rows;
   g.push_C = o.push_C; g.push_c0 = o.push_c0; g.push_chunk = o.push_chunk; g.W = o.W; g.my_rank = o.my_rank;
@@ -761,6 +761,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_readwrite("gate_nblk", &GemmOpts::gate_nblk)
       .def_readwrite("perm_w", &GemmOpts::perm_w)
       .def_readwrite("perm_seg_rows", &GemmOpts::perm_seg_rows)
+      .def_readwrite("perm_local_first", &GemmOpts::perm_local_first)
       .def_readwrite("copy_nblk", &GemmOpts::copy_nblk)
       .def_readwrite("trace_ptr", &GemmOpts::trace_ptr)
       .def_readwrite("dq_ptr", &GemmOpts::dq_ptr)

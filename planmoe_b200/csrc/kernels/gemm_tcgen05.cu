@@ -242,7 +242,7 @@ struct KernelParams {
   const __nv_bfloat16* bias; long long bias_group_stride;
   const unsigned long long* gate_flags; int gate_rows; unsigned long long gate_want;
   const unsigned long long* gate_want_ptr;
-  int gate_mode, gate_nblk, perm_w, perm_q;
+  int gate_mode, gate_nblk, perm_w, perm_q, perm_local, send_local_first;
   const void* a_ptr; long long a_row_stride, a_group_stride;   // the A operand as plain memory (de-quantiser output)
   const unsigned long long* heap_bases; unsigned long long push_data_off, push_flag_off;
   int push_rows, push_C, push_c0, push_chunk, W, my_rank;
@@ -358,15 +358,46 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// Tile order.  A tile index runs over (group, m-tile, n-tile) with the n-tile fastest.  When the A operand
-// is filled by the fused dispatch send and every source rank's segment of a group holds perm_q > 1 tiles,
-// the m-tiles are visited segment-interleaved (tile 0 of every source, then tile 1 of every source, ...):
-// that is the order in which the senders deliver rows, so the tensor cores are never parked on a segment
-// whose rows leave last.
+// Tile order.  A tile index is (m-tile ordinal) * nt_count + n-tile; the m-tile ordinal runs over (group,
+// m-tile) in the order in which the A rows become available.  Plain launches: groups in order, m-tiles in
+// order.  When the A operand is filled by the fused dispatch send and every source rank's segment of a group
+// holds perm_q > 1 whole tiles:
+//   perm_local == 0: within a group the m-tiles are visited segment-interleaved (tile 0 of every source, then
+//                    tile 1 of every source, ...), the order in which the senders deliver rows;
+//   perm_local == 1: within a pipeline chunk, first this rank's own segment of every group (those rows never
+//                    cross a link and the senders deliver them first), then, group by group, the other
+//                    sources segment-interleaved starting at the right-hand neighbour.
 // ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ int permute_mt(const KernelParams& p, int mt_lin) {
-  if (p.perm_q <= 1) return mt_lin;
-  return (mt_lin % p.perm_w) * p.perm_q + mt_lin / p.perm_w;
+__device__ __forceinline__ void mtile_coord(const KernelParams& p, int ord, int mt_count, int& g, int& mt) {
+  if (p.perm_q <= 1) {
+    g = ord / mt_count;
+    mt = ord - g * mt_count;
+    return;
+  }
+  if (!p.perm_local) {
+    g = ord / mt_count;
+    const int l = ord - g * mt_count;
+    mt = (l % p.perm_w) * p.perm_q + l / p.perm_w;
+    return;
+  }
+  const int gpc = p.chunk_groups > 0 ? p.chunk_groups : p.groups;      // groups of one pipeline chunk
+  const int per_chunk = gpc * mt_count;
+  const int chunk = ord / per_chunk;
+  int u = ord - chunk * per_chunk;
+  int el;
+  if (u < gpc * p.perm_q) {                                            // own segments
+    el = u / p.perm_q;
+    mt = p.my_rank * p.perm_q + (u - el * p.perm_q);
+  } else {
+    u -= gpc * p.perm_q;
+    const int others = p.perm_w - 1, rem = others * p.perm_q;
+    el = u / rem;
+    const int l = u - el * rem;
+    int src = p.my_rank + 1 + l % others;
+    if (src >= p.perm_w) src -= p.perm_w;
+    mt = src * p.perm_q + l / others;
+  }
+  g = chunk * gpc + el;
 }
 
 __device__ __forceinline__ void red_release_gpu_add(unsigned long long* p, unsigned long long v) {
@@ -423,14 +454,36 @@ __device__ __forceinline__ void copy_role(const KernelParams& p, uint8_t* cring,
 
   // geometry of an item (uniform over the warp)
   struct Item { int r, g, j, el, row0, nrows; };
+  // Item order.  send_local_first == 0: (group, row range, destination) with the destinations starting at my
+  // right-hand neighbour.  send_local_first == 1: chunk by chunk, first the items that stay on this rank (every
+  // group of the chunk), then the others as (group, row range, destination): the destinations' tile loops start
+  // on their own rows, which reach them without crossing a link.
+  const long long per_chunk_loc = (long long)c.E_local * items_per_seg;
+  const long long per_chunk = per_chunk_loc * p.W;
   auto decode = [&](long long item) {
     Item it;
-    const int rr = (int)(item % p.W);
-    long long t = item / p.W;
-    const int sub = (int)(t % items_per_seg);
-    it.g = (int)(t / items_per_seg);                             // chunk * E_local + local expert
-    it.j = it.g / c.E_local; it.el = it.g - it.j * c.E_local;
-    it.r = (p.my_rank + 1 + rr) % p.W;                           // start at my right-hand neighbour
+    int rr, sub;
+    if (!p.send_local_first || p.W == 1) {
+      rr = (int)(item % p.W);
+      long long t = item / p.W;
+      sub = (int)(t % items_per_seg);
+      it.g = (int)(t / items_per_seg);                           // chunk * E_local + local expert
+      it.j = it.g / c.E_local; it.el = it.g - it.j * c.E_local;
+    } else {
+      it.j = (int)(item / per_chunk);
+      long long t = item - (long long)it.j * per_chunk;
+      if (t < per_chunk_loc) {
+        rr = p.W - 1;                                            // myself
+      } else {
+        t -= per_chunk_loc;
+        rr = (int)(t % (p.W - 1));
+        t /= (p.W - 1);
+      }
+      sub = (int)(t % items_per_seg);
+      it.el = (int)(t / items_per_seg);
+      it.g = it.j * c.E_local + it.el;
+    }
+    it.r = (p.my_rank + 1 + rr) % p.W;                           // rr == W - 1 is this rank
     it.row0 = sub * half;
     it.nrows = min(half, Cc - it.row0);
     return it;
@@ -558,8 +611,8 @@ __device__ __forceinline__ void dequant_role(const KernelParams& p, __nv_bfloat1
     const int sub = (int)(u % kUnitsPerBlock);
     long long t = u / kUnitsPerBlock;
     const int b = (int)(t % CG); t /= CG;
-    const int mt = permute_mt(p, (int)(t % mt_count));
-    const int g = (int)(t / mt_count);
+    int g, mt;
+    mtile_coord(p, (int)t, mt_count, g, mt);
     const int blk = mt * CG + b;
     const int row0 = blk * kGateBlock + sub * kDequantRows;
     if (row0 >= p.M) continue;
@@ -712,8 +765,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const unsigned long long gate_want = p.gate_want_ptr != nullptr ? *p.gate_want_ptr : p.gate_want;
       for (int tile = unit; tile < tiles && ok; tile += nunits) {
         const int nt = tile % nt_count;
-        const int mt = permute_mt(p, (tile / nt_count) % mt_count);
-        const int g = tile / (nt_count * mt_count);
+        int g, mt;
+        mtile_coord(p, tile / nt_count, mt_count, g, mt);
         const int m0 = mt * (BM * CG) + cr * BM;                         // my 128 rows of the tile
         const int n0 = nt * BN + cr * G::kBRows;                         // my share of the B columns
         const int gb = p.chunk_groups > 0 ? g % p.chunk_groups : g;      // group of the B operand
@@ -850,8 +903,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const long long epi_t0 = trace != nullptr ? clock64() : 0ll;
     for (int tile = unit; tile < tiles && ok; tile += nunits) {
       const int nt = tile % nt_count;
-      const int mt = permute_mt(p, (tile / nt_count) % mt_count);
-      const int g = tile / (nt_count * mt_count);
+      int g, mt;
+      mtile_coord(p, tile / nt_count, mt_count, g, mt);
       const int m0 = mt * (BM * CG) + cr * BM, n0 = nt * BN;
 
       // Activation backward: the 32 x 64 slab of saved activation derivatives this warp needs first
@@ -1432,10 +1485,12 @@ cudaError_t launch_grouped_gemm(const GemmArgs& a, cudaStream_t stream) {
   kp.gate_flags = a.gate_flags; kp.gate_rows = a.gate_rows > 0 ? a.gate_rows : a.M; kp.gate_want = a.gate_want;
   kp.gate_want_ptr = a.gate_want_ptr;
   kp.gate_mode = a.gate_mode; kp.gate_nblk = a.gate_nblk;
-  kp.perm_w = 0; kp.perm_q = 0;
+  kp.perm_w = 0; kp.perm_q = 0; kp.perm_local = 0;
+  kp.send_local_first = a.perm_local_first ? 1 : 0;
   if (a.perm_w > 1 && a.perm_seg_rows > BM * cg && a.perm_seg_rows % (BM * cg) == 0 &&
       (long long)a.perm_w * a.perm_seg_rows == a.M) {
     kp.perm_w = a.perm_w; kp.perm_q = a.perm_seg_rows / (BM * cg);   // every segment is perm_q > 1 whole tiles
+    kp.perm_local = a.perm_local_first ? 1 : 0;
   }
   kp.a_ptr = a.A.ptr; kp.a_row_stride = a.A.row_stride;
   kp.a_group_stride = a.A.group_stride > 0 ? a.A.group_stride : a.A.rows * a.A.row_stride;

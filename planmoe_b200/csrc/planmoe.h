@@ -148,6 +148,9 @@ struct GemmArgs {
   // number (> 1) of tiles, the tiles are visited segment-interleaved (tile 0 of every source, then tile 1, ...),
   // the order in which the fused send delivers rows
   int perm_w, perm_seg_rows;
+  // 1: the copy role sends the rows that stay on this rank first (chunk by chunk) and the tile loop starts on this
+  // rank's own segments; 0: destinations and sources are interleaved from the first row on
+  int perm_local_first;
   // push epilogue: row m of group g belongs to rank s = m / push_rows; it is stored at
   // heap_bases[s] + push_data_off + ((my_rank*groups + g) * push_C + push_c0 + m % push_rows) * N
   // and flag (push_flag_off)[push_chunk * W + my_rank] on rank s is incremented once per tile.

@@ -185,6 +185,13 @@ def _fuse_send(world):
 _TRACE = {}
 
 
+def _local_first():
+    """PLANMOE_LOCAL_FIRST=1: own rows are sent first and the tile loop starts on them.  Off by default: at 2 GPUs it
+    measured 2.6 % slower per step (the first tile waits 15 us instead of 20, but the link idles while the own rows
+    are copied and the second and third tiles then wait for the late remote rows)."""
+    return 1 if os.environ.get('PLANMOE_LOCAL_FIRST', '0') == '1' else 0
+
+
 def _trace_buffer(phase, device):
     if os.environ.get('PLANMOE_GEMM_TRACE', '0') != '1':
         return None
@@ -235,6 +242,7 @@ def _send_and_gemm(lib, bs, phase, src, slot_map, gates, K, E, C, W, rank, d, ge
         return
     nblk = (W * Cc + GATE_BLOCK - 1) // GATE_BLOCK
     opts = dict(gate_mode=1, gate_nblk=nblk, gate_want_ptr=bs.expect(phase, 1), perm_w=W, perm_seg_rows=Cc,
+                perm_local_first=_local_first(),
                 heap_bases_ptr=bases, copy_x=src, copy_slot_map=slot_map, copy_K=K, copy_E_local=E // W, copy_C=C,
                 copy_chunks=d, copy_ctas=1, copy_data_off=bs.landing_off(phase), copy_flag_off=bs.flag_off(phase),
                 copy_nblk=nblk)

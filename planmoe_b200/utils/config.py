@@ -43,6 +43,8 @@ ENV = {
     'PLANMOE_GEMM_TMA_STORE': ('1', '0: epilogues write with 16-byte stores instead of bulk tensor stores'),
     'PLANMOE_GEMM_COPY_VARIANT': ('0', '1: plain launches use the kernel variant that carries the dispatch send (one ring '
                                   'stage less); for measuring that variant alone'),
+    'PLANMOE_LOCAL_FIRST': ('0', '0: the dispatch send interleaves all destinations from the first row and the tile loop '
+                            'visits sources round-robin; 1: own rows are sent and consumed first (measured slower)'),
     'PLANMOE_GEMM_TRACE': ('0', '1: fused launches record per-CTA role timestamps; fused_moe.last_trace() summarises them'),
     'PLANMOE_COPY_DBG': ('0', 'bit 0: fence + release on every flag add of the dispatch send; bit 1: all flag adds at the end '
                          '(experiments)'),

@@ -10,7 +10,7 @@ world size the layer supports (1, 2, 4, 8) without a GPU:
     arrivals each (chunk, source) flag receives equals what the host helper ``gemm_push_arrivals`` tells
     the receiver to wait for.
 
-The formulas mirror ``csrc/kernels/gemm_tcgen05.cu`` (``copy_role``, ``dequant_role``, ``permute_mt``, the
+The formulas mirror ``csrc/kernels/gemm_tcgen05.cu`` (``copy_role``, ``dequant_role``, ``mtile_coord``, the
 producer's gate, the push epilogue) and ``ops/fused_moe.py``."""
 
 import itertools
@@ -24,7 +24,7 @@ GATE_BLOCK = 128    # rows per arrival flag
 COPY_BYTES, MIN_SLOT = 65536, 4096
 
 
-def _copy_items(W, my_rank, E_l, C, d, M, grid, quant=False):
+def _copy_items(W, my_rank, E_l, C, d, M, grid, quant=False, local_first=True):
     """(cta, dest, group, first row in the destination group, rows, [dst byte offset of each row]) per item."""
     Cc = C // d
     wire = M + 16 if quant else M * 2                        # bytes of a row, at the source and on the wire
@@ -37,9 +37,21 @@ def _copy_items(W, my_rank, E_l, C, d, M, grid, quant=False):
     out = []
     for cta in range(grid):
         for item in range(cta, n_items, grid):
-            rr = item % W
-            t = item // W
-            sub, g = t % per_seg, t // per_seg
+            if not local_first or W == 1:
+                rr = item % W
+                t = item // W
+                sub, g = t % per_seg, t // per_seg
+            else:                                            # chunk by chunk: own rows of every group, then the others
+                per_chunk_loc = E_l * per_seg
+                j, t = divmod(item, per_chunk_loc * W)
+                if t < per_chunk_loc:
+                    rr = W - 1
+                else:
+                    t -= per_chunk_loc
+                    rr = t % (W - 1)
+                    t //= W - 1
+                sub, el = t % per_seg, t // per_seg
+                g = j * E_l + el
             r = (my_rank + 1 + rr) % W
             row0 = sub * lanes
             nrows = min(lanes, Cc - row0)
@@ -48,11 +60,12 @@ def _copy_items(W, my_rank, E_l, C, d, M, grid, quant=False):
     return out, wire
 
 
+@pytest.mark.parametrize("local_first", [False, True])
 @pytest.mark.parametrize("quant", [False, True])
 @pytest.mark.parametrize("W,E_l,C,d,M", [(1, 2, 8192, 1, 2048), (2, 2, 4096, 4, 2048), (4, 2, 2048, 2, 2048),
                                         (8, 2, 1024, 4, 2048), (8, 8, 320, 1, 1024), (8, 1, 96, 2, 4096),
                                         (4, 3, 40, 1, 72), (2, 2, 260, 1, 8192)])
-def test_dispatch_send_covers_every_slot_once(W, E_l, C, d, M, quant):
+def test_dispatch_send_covers_every_slot_once(W, E_l, C, d, M, quant, local_first):
     if quant and M % 16:
         pytest.skip("int8 rows need a multiple of 16 elements")
     grid = 148
@@ -61,7 +74,13 @@ def test_dispatch_send_covers_every_slot_once(W, E_l, C, d, M, quant):
     nblk = (R + GATE_BLOCK - 1) // GATE_BLOCK
     flags = {}                                               # (dest, group, block) -> rows added by all senders
     for my_rank in range(W):
-        items, wire = _copy_items(W, my_rank, E_l, C, d, M, grid, quant)
+        items, wire = _copy_items(W, my_rank, E_l, C, d, M, grid, quant, local_first)
+        if local_first and W > 1:                            # a chunk's own-rank items come before its other items
+            per_cta = {}
+            for cta, r, g, first, nrows, dsts in items:
+                per_cta.setdefault(cta, []).append((g // E_l, r != my_rank))
+            for seq in per_cta.values():
+                assert seq == sorted(seq)
         buf_bytes = d * E_l * W * Cc * wire                  # receive buffer of one destination rank
         seen = set()
         rows_to = {}
@@ -88,15 +107,30 @@ def test_dispatch_send_covers_every_slot_once(W, E_l, C, d, M, quant):
                 assert flags.get((r, g, blk), 0) == min(GATE_BLOCK, R - blk * GATE_BLOCK), (r, g, blk)
 
 
-def _permute_mt(mt_lin, perm_w, perm_q):
+def _mtile_coord(ordinal, mt_count, perm_w, perm_q, perm_local, gpc, my_rank):
+    """(group, m-tile) of the ordinal-th m-tile in consumption order (mtile_coord of the kernel)."""
     if perm_q <= 1:
-        return mt_lin
-    return (mt_lin % perm_w) * perm_q + mt_lin // perm_w
+        return divmod(ordinal, mt_count)
+    if not perm_local:
+        g, l = divmod(ordinal, mt_count)
+        return g, (l % perm_w) * perm_q + l // perm_w
+    chunk, u = divmod(ordinal, gpc * mt_count)
+    if u < gpc * perm_q:
+        el, k = divmod(u, perm_q)
+        mt = my_rank * perm_q + k
+    else:
+        u -= gpc * perm_q
+        others = perm_w - 1
+        el, l = divmod(u, others * perm_q)
+        src = (my_rank + 1 + l % others) % perm_w
+        mt = src * perm_q + l // others
+    return chunk * gpc + el, mt
 
 
+@pytest.mark.parametrize("perm_local", [0, 1])
 @pytest.mark.parametrize("W,E_l,C,d,cg", [(1, 2, 8192, 1, 2), (2, 2, 4096, 4, 2), (4, 2, 2048, 2, 2), (8, 2, 1024, 4, 2),
                                          (8, 2, 1024, 1, 2), (8, 2, 1024, 8, 2), (8, 8, 320, 1, 2), (2, 2, 48, 2, 1)])
-def test_tile_order_and_dequant_units_cover_every_block(W, E_l, C, d, cg):
+def test_tile_order_and_dequant_units_cover_every_block(W, E_l, C, d, cg, perm_local):
     Cc = C // d
     R = W * Cc                                               # rows per (chunk, expert) group
     tile_rows = BM * cg
@@ -104,10 +138,19 @@ def test_tile_order_and_dequant_units_cover_every_block(W, E_l, C, d, cg):
     perm_w, perm_q = 0, 0
     if W > 1 and Cc > tile_rows and Cc % tile_rows == 0 and W * Cc == R:
         perm_w, perm_q = W, Cc // tile_rows
-    order = [_permute_mt(i, perm_w, perm_q) for i in range(mt_count)]
-    assert sorted(order) == list(range(mt_count))            # a permutation of the m-tiles
-    if perm_q > 1:                                           # first tile of every source before any second tile
-        assert [mt // perm_q for mt in order[:W]] == list(range(W))
+    groups = d * E_l
+    my_rank = W // 2
+    coords = [_mtile_coord(i, mt_count, perm_w, perm_q, perm_local, E_l, my_rank) for i in range(groups * mt_count)]
+    assert sorted(coords) == [(g, mt) for g in range(groups) for mt in range(mt_count)]     # a permutation
+    assert [g // E_l for g, _ in coords] == sorted(g // E_l for g, _ in coords)              # chunks stay in order
+    if perm_q > 1 and not perm_local:                        # first tile of every source before any second tile
+        assert [mt // perm_q for _, mt in coords[:W]] == list(range(W))
+    if perm_q > 1 and perm_local:                            # a chunk starts with this rank's segment of every group
+        head = coords[:E_l * perm_q]
+        assert all(mt // perm_q == my_rank for _, mt in head) and sorted({g for g, _ in head}) == list(range(E_l))
+        nxt = coords[E_l * perm_q:E_l * perm_q + W - 1]      # then tile 0 of every other source, right neighbour first
+        assert [mt // perm_q for _, mt in nxt] == [(my_rank + 1 + i) % W for i in range(W - 1)]
+    order = [mt for g, mt in coords if g == 0]
     nblk = (R + GATE_BLOCK - 1) // GATE_BLOCK
     # de-quantiser units: 32 rows each, listed in tile order; every row exactly once, inside a flagged block
     units_per_block = GATE_BLOCK // 32
@@ -116,7 +159,7 @@ def test_tile_order_and_dequant_units_cover_every_block(W, E_l, C, d, cg):
         sub = u % units_per_block
         t = u // units_per_block
         b = t % cg
-        mt = _permute_mt(t // cg, perm_w, perm_q)
+        mt = order[t // cg]                                  # the units of group 0, in its tile order
         blk = mt * cg + b
         row0 = blk * GATE_BLOCK + sub * 32
         if row0 >= R:
