@@ -274,3 +274,28 @@ def test_generic_cuda_path_matches_fused():
             os.environ.pop('PLANMOE_FUSED'); os.environ.pop('PLANMOE_GEMM')
     assert layer.last_stats is not None
     assert ((y_fused.float() - y_gen.float()).abs().max() / y_gen.float().abs().max()).item() < 3e-2
+
+
+def test_plans_outside_the_fused_limits_take_the_generic_path():
+    """top-8 (the fused gate stops at top-4) and a pipeline degree above the flag table's 32 chunks must not reach the
+    fused kernels: the layer answers through the generic path instead of raising or overrunning the flags."""
+    from planmoe_b200.parallel import transport
+    layer = _layer(16, 256, 256, 8, 1.0, act='relu')
+    x = torch.randn(512, 256, device='cuda').to(torch.bfloat16).requires_grad_(True)
+    y = layer(x)
+    assert layer.last_stats['path'] == 'generic' and torch.isfinite(y.float()).all()
+    y.float().sum().backward()
+    assert torch.isfinite(x.grad.float()).all()
+    # the same layer with a per-call top-2 override is inside the limits again
+    y2 = layer(x, top_k=2)
+    assert layer.last_stats['path'] == 'fused' and torch.isfinite(y2.float()).all()
+    # degree 64 > 32 chunks: generic
+    layer2 = _layer(2, 256, 256, 2, 1.0)
+    xb = torch.randn(4096, 256, device='cuda').to(torch.bfloat16)
+    with torch.no_grad():
+        ya = layer2(xb, a2a_ffn_overlap_degree=64)
+        assert layer2.last_stats['path'] == 'generic'
+        yb = layer2(xb, a2a_ffn_overlap_degree=1)
+        assert layer2.last_stats['path'] == 'fused'
+    transport.get_transport(layer2.group).check()
+    assert torch.isfinite(ya.float()).all() and torch.isfinite(yb.float()).all()
