@@ -128,15 +128,20 @@ gate_assign_kernel(int S, int E, int K, int C, int normalize, float eps,
 {
   __shared__ int base[kMaxK][kMaxE];
   __shared__ float red[kMaxE];
-  const int tid = threadIdx.x;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int b = blockIdx.x;
-  for (int i = tid; i < K * E; i += kGateThreads) {
+  // base[k][e] = picks of expert e that rank before this block's k-th picks: every block's picks of a lower k,
+  // then the k-th picks of the blocks before this one.  One warp per (k, e), lanes strided over that list.
+  for (int i = warp; i < K * E; i += kGateWarps) {
     const int k = i / E, e = i - k * E;
+    const int n = k * nblk + b;
     int acc = 0;
-    for (int kk = 0; kk < k; ++kk)
-      for (int bb = 0; bb < nblk; ++bb) acc += blk_count[((size_t)bb * K + kk) * E + e];
-    for (int bb = 0; bb < b; ++bb) acc += blk_count[((size_t)bb * K + k) * E + e];
-    base[k][e] = acc;
+    for (int j = lane; j < n; j += 32) {
+      const int kk = j / nblk, bb = j - kk * nblk;
+      acc += blk_count[((size_t)bb * K + kk) * E + e];
+    }
+    acc = __reduce_add_sync(0xffffffffu, acc);
+    if (lane == 0) base[k][e] = acc;
   }
   __syncthreads();
 
@@ -156,16 +161,21 @@ gate_assign_kernel(int S, int E, int K, int C, int normalize, float eps,
   }
 
   if (b == 0) {
-    // l_aux = E / S^2 * sum_e (sum_t score[t][e]) * (#tokens with top-1 == e)
-    for (int e = tid; e < E; e += kGateThreads) {
+    // l_aux = E / S^2 * sum_e (sum_t score[t][e]) * (#tokens with top-1 == e); one warp per expert, lanes strided
+    // over the blocks, lane sums combined by a shuffle tree: a fixed order
+    for (int e = warp; e < E; e += kGateWarps) {
       float s = 0.f;
       int c = 0;
-      for (int bb = 0; bb < nblk; ++bb) {
+      for (int bb = lane; bb < nblk; bb += 32) {
         s += blk_score[(size_t)bb * E + e];
         c += blk_count[((size_t)bb * K + 0) * E + e];
       }
-      top1_count[e] = c;
-      red[e] = s * (float)c;
+      s = warp_sum(s);
+      c = __reduce_add_sync(0xffffffffu, c);
+      if (lane == 0) {
+        top1_count[e] = c;
+        red[e] = s * (float)c;
+      }
     }
     __syncthreads();
     if (tid == 0) {

@@ -124,8 +124,12 @@ def build(force=False, verbose=False, ptxas_info=False):
                 '-lc10', '-ltorch_cpu', '-ltorch', '-ltorch_python', '-lc10_cuda', '-ltorch_cuda',
                 '-lcudart', '-ldl', '-lpthread']
         rpath = ['-Wl,-rpath,' + p for p in ce.library_paths()]
-        _run(['g++', '-shared', '-o', TARGET] + objs + libs + rpath +
+        # link beside the target and rename: a reader (an importing process, a snapshot of the tree) sees the old
+        # or the new library, never a partly written one
+        tmp = TARGET + '.linking'
+        _run(['g++', '-shared', '-o', tmp] + objs + libs + rpath +
              ['-Wl,--no-as-needed'], verbose)
+        os.replace(tmp, TARGET)
     return TARGET
 
 

@@ -277,8 +277,8 @@ def test_generic_cuda_path_matches_fused():
 
 
 def test_plans_outside_the_fused_limits_take_the_generic_path():
-    """top-8 (the fused gate stops at top-4) and a pipeline degree above the flag table's 32 chunks must not reach the
-    fused kernels: the layer answers through the generic path instead of raising or overrunning the flags."""
+    """top-8 (the fused gate stops at top-4) must not reach the fused kernels: the layer answers through the generic
+    path; a pipeline degree above the flag table's 32 chunks is refused instead of overrunning the flags."""
     from planmoe_b200.parallel import transport
     layer = _layer(16, 256, 256, 8, 1.0, act='relu')
     x = torch.randn(512, 256, device='cuda').to(torch.bfloat16).requires_grad_(True)
@@ -289,13 +289,14 @@ def test_plans_outside_the_fused_limits_take_the_generic_path():
     # the same layer with a per-call top-2 override is inside the limits again
     y2 = layer(x, top_k=2)
     assert layer.last_stats['path'] == 'fused' and torch.isfinite(y2.float()).all()
-    # degree 64 > 32 chunks: generic
+    # a degree above the 32 chunks that both the flag tables and AllToAllStatus.max_num_split allow is refused
+    # before any kernel runs (the reference asserts the same limit, PlanMoE/impls/overlap.py:49-50)
     layer2 = _layer(2, 256, 256, 2, 1.0)
     xb = torch.randn(4096, 256, device='cuda').to(torch.bfloat16)
     with torch.no_grad():
-        ya = layer2(xb, a2a_ffn_overlap_degree=64)
-        assert layer2.last_stats['path'] == 'generic'
-        yb = layer2(xb, a2a_ffn_overlap_degree=1)
+        with pytest.raises(AssertionError, match='max_num_split'):
+            layer2(xb, a2a_ffn_overlap_degree=64)
+        yb = layer2(xb, a2a_ffn_overlap_degree=32)
         assert layer2.last_stats['path'] == 'fused'
     transport.get_transport(layer2.group).check()
-    assert torch.isfinite(ya.float()).all() and torch.isfinite(yb.float()).all()
+    assert torch.isfinite(yb.float()).all()
