@@ -5,13 +5,15 @@ Forward, per pipeline chunk j of the capacity dimension (``degree`` chunks):
     fused gate kernel      softmax + top-k + slot scan + slot map + GShard loss
     dispatch + GEMM 1      ONE launch.  A copy warp in every CTA moves token rows (picked by slot
                            map) with the bulk-copy engine straight into the receive buffer of the
-                           rank that owns the expert, 16 rows at a time, and release-adds the row
-                           count to the flag of the 128-row block they land in; the tcgen05 GEMM of
-                           the same launch reads a 128-row block of its own receive buffer as soon
-                           as that block is complete; bias + activation epilogue.  Transfer and math
-                           overlap 128 rows at a time, whatever the pipeline degree.
+                           rank that owns the expert, eight rows at a time, and once their stores
+                           have completed adds the row count to the flag of the 128-row block they
+                           land in; the tcgen05 GEMM of the same launch reads a 128-row block of its
+                           own receive buffer as soon as that block is complete; bias + activation
+                           epilogue.  Transfer and math overlap 128 rows at a time, whatever the
+                           pipeline degree.  With int8 rows a de-quantiser warp sits in between.
     expert GEMM 2          tcgen05; the epilogue stores rows straight into the combine buffer of
-                           the rank that owns the token, + release-add on its flag
+                           the rank that owns the token (bf16, or int8 with per-group scales), then
+                           adds to its flag
     combine   (gather)     waits for the flags, gate-weighted sum over the k picks
 
 Backward mirrors it (combine-backward is a dispatch-like push of dY, the two dgrad GEMMs are
