@@ -16,15 +16,17 @@ def _free_port():
 
 
 def run_workers(fn, world, backend='gloo', timeout=180, env=None, args=()):
-    """Run the workers; a failed attempt is repeated once on a fresh port (a rendezvous on a shared host can
-    lose its port between the probe and the bind), and only a second failure fails the test."""
-    try:
-        return _run_workers_once(fn, world, backend, timeout, env, args)
-    except AssertionError as first:
+    """Run the workers; a failed attempt is repeated, up to twice, on a fresh port after a short pause (a rendezvous
+    on a shared host can lose its port between the probe and the bind), and only a third failure fails the test."""
+    import time
+    failures = []
+    for attempt in range(3):
         try:
             return _run_workers_once(fn, world, backend, timeout, env, args)
-        except AssertionError as second:
-            raise AssertionError('%s\n==== first attempt ====\n%s' % (second, first))
+        except AssertionError as exc:
+            failures.append(str(exc))
+            time.sleep(1.0 + attempt)
+    raise AssertionError('\n==== earlier attempt ====\n'.join(reversed(failures)))
 
 
 def _run_workers_once(fn, world, backend, timeout, env, args):
