@@ -218,7 +218,7 @@ void launch_colsum_bf16(const void* x, float* out, int groups, long long rows, i
                         long long row_stride, long long group_stride, int fold, void* out_bf16,
                         cudaStream_t stream);
 // One or two column-sum jobs in the same two launches (see launch_colsum_bf16 for the meaning of the fields).
-// `partial`: groups * colsum_slabs(rows) * N floats; `counters`: (groups / fold) * colsum_colblocks(N) words.
+// `partial`: groups * colsum_slabs(rows) * N floats; `counters` is reserved (the two-stage form does not use it).
 struct ColsumJob {
   const void* x; float* out; void* out_bf16; float* partial; unsigned* counters;
   long long rows, row_stride, group_stride;
